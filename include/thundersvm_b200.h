@@ -1,0 +1,201 @@
+/*
+ * thundersvm_b200 - C ABI of the B200 (sm_100a) implementation of ThunderSVM's training and
+ * prediction hot path: KernelMatrix rows, the batched SMO solver and the prediction
+ * contraction.
+ *
+ * Conventions
+ *   - Every entry point returns a tsvm_status (0 = success). No C++ exception and no STL
+ *     type crosses this boundary; tsvm_last_error() returns the message of the calling
+ *     thread's last failure.
+ *   - Pointers named *_dev are device pointers on the current CUDA device, *_host are host
+ *     pointers. `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ *   - Types follow the reference (include/thundersvm/thundersvm.h:16-22): feature and
+ *     kernel values are float, alpha / f / rho / coefficients / decision values are double,
+ *     labels and ids are int.
+ *   - Kernel rows are written row-major, out[i * ld + j] = K(x_idx[i], x_j), the layout the
+ *     reference's consumers read (src/thundersvm/kernel/smo_kernel.cu:62,298).
+ *   - Handles own every device allocation they make; there is no process-global device
+ *     state.
+ */
+#ifndef THUNDERSVM_B200_H
+#define THUNDERSVM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int tsvm_status;
+enum {
+    TSVM_OK = 0,
+    TSVM_ERR_INVALID = 1,     /* bad argument (the reference CHECK-fails / LOG(FATAL)s here)   */
+    TSVM_ERR_CUDA = 2,        /* CUDA runtime / driver error                                    */
+    TSVM_ERR_OOM = 3,         /* device allocation failed (reference: std::bad_alloc,           */
+                              /* include/thundersvm/util/common.h:33-39)                        */
+    TSVM_ERR_DEVICE = 4,      /* a kernel reported an error status (bounded wait ran out, ...)  */
+    TSVM_ERR_UNSUPPORTED = 5
+};
+
+/* SvmParam::KERNEL_TYPE (include/thundersvm/svmparam.h:35-37) */
+enum { TSVM_LINEAR = 0, TSVM_POLY = 1, TSVM_RBF = 2, TSVM_SIGMOID = 3, TSVM_PRECOMPUTED = 4 };
+/* which solver: CSMOSolver, NuSMOSolver(for_svr=false), NuSMOSolver(for_svr=true) */
+enum { TSVM_SOLVER_C = 0, TSVM_SOLVER_NU_SVC = 1, TSVM_SOLVER_NU_SVR = 2 };
+/* where a caller's buffer lives */
+enum { TSVM_HOST = 0, TSVM_DEVICE = 1 };
+
+const char *tsvm_last_error(void);
+/* ABI version, bumped on any signature change. */
+int tsvm_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * KernelMatrix  (replaces include/thundersvm/kernelmatrix.h:46-72,
+ *                src/thundersvm/kernelmatrix.cpp:183-316)
+ * ---------------------------------------------------------------------------------------- */
+typedef struct tsvm_km tsvm_km;
+
+/* Constructor for dense instances: X is n x d row-major with row stride ld (floats).
+ * loc = TSVM_HOST: X is copied to the device. loc = TSVM_DEVICE: if ld is a multiple of 4 and
+ * X is 16-byte aligned the buffer is used in place (the caller keeps it alive), else copied.
+ * Computes self dots (double accumulate, float store) and the diagonal as
+ * kernelmatrix.cpp:194-247 does. Replaces KernelMatrix::KernelMatrix (kernelmatrix.cpp:183). */
+tsvm_status tsvm_km_create_dense(const float *X, int n, int d, int ld, int loc, int kernel_type, int degree,
+                                 float gamma, float coef0, void *stream, tsvm_km **out);
+
+/* Constructor for CSR instances (0-based column ids < d, ascending inside a row).
+ * Replaces KernelMatrix::KernelMatrix + CSR_DenseCSR (kernelmatrix.cpp:16-249). */
+tsvm_status tsvm_km_create_csr(const float *val, const int *row_ptr, const int *col, int n, int d, int loc,
+                               int kernel_type, int degree, float gamma, float coef0, void *stream,
+                               tsvm_km **out);
+
+void tsvm_km_destroy(tsvm_km *km);
+
+int tsvm_km_n_instances(const tsvm_km *km);   /* KernelMatrix::n_instances, kernelmatrix.h:64 */
+int tsvm_km_n_features(const tsvm_km *km);    /* KernelMatrix::n_features,  kernelmatrix.h:66 */
+long long tsvm_km_nnz(const tsvm_km *km);     /* KernelMatrix::nnz,         kernelmatrix.h:68 */
+int tsvm_km_is_dense(const tsvm_km *km);
+
+/* Device pointers owned by the handle: diag()[n] (KernelMatrix::diag, kernelmatrix.cpp:314)
+ * and the self dots [n]. */
+const float *tsvm_km_diag_dev(const tsvm_km *km);
+const float *tsvm_km_self_dot_dev(const tsvm_km *km);
+
+/* q rows of the kernel matrix: out_dev[i * ld_out + j] = K(x_idx[i], x_j), j < n.
+ * Replaces KernelMatrix::get_rows(idx, kernel_rows) (kernelmatrix.cpp:251-279) and the
+ * svm_kernel:: calls under it (get_working_set_ins, dns_csr_mul, dns_dns_mul, RBF_kernel,
+ * poly_kernel, sigmoid_kernel; include/thundersvm/kernel/kernelmatrix_kernel.h:13-66). */
+tsvm_status tsvm_km_rows_by_index(tsvm_km *km, const int *idx_dev, int q, float *out_dev, long long ld_out,
+                                  void *stream);
+
+/* Kernel values of m new instances against the stored ones: out_dev[r * ld_out + j].
+ * Features with id >= n_features are ignored in the product but counted in the test self
+ * dot, as the reference does. Replaces KernelMatrix::get_rows(instances, kernel_rows)
+ * (kernelmatrix.cpp:281-312, 385-406). The stored matrix and the batch may differ in
+ * storage (dense / CSR). */
+tsvm_status tsvm_km_rows_by_instances_dense(tsvm_km *km, const float *T_dev, int m, int dt, int ldt, float *out_dev,
+                                            long long ld_out, void *stream);
+tsvm_status tsvm_km_rows_by_instances_csr(tsvm_km *km, const float *tval_dev, const int *trow_ptr_dev,
+                                          const int *tcol_dev, int m, long long tnnz, float *out_dev,
+                                          long long ld_out, void *stream);
+
+/* Selects the dense kernel-row engine: 0 = tcgen05 tensor-core tiles (default),
+ * 1 = plain FP32 CUDA-core tiles (diagnostic cross-check only). */
+tsvm_status tsvm_km_set_dense_engine(tsvm_km *km, int engine);
+
+/* ------------------------------------------------------------------------------------------
+ * Batched SMO solver (replaces include/thundersvm/solver/csmosolver.h:16-17,
+ *                     include/thundersvm/solver/nusmosolver.h:15,
+ *                     src/thundersvm/solver/csmosolver.cpp:10-239, nusmosolver.cpp:9-136)
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+    long long outer_iters;      /* "global iter" of csmosolver.cpp:103-105                  */
+    long long local_iters;      /* "total local iter"                                        */
+    double final_diff;          /* last diff[0] (global maximal violation)                   */
+    double objective;           /* calculate_obj, csmosolver.cpp:227-239 (before nu scaling) */
+    double seconds_select;      /* host-observed phase times, seconds                        */
+    double seconds_rows;
+    double seconds_local;
+    double seconds_update;
+    double seconds_total;
+    long long kernel_rows;      /* rows of length n produced by get_rows                     */
+    long long gpu_launches;     /* kernels launched by this call                             */
+} tsvm_solve_stats;
+
+/* CSMOSolver::solve / NuSMOSolver::solve. y_dev[n] (+1/-1), alpha_dev[n] and f_dev[n] are
+ * read and updated in place on the device; *rho_host receives rho. max_iter = -1 means no
+ * limit on outer iterations (csmosolver.cpp:110). stats_host may be NULL. */
+tsvm_status tsvm_smo_solve(tsvm_km *km, int solver_kind, const int *y_dev, double *alpha_dev, double *f_dev,
+                           double eps, double Cp, double Cn, int ws_size, int max_iter, double *rho_host,
+                           tsvm_solve_stats *stats_host, void *stream);
+
+/* SvmModel::get_working_set_size (src/thundersvm/model/svmmodel.cpp:437-451) with the
+ * memory budget in bytes. Returns the working-set size, or -1 when the budget is already
+ * exceeded (the reference throws std::bad_alloc there). */
+int tsvm_working_set_size(int n_instances, int n_features, size_t max_mem_bytes, size_t used_bytes);
+
+/* ---- the solver's steps, one entry point each (used by the column-sharded multi-GPU
+ *      driver and by the unit tests) ---------------------------------------------------- */
+typedef struct tsvm_ws tsvm_ws;   /* scratch for working-set selection */
+tsvm_status tsvm_ws_create(int n_max, int ws_max, tsvm_ws **out);
+void tsvm_ws_destroy(tsvm_ws *w);
+
+/* Candidate lists for the working set: for each of the solver's pointer walks
+ * (C: I_up ascending f, I_low descending f; nu: the same per class) the first `want`
+ * instances in (f, id) order that are not flagged in in_ws_dev[n] (0/1 bytes, may be NULL).
+ * cand_f_dev[list * want + r], cand_id_dev[...] (id -1 = list exhausted). id_offset is
+ * added to every reported id (a shard's first global column). Replaces svm_kernel::sort_f
+ * (smo_kernel.cu:312-315). */
+tsvm_status tsvm_ws_candidates(tsvm_ws *w, int solver_kind, int n, const double *f_dev, const double *alpha_dev,
+                               const int *y_dev, const unsigned char *in_ws_dev, double Cp, double Cn, int want,
+                               int id_offset, double *cand_f_dev, int *cand_id_dev, void *stream);
+
+/* Alternating merge of the candidate lists (each of length `len`, sorted as above) into
+ * `want` distinct ids: CSMOSolver::select_working_set (csmosolver.cpp:123-165) /
+ * NuSMOSolver::select_working_set (nusmosolver.cpp:48-118) restricted to the candidates. */
+tsvm_status tsvm_ws_merge(tsvm_ws *w, int solver_kind, const double *cand_f_dev, const int *cand_id_dev, int len,
+                          int want, int *out_ids_dev, void *stream);
+
+/* Full selection = candidates + merge on one device. */
+tsvm_status tsvm_select_working_set(tsvm_ws *w, int solver_kind, int n, const double *f_dev,
+                                    const double *alpha_dev, const int *y_dev, const unsigned char *in_ws_dev,
+                                    double Cp, double Cn, int want, int *out_ids_dev, void *stream);
+
+/* Local SMO on one working set: svm_kernel::c_smo_solve / nu_smo_solve
+ * (smo_kernel.cu:28-287). kww_dev is the ws x ws block K(x_ws[a], x_ws[b]) (row-major,
+ * stride ws); y/f/alpha/diag_ws_dev hold the working set's values in slot order. Outputs:
+ * alpha_ws_dev (updated), alpha_diff_dev[ws] = -(a - a_old) * y, diff_dev[0] = first gap,
+ * diff_dev[1] = #local iterations. */
+tsvm_status tsvm_local_smo(int solver_kind, int ws_size, const float *kww_dev, const float *diag_ws_dev,
+                           const int *y_ws_dev, const double *f_ws_dev, double *alpha_ws_dev,
+                           double *alpha_diff_dev, double Cp, double Cn, double eps, int max_iter, double *diff_dev,
+                           void *stream);
+
+/* f[j] -= sum_i alpha_diff[i] * rows[i * ld + j] (zero alpha_diff rows skipped, double
+ * accumulation): svm_kernel::update_f (smo_kernel.cu:289-310). */
+tsvm_status tsvm_update_f(double *f_dev, int n, const double *alpha_diff_dev, int ws_size, const float *rows_dev,
+                          long long ld, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Prediction (replaces SvmModel::predict_dec_values, src/thundersvm/model/svmmodel.cpp:74-117
+ *             and svm_kernel::sum_kernel_values, kernelmatrix_kernel.cu:69-97,154-162)
+ * ---------------------------------------------------------------------------------------- */
+
+/* dec_dev[r * nb + k] = sum over the support vectors of pair k of coef * K(sv, x_r) - rho[k],
+ * nb = n_classes (n_classes - 1) / 2, pairs ordered (0,1),(0,2),...; coef_dev is the
+ * (n_classes - 1) x n_sv layout of include/thundersvm/model/svmmodel.h:155-164, sv_count_host
+ * the per-class support-vector counts, rho_dev[nb]. km_sv holds the support vectors. The test
+ * batch is dense (T_dev != NULL) or CSR. Batching over the test rows is internal. */
+tsvm_status tsvm_predict_dec(tsvm_km *km_sv, const double *coef_dev, const int *sv_count_host,
+                             const double *rho_dev, int n_classes, int m, const float *T_dev, int dt, int ldt,
+                             const float *tval_dev, const int *trow_ptr_dev, const int *tcol_dev, long long tnnz,
+                             double *dec_dev, size_t max_mem_bytes, void *stream);
+
+/* SVC::predict_label voting (src/thundersvm/model/svc.cpp:265-289): out_dev[r] = index of the
+ * winning class. */
+tsvm_status tsvm_vote(const double *dec_dev, int m, int n_classes, int *out_dev, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* THUNDERSVM_B200_H */

@@ -146,7 +146,7 @@ void oracle_kernel_rows_ins(int n, int n_features, const float *val, const int *
         float s = 0;
         for (int p = trow_ptr[c]; p < trow_ptr[c + 1]; ++p) {
             if (tcol[p] < n_features) B[(size_t) c * n_features + tcol[p]] = tval[p];
-            s += tval[p] * tval[p];
+            s = fmaf(tval[p], tval[p], s);   /* the reference's Release build fuses this (FMA targets) */
         }
         tsd[c] = s;
     }

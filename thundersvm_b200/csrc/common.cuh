@@ -1,0 +1,170 @@
+// Shared helpers for the sm_100a kernels: status/error plumbing, launch accounting,
+// order-preserving keys and warp reductions.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include <math.h>
+#include "../../include/thundersvm_b200.h"
+
+namespace tsvm {
+
+void set_error(const char *fmt, ...);
+long long launch_count();
+void count_launch(int k = 1);
+
+#define TSVM_CUDA(expr)                                                                          \
+    do {                                                                                         \
+        cudaError_t e__ = (expr);                                                                \
+        if (e__ != cudaSuccess) {                                                                \
+            tsvm::set_error("%s failed at %s:%d: %s", #expr, __FILE__, __LINE__,                 \
+                            cudaGetErrorString(e__));                                            \
+            return e__ == cudaErrorMemoryAllocation ? TSVM_ERR_OOM : TSVM_ERR_CUDA;              \
+        }                                                                                        \
+    } while (0)
+
+#define TSVM_TRY(expr)                        \
+    do {                                      \
+        tsvm_status s__ = (expr);             \
+        if (s__ != TSVM_OK) return s__;       \
+    } while (0)
+
+#define TSVM_REQUIRE(cond, ...)               \
+    do {                                      \
+        if (!(cond)) {                        \
+            tsvm::set_error(__VA_ARGS__);     \
+            return TSVM_ERR_INVALID;          \
+        }                                     \
+    } while (0)
+
+// Launch + account + check the launch (not the execution).
+#define TSVM_LAUNCH(kernel, grid, block, smem, stream, ...)                                      \
+    do {                                                                                         \
+        kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__);                              \
+        tsvm::count_launch();                                                                    \
+        TSVM_CUDA(cudaPeekAtLastError());                                                        \
+    } while (0)
+
+template <typename T>
+inline tsvm_status dev_alloc(T **p, size_t count) {
+    *p = nullptr;
+    if (count == 0) count = 1;
+    TSVM_CUDA(cudaMalloc((void **) p, count * sizeof(T)));
+    return TSVM_OK;
+}
+
+inline int ceil_div(long long a, long long b) { return (int) ((a + b - 1) / b); }
+
+// ---- device helpers ------------------------------------------------------------------
+
+// Monotone map double -> uint64 (ascending). -0.0 and +0.0 map to neighbouring keys.
+__host__ __device__ __forceinline__ unsigned long long ordered_key(double v) {
+#ifdef __CUDA_ARCH__
+    unsigned long long b = (unsigned long long) __double_as_longlong(v);
+#else
+    unsigned long long b;
+    memcpy(&b, &v, 8);
+#endif
+    return (b & 0x8000000000000000ull) ? ~b : (b | 0x8000000000000000ull);
+}
+
+__host__ __device__ __forceinline__ double key_to_double(unsigned long long k) {
+    unsigned long long b = (k & 0x8000000000000000ull) ? (k & 0x7fffffffffffffffull) : ~k;
+#ifdef __CUDA_ARCH__
+    return __longlong_as_double((long long) b);
+#else
+    double v;
+    memcpy(&v, &b, 8);
+    return v;
+#endif
+}
+
+// I_up / I_low / free membership, include/thundersvm/kernel/smo_kernel.h:13-23
+__host__ __device__ __forceinline__ bool in_I_up(double a, int y, double Cp, double Cn) {
+    return (y > 0 && a < Cp) || (y < 0 && a > 0);
+}
+__host__ __device__ __forceinline__ bool in_I_low(double a, int y, double Cp, double Cn) {
+    return (y > 0 && a > 0) || (y < 0 && a < Cn);
+}
+__host__ __device__ __forceinline__ bool is_free_sv(double a, int y, double Cp, double Cn) {
+    return a > 0 && (y > 0 ? a < Cp : a < Cn);
+}
+
+#ifdef __CUDACC__
+// Warp-wide minimum of a 64-bit key and the lowest `slot` among the lanes that hold it.
+__device__ __forceinline__ void warp_argmin_u64(unsigned long long &key, int &slot) {
+    const unsigned full = 0xffffffffu;
+    unsigned hi = (unsigned) (key >> 32), lo = (unsigned) key;
+    unsigned mhi = __reduce_min_sync(full, hi);
+    unsigned mlo = __reduce_min_sync(full, hi == mhi ? lo : 0xffffffffu);
+    bool win = (hi == mhi) && (lo == mlo);
+    unsigned ms = __reduce_min_sync(full, win ? (unsigned) slot : 0x7fffffffu);
+    key = ((unsigned long long) mhi << 32) | mlo;
+    slot = (int) ms;
+}
+
+__device__ __forceinline__ unsigned long long warp_min_u64(unsigned long long key) {
+    const unsigned full = 0xffffffffu;
+    unsigned hi = (unsigned) (key >> 32), lo = (unsigned) key;
+    unsigned mhi = __reduce_min_sync(full, hi);
+    unsigned mlo = __reduce_min_sync(full, hi == mhi ? lo : 0xffffffffu);
+    return ((unsigned long long) mhi << 32) | mlo;
+}
+#endif
+
+// The reference's kernel functions (src/thundersvm/kernel/kernelmatrix_kernel.cu:47-67,
+// 141-152): RBF expf(-(sd_i + sd_j - 2 dot) gamma), poly powf(gamma dot + coef0, degree),
+// sigmoid tanhf(gamma dot + coef0), linear = dot.
+struct KernelFn {
+    int type;
+    int degree;
+    float gamma;
+    float coef0;
+};
+
+__device__ __forceinline__ float apply_kernel(const KernelFn &k, float dot, float sd_i, float sd_j) {
+    switch (k.type) {
+        case TSVM_RBF:
+        case TSVM_PRECOMPUTED:
+            return expf(-(sd_i + sd_j - dot * 2.0f) * k.gamma);
+        case TSVM_POLY:
+            return powf(k.gamma * dot + k.coef0, (float) k.degree);
+        case TSVM_SIGMOID:
+            return tanhf(k.gamma * dot + k.coef0);
+        default:
+            return dot;
+    }
+}
+
+}  // namespace tsvm
+
+// Opaque handle behind tsvm_km.
+struct tsvm_km {
+    int n = 0, d = 0;
+    long long nnz = 0;
+    bool dense = true;
+    tsvm::KernelFn fn{};
+    int engine = 0;                 // 0 = tcgen05, 1 = CUDA-core FP32
+    // dense storage: row-major, row stride ldx floats (multiple of 4)
+    const float *X = nullptr;
+    int ldx = 0;
+    float *X_owned = nullptr;
+    float *Xhi = nullptr, *Xlo = nullptr;   // TF32 split of X, row stride d_pad
+    int d_pad = 0;
+    // CSR storage
+    const float *val = nullptr;
+    const int *row_ptr = nullptr, *col = nullptr;
+    float *val_owned = nullptr;
+    int *row_ptr_owned = nullptr, *col_owned = nullptr;
+    float *self_dot = nullptr, *diag = nullptr;
+    // scratch for the rows whose kernel values are requested
+    int w_cap = 0;                  // rows the scratch below can hold
+    float *W = nullptr;             // dense engines: w_cap x d_pad (row-major), FP32
+    float *Whi = nullptr, *Wlo = nullptr;   // TF32 split of W
+    float *WT = nullptr;            // CSR engine: d x wt_ld, column = requested row
+    int wt_ld = 0;
+    float *sd_rows = nullptr;       // self dots of the requested rows [w_cap]
+    int *status_dev = nullptr;      // device status word written by kernels with bounded waits
+    int *status_host = nullptr;     // pinned mirror
+};

@@ -1,0 +1,567 @@
+// KernelMatrix on the device: construction, self dots / diagonal, and kernel rows for the
+// CSR engine and the CUDA-core dense engine. The tensor-core dense engine lives in
+// dense_tc.cu. Reference behaviour: src/thundersvm/kernelmatrix.cpp:183-316,385-406.
+#include "common.cuh"
+#include <string.h>
+#include <atomic>
+
+namespace tsvm {
+
+static thread_local char g_err[512] = "";
+static std::atomic<long long> g_launches{0};
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+long long launch_count() { return g_launches.load(); }
+void count_launch(int k) { g_launches.fetch_add(k); }
+
+tsvm_status launch_dense_tc(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st);  // dense_tc.cu
+
+// ---- construction kernels ---------------------------------------------------------------
+
+// self_dot[i] = float(sum_k double(x_ik)^2), one warp per row (kernelmatrix.cpp:194-204).
+__global__ void self_dot_dense_kernel(const float *__restrict__ X, int n, int d, int ld, float *__restrict__ out) {
+    int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (row >= n) return;
+    const float *x = X + (size_t) row * ld;
+    double s = 0;
+    for (int k = lane; k < d; k += 32) { double v = x[k]; s += v * v; }
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) out[row] = (float) s;
+}
+
+__global__ void self_dot_csr_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr, int n,
+                                    float *__restrict__ out) {
+    int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (row >= n) return;
+    double s = 0;
+    for (int p = row_ptr[row] + lane; p < row_ptr[row + 1]; p += 32) { double v = val[p]; s += v * v; }
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) out[row] = (float) s;
+}
+
+// diag (kernelmatrix.cpp:225-247)
+__global__ void diag_kernel(const float *__restrict__ sd, int n, KernelFn fn, float *__restrict__ out) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = sd[i];
+    switch (fn.type) {
+        case TSVM_RBF: case TSVM_PRECOMPUTED: v = 1.0f; break;
+        case TSVM_POLY: v = powf(fn.gamma * v + fn.coef0, (float) fn.degree); break;
+        case TSVM_SIGMOID: v = tanhf(fn.gamma * v + fn.coef0); break;
+        default: break;
+    }
+    out[i] = v;
+}
+
+// Self dot of a batch of new instances, accumulated sequentially in float in storage order
+// as kernelmatrix.cpp:288-296 does (one thread per row keeps that order).
+__global__ void self_dot_seq_dense_kernel(const float *__restrict__ T, int m, int dt, int ldt,
+                                          float *__restrict__ out) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= m) return;
+    const float *x = T + (size_t) r * ldt;
+    float s = 0;
+    for (int k = 0; k < dt; ++k) s = fmaf(x[k], x[k], s);
+    out[r] = s;
+}
+
+__global__ void self_dot_seq_csr_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr, int m,
+                                        float *__restrict__ out) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= m) return;
+    float s = 0;
+    for (int p = row_ptr[r]; p < row_ptr[r + 1]; ++p) s = fmaf(val[p], val[p], s);
+    out[r] = s;
+}
+
+// TF32 split x = hi + lo (+ <= 2^-22 |x|): hi = x rounded to TF32, lo = (x - hi) rounded to
+// TF32, both with the 13 low mantissa bits cleared so that the tensor core reads exactly
+// these values whether it truncates or rounds its FP32 operands.
+__device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
+    unsigned h, l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    hi = __uint_as_float(h);
+    float r = x - hi;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(r));
+    lo = __uint_as_float(l);
+}
+
+// Xhi/Xlo[row * d_pad + k] from X[row * ld + k]; columns d..d_pad-1 are zero.
+__global__ void split_rows_kernel(const float *__restrict__ X, int n, int d, int ld, int d_pad,
+                                  float *__restrict__ hi, float *__restrict__ lo) {
+    size_t total = (size_t) n * d_pad;
+    for (size_t e = (size_t) blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t) gridDim.x * blockDim.x) {
+        int row = (int) (e / d_pad), k = (int) (e % d_pad);
+        float h = 0, l = 0;
+        if (k < d) split_tf32(X[(size_t) row * ld + k], h, l);
+        hi[e] = h;
+        lo[e] = l;
+    }
+}
+
+// ---- gathering the requested rows ----------------------------------------------------------
+
+// W[i][0..d_pad) = X[idx[i]][0..d) (zero padded); optional TF32 split; sd_rows[i].
+__global__ void gather_rows_dense_kernel(const float *__restrict__ X, int ld, int d, int d_pad,
+                                         const int *__restrict__ idx, int m, const float *__restrict__ sd,
+                                         float *__restrict__ W, float *__restrict__ Whi, float *__restrict__ Wlo,
+                                         float *__restrict__ sd_rows) {
+    int i = blockIdx.x;
+    if (i >= m) return;
+    int r = idx[i];
+    const float *x = X + (size_t) r * ld;
+    for (int k = threadIdx.x; k < d_pad; k += blockDim.x) {
+        float v = k < d ? x[k] : 0.0f;
+        if (W) W[(size_t) i * d_pad + k] = v;
+        if (Whi) {
+            float h, l;
+            split_tf32(v, h, l);
+            Whi[(size_t) i * d_pad + k] = h;
+            Wlo[(size_t) i * d_pad + k] = l;
+        }
+    }
+    if (threadIdx.x == 0) sd_rows[i] = sd[r];
+}
+
+// Same for a batch of new dense instances T (m x dt, stride ldt); features >= d are dropped.
+__global__ void stage_rows_dense_kernel(const float *__restrict__ T, int ldt, int dt, int d, int d_pad, int m,
+                                        float *__restrict__ W, float *__restrict__ Whi, float *__restrict__ Wlo) {
+    int i = blockIdx.x;
+    if (i >= m) return;
+    const float *x = T + (size_t) i * ldt;
+    for (int k = threadIdx.x; k < d_pad; k += blockDim.x) {
+        float v = (k < d && k < dt) ? x[k] : 0.0f;
+        if (W) W[(size_t) i * d_pad + k] = v;
+        if (Whi) {
+            float h, l;
+            split_tf32(v, h, l);
+            Whi[(size_t) i * d_pad + k] = h;
+            Wlo[(size_t) i * d_pad + k] = l;
+        }
+    }
+}
+
+// CSR rows -> zero-initialised dense W (row-major) for the dense engines.
+__global__ void scatter_csr_to_w_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr,
+                                        const int *__restrict__ col, const int *__restrict__ idx, int m, int d,
+                                        int d_pad, float *__restrict__ W, float *__restrict__ Whi,
+                                        float *__restrict__ Wlo) {
+    int i = blockIdx.x;
+    if (i >= m) return;
+    int r = idx ? idx[i] : i;
+    for (int p = row_ptr[r] + threadIdx.x; p < row_ptr[r + 1]; p += blockDim.x) {
+        int c = col[p];
+        if (c >= d) continue;
+        float v = val[p];
+        if (W) W[(size_t) i * d_pad + c] = v;
+        if (Whi) {
+            float h, l;
+            split_tf32(v, h, l);
+            Whi[(size_t) i * d_pad + c] = h;
+            Wlo[(size_t) i * d_pad + c] = l;
+        }
+    }
+}
+
+// CSR engine staging: WT[c * wt_ld + i] = value of feature c in requested row i. WT is kept
+// all-zero between calls: `clear` = true writes zeros back at the same places.
+__global__ void scatter_csr_to_wt_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr,
+                                         const int *__restrict__ col, const int *__restrict__ idx, int m, int d,
+                                         int wt_ld, float *__restrict__ WT, const float *__restrict__ sd,
+                                         float *__restrict__ sd_rows, bool clear) {
+    int i = blockIdx.x;
+    if (i >= m) return;
+    int r = idx ? idx[i] : i;
+    for (int p = row_ptr[r] + threadIdx.x; p < row_ptr[r + 1]; p += blockDim.x) {
+        int c = col[p];
+        if (c < d) WT[(size_t) c * wt_ld + i] = clear ? 0.0f : val[p];
+    }
+    if (!clear && sd && threadIdx.x == 0) sd_rows[i] = sd[r];
+}
+
+// WT from a dense batch T (m x dt): WT[c * wt_ld + i] = T[i][c] for c < min(d, dt).
+__global__ void transpose_dense_to_wt_kernel(const float *__restrict__ T, int ldt, int dt, int d, int m, int wt_ld,
+                                             float *__restrict__ WT, bool clear) {
+    __shared__ float tile[32][33];
+    int c0 = blockIdx.x * 32, i0 = blockIdx.y * 32;
+    int tx = threadIdx.x, ty = threadIdx.y;   // 32 x 8
+    int lim = d < dt ? d : dt;
+    for (int r = ty; r < 32; r += 8) {
+        int i = i0 + r, c = c0 + tx;
+        tile[r][tx] = (!clear && i < m && c < lim) ? T[(size_t) i * ldt + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        int c = c0 + r, i = i0 + tx;
+        if (c < d && i < m) WT[(size_t) c * wt_ld + i] = tile[tx][r];
+    }
+}
+
+// ---- CUDA-core dense engine: out[i][j] = kfn(sum_k W[i][k] X[j][k]) -------------------------
+// 64 instances x 64 requested rows per block, 16-wide k slabs, 4x4 outputs per thread.
+__global__ void __launch_bounds__(256)
+dense_rows_simt_kernel(const float *__restrict__ X, int ldx, int n, const float *__restrict__ W, int ldw, int m,
+                       int d_pad, const float *__restrict__ sd, const float *__restrict__ sd_rows, KernelFn fn,
+                       float *__restrict__ out, long long ld_out) {
+    __shared__ float xs[16][64 + 4];
+    __shared__ float wsm[16][64 + 4];
+    const int j0 = blockIdx.x * 64, i0 = blockIdx.y * 64;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
+    const int lr = tid >> 2, lk = (tid & 3) * 4;   // 64 rows x 4 float4 per slab
+    for (int k0 = 0; k0 < d_pad; k0 += 16) {
+        float4 xv = make_float4(0, 0, 0, 0), wv = make_float4(0, 0, 0, 0);
+        if (j0 + lr < n && k0 + lk < d_pad) xv = *reinterpret_cast<const float4 *>(X + (size_t) (j0 + lr) * ldx + k0 + lk);
+        if (i0 + lr < m && k0 + lk < d_pad) wv = *reinterpret_cast<const float4 *>(W + (size_t) (i0 + lr) * ldw + k0 + lk);
+        __syncthreads();
+        xs[lk + 0][lr] = xv.x; xs[lk + 1][lr] = xv.y; xs[lk + 2][lr] = xv.z; xs[lk + 3][lr] = xv.w;
+        wsm[lk + 0][lr] = wv.x; wsm[lk + 1][lr] = wv.y; wsm[lk + 2][lr] = wv.z; wsm[lk + 3][lr] = wv.w;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float xa[4], wb[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) { xa[a] = xs[k][tx + 16 * a]; wb[a] = wsm[k][ty + 16 * a]; }
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+#pragma unroll
+                for (int a = 0; a < 4; ++a) acc[b][a] = fmaf(wb[b], xa[a], acc[b][a]);
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        int i = i0 + ty + 16 * b;
+        if (i >= m) continue;
+        float sdi = sd_rows[i];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            int j = j0 + tx + 16 * a;
+            if (j < n) out[(size_t) i * ld_out + j] = apply_kernel(fn, acc[b][a], sdi, sd[j]);
+        }
+    }
+}
+
+// ---- CSR engine ------------------------------------------------------------------------------
+// One warp per stored instance; lanes own requested rows c = 4*lane + 128*v (float4 each). For
+// every stored entry (col, val) in storage order: acc[c] += val * WT[col][c], the same FP32
+// recurrence as the reference's sparse x dense product (kernelmatrix_kernel.cpp:149-160).
+// A block covers 32 consecutive instances and transposes its results through shared memory so
+// that every requested row receives 128-byte coalesced stores.
+template <int NV>
+__global__ void __launch_bounds__(256)
+csr_rows_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr, const int *__restrict__ col, int n,
+                const float *__restrict__ WT, int wt_ld, int m, const float *__restrict__ sd,
+                const float *__restrict__ sd_rows, KernelFn fn, float *__restrict__ out, long long ld_out) {
+    extern __shared__ float tile[];   // [NV*128][33]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j0 = blockIdx.x * 32;
+    for (int jj = warp; jj < 32; jj += 8) {
+        const int j = j0 + jj;
+        float4 acc[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) acc[v] = make_float4(0, 0, 0, 0);
+        if (j < n) {
+            const int b = row_ptr[j], e = row_ptr[j + 1];
+            for (int p0 = b; p0 < e; p0 += 32) {
+                int cc = 0;
+                float vv = 0;
+                if (p0 + lane < e) { cc = col[p0 + lane]; vv = val[p0 + lane]; }
+                const int cnt = min(32, e - p0);
+                for (int t = 0; t < cnt; ++t) {
+                    const int c = __shfl_sync(0xffffffffu, cc, t);
+                    const float x = __shfl_sync(0xffffffffu, vv, t);
+                    const float4 *w = reinterpret_cast<const float4 *>(WT + (size_t) c * wt_ld) + lane;
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) {
+                        float4 wv = __ldg(w + 32 * v);
+                        acc[v].x = fmaf(x, wv.x, acc[v].x);
+                        acc[v].y = fmaf(x, wv.y, acc[v].y);
+                        acc[v].z = fmaf(x, wv.z, acc[v].z);
+                        acc[v].w = fmaf(x, wv.w, acc[v].w);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const int c = 128 * v + 4 * lane;
+            tile[(c + 0) * 33 + jj] = acc[v].x;
+            tile[(c + 1) * 33 + jj] = acc[v].y;
+            tile[(c + 2) * 33 + jj] = acc[v].z;
+            tile[(c + 3) * 33 + jj] = acc[v].w;
+        }
+    }
+    __syncthreads();
+    const int j = j0 + lane;
+    const float sdj = j < n ? sd[j] : 0.0f;
+    for (int c = warp; c < m; c += 8) {
+        if (j < n) out[(size_t) c * ld_out + j] = apply_kernel(fn, tile[c * 33 + lane], sd_rows[c], sdj);
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+
+static tsvm_status ensure_scratch(tsvm_km *km, int m) {
+    if (m <= km->w_cap) return TSVM_OK;
+    int cap = 128;
+    while (cap < m) cap *= 2;
+    cudaFree(km->W); cudaFree(km->Whi); cudaFree(km->Wlo); cudaFree(km->WT); cudaFree(km->sd_rows);
+    km->W = km->Whi = km->Wlo = km->WT = km->sd_rows = nullptr;
+    km->w_cap = 0;
+    TSVM_TRY(dev_alloc(&km->sd_rows, (size_t) cap));
+    if (km->dense) {
+        TSVM_TRY(dev_alloc(&km->W, (size_t) cap * km->d_pad));
+        TSVM_TRY(dev_alloc(&km->Whi, (size_t) cap * km->d_pad));
+        TSVM_TRY(dev_alloc(&km->Wlo, (size_t) cap * km->d_pad));
+    } else {
+        km->wt_ld = cap;
+        TSVM_TRY(dev_alloc(&km->WT, (size_t) km->d * cap));
+        TSVM_CUDA(cudaMemset(km->WT, 0, sizeof(float) * (size_t) km->d * cap));
+    }
+    km->w_cap = cap;
+    return TSVM_OK;
+}
+
+static tsvm_status finish_create(tsvm_km *km, cudaStream_t st) {
+    TSVM_TRY(dev_alloc(&km->self_dot, (size_t) km->n));
+    TSVM_TRY(dev_alloc(&km->diag, (size_t) km->n));
+    TSVM_TRY(dev_alloc(&km->status_dev, 4));
+    TSVM_CUDA(cudaMemsetAsync(km->status_dev, 0, 4 * sizeof(int), st));
+    TSVM_CUDA(cudaMallocHost((void **) &km->status_host, 4 * sizeof(int)));
+    const int blocks = ceil_div((long long) km->n * 32, 256);
+    if (km->dense)
+        TSVM_LAUNCH(self_dot_dense_kernel, blocks, 256, 0, st, km->X, km->n, km->d, km->ldx, km->self_dot);
+    else
+        TSVM_LAUNCH(self_dot_csr_kernel, blocks, 256, 0, st, km->val, km->row_ptr, km->n, km->self_dot);
+    TSVM_LAUNCH(diag_kernel, ceil_div(km->n, 256), 256, 0, st, km->self_dot, km->n, km->fn, km->diag);
+    if (km->dense) {
+        TSVM_TRY(dev_alloc(&km->Xhi, (size_t) km->n * km->d_pad));
+        TSVM_TRY(dev_alloc(&km->Xlo, (size_t) km->n * km->d_pad));
+        TSVM_LAUNCH(split_rows_kernel, 148 * 8, 256, 0, st, km->X, km->n, km->d, km->ldx, km->d_pad, km->Xhi,
+                    km->Xlo);
+    }
+    return TSVM_OK;
+}
+
+static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
+    // W / WT and sd_rows are staged; run the engine.
+    if (km->dense) {
+        if (km->engine == 0) return launch_dense_tc(km, m, out, ld_out, st);
+        dim3 grid(ceil_div(km->n, 64), ceil_div(m, 64));
+        TSVM_LAUNCH(dense_rows_simt_kernel, grid, 256, 0, st, km->X, km->ldx, km->n, km->W, km->d_pad, m, km->d_pad,
+                    km->self_dot, km->sd_rows, km->fn, out, ld_out);
+        return TSVM_OK;
+    }
+    const int nv = ceil_div(m, 128);
+    const int grid = ceil_div(km->n, 32);
+#define CSR_CASE(NV)                                                                                             \
+    {                                                                                                            \
+        size_t smem = (size_t) (NV) * 128 * 33 * sizeof(float);                                                  \
+        TSVM_CUDA(cudaFuncSetAttribute(csr_rows_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                                       (int) smem));                                                             \
+        TSVM_LAUNCH(csr_rows_kernel<NV>, grid, 256, smem, st, km->val, km->row_ptr, km->col, km->n, km->WT,      \
+                    km->wt_ld, m, km->self_dot, km->sd_rows, km->fn, out, ld_out);                               \
+    }
+    if (nv <= 1) CSR_CASE(1)
+    else if (nv <= 2) CSR_CASE(2)
+    else if (nv <= 4) CSR_CASE(4)
+    else if (nv <= 8) CSR_CASE(8)
+    else { set_error("CSR engine handles at most 1024 rows per call, got %d", m); return TSVM_ERR_INVALID; }
+#undef CSR_CASE
+    return TSVM_OK;
+}
+
+}  // namespace tsvm
+
+using namespace tsvm;
+
+extern "C" {
+
+const char *tsvm_last_error(void) { return tsvm::g_err; }
+int tsvm_abi_version(void) { return 1; }
+
+tsvm_status tsvm_km_create_dense(const float *X, int n, int d, int ld, int loc, int kernel_type, int degree,
+                                 float gamma, float coef0, void *stream, tsvm_km **out) {
+    TSVM_REQUIRE(out && X && n > 0 && d > 0 && ld >= d, "km_create_dense: bad arguments (n=%d d=%d ld=%d)", n, d, ld);
+    TSVM_REQUIRE(kernel_type >= TSVM_LINEAR && kernel_type <= TSVM_PRECOMPUTED, "unknown kernel type %d", kernel_type);
+    cudaStream_t st = (cudaStream_t) stream;
+    tsvm_km *km = new tsvm_km;
+    *out = nullptr;
+    km->n = n; km->d = d; km->nnz = (long long) n * d; km->dense = true;
+    km->fn = KernelFn{kernel_type, degree, gamma, coef0};
+    km->d_pad = (d + 3) & ~3;
+    tsvm_status s = TSVM_OK;
+    bool in_place = loc == TSVM_DEVICE && (d % 4 == 0) && (ld % 4 == 0) && (((uintptr_t) X & 15) == 0) && ld >= km->d_pad;
+    if (in_place) { km->X = X; km->ldx = ld; }
+    else {
+        km->ldx = km->d_pad;
+        s = dev_alloc(&km->X_owned, (size_t) n * km->d_pad);
+        if (s == TSVM_OK && km->d_pad != d) {
+            cudaError_t e = cudaMemsetAsync(km->X_owned, 0, sizeof(float) * (size_t) n * km->d_pad, st);
+            if (e != cudaSuccess) { set_error("memset failed: %s", cudaGetErrorString(e)); s = TSVM_ERR_CUDA; }
+        }
+        if (s == TSVM_OK) {
+            cudaError_t e = cudaMemcpy2DAsync(km->X_owned, sizeof(float) * km->d_pad, X, sizeof(float) * ld,
+                                              sizeof(float) * d, n,
+                                              loc == TSVM_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
+                                              st);
+            if (e != cudaSuccess) { set_error("copy of X failed: %s", cudaGetErrorString(e)); s = TSVM_ERR_CUDA; }
+        }
+        km->X = km->X_owned;
+    }
+    if (s == TSVM_OK) s = finish_create(km, st);
+    if (s != TSVM_OK) { tsvm_km_destroy(km); return s; }
+    *out = km;
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_km_create_csr(const float *val, const int *row_ptr, const int *col, int n, int d, int loc,
+                               int kernel_type, int degree, float gamma, float coef0, void *stream, tsvm_km **out) {
+    TSVM_REQUIRE(out && row_ptr && n > 0 && d > 0, "km_create_csr: bad arguments (n=%d d=%d)", n, d);
+    TSVM_REQUIRE(kernel_type >= TSVM_LINEAR && kernel_type <= TSVM_PRECOMPUTED, "unknown kernel type %d", kernel_type);
+    cudaStream_t st = (cudaStream_t) stream;
+    tsvm_km *km = new tsvm_km;
+    *out = nullptr;
+    km->n = n; km->d = d; km->dense = false;
+    km->fn = KernelFn{kernel_type, degree, gamma, coef0};
+    tsvm_status s = TSVM_OK;
+    int last = 0;
+    if (loc == TSVM_HOST) last = row_ptr[n];
+    else if (cudaMemcpy(&last, row_ptr + n, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) s = TSVM_ERR_CUDA;
+    km->nnz = last;
+    if (s == TSVM_OK && loc == TSVM_DEVICE) { km->val = val; km->row_ptr = row_ptr; km->col = col; }
+    else if (s == TSVM_OK) {
+        s = dev_alloc(&km->val_owned, (size_t) last);
+        if (s == TSVM_OK) s = dev_alloc(&km->col_owned, (size_t) last);
+        if (s == TSVM_OK) s = dev_alloc(&km->row_ptr_owned, (size_t) n + 1);
+        if (s == TSVM_OK) {
+            cudaError_t e = cudaMemcpyAsync(km->val_owned, val, sizeof(float) * last, cudaMemcpyHostToDevice, st);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(km->col_owned, col, sizeof(int) * last, cudaMemcpyHostToDevice, st);
+            if (e == cudaSuccess)
+                e = cudaMemcpyAsync(km->row_ptr_owned, row_ptr, sizeof(int) * ((size_t) n + 1), cudaMemcpyHostToDevice, st);
+            if (e != cudaSuccess) { set_error("copy of CSR failed: %s", cudaGetErrorString(e)); s = TSVM_ERR_CUDA; }
+        }
+        km->val = km->val_owned; km->col = km->col_owned; km->row_ptr = km->row_ptr_owned;
+    }
+    if (s == TSVM_OK) s = finish_create(km, st);
+    if (s != TSVM_OK) { tsvm_km_destroy(km); return s; }
+    *out = km;
+    return TSVM_OK;
+}
+
+void tsvm_km_destroy(tsvm_km *km) {
+    if (!km) return;
+    cudaFree(km->X_owned); cudaFree(km->Xhi); cudaFree(km->Xlo);
+    cudaFree(km->val_owned); cudaFree(km->row_ptr_owned); cudaFree(km->col_owned);
+    cudaFree(km->self_dot); cudaFree(km->diag);
+    cudaFree(km->W); cudaFree(km->Whi); cudaFree(km->Wlo); cudaFree(km->WT); cudaFree(km->sd_rows);
+    cudaFree(km->status_dev);
+    if (km->status_host) cudaFreeHost(km->status_host);
+    delete km;
+}
+
+int tsvm_km_n_instances(const tsvm_km *km) { return km ? km->n : 0; }
+int tsvm_km_n_features(const tsvm_km *km) { return km ? km->d : 0; }
+long long tsvm_km_nnz(const tsvm_km *km) { return km ? km->nnz : 0; }
+int tsvm_km_is_dense(const tsvm_km *km) { return km && km->dense; }
+const float *tsvm_km_diag_dev(const tsvm_km *km) { return km ? km->diag : nullptr; }
+const float *tsvm_km_self_dot_dev(const tsvm_km *km) { return km ? km->self_dot : nullptr; }
+
+tsvm_status tsvm_km_set_dense_engine(tsvm_km *km, int engine) {
+    TSVM_REQUIRE(km && (engine == 0 || engine == 1), "set_dense_engine: bad arguments");
+    km->engine = engine;
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_km_rows_by_index(tsvm_km *km, const int *idx_dev, int q, float *out_dev, long long ld_out,
+                                  void *stream) {
+    TSVM_REQUIRE(km && idx_dev && out_dev && q > 0 && ld_out >= km->n, "rows_by_index: bad arguments (q=%d)", q);
+    cudaStream_t st = (cudaStream_t) stream;
+    TSVM_TRY(ensure_scratch(km, q));
+    if (km->dense) {
+        const bool tc = km->engine == 0;
+        TSVM_LAUNCH(gather_rows_dense_kernel, q, 256, 0, st, km->X, km->ldx, km->d, km->d_pad, idx_dev, q,
+                    km->self_dot, tc ? nullptr : km->W, tc ? km->Whi : nullptr, tc ? km->Wlo : nullptr, km->sd_rows);
+        return rows_common(km, q, out_dev, ld_out, st);
+    }
+    TSVM_REQUIRE(q <= 1024, "CSR engine handles at most 1024 rows per call, got %d", q);
+    TSVM_LAUNCH(scatter_csr_to_wt_kernel, q, 128, 0, st, km->val, km->row_ptr, km->col, idx_dev, q, km->d, km->wt_ld,
+                km->WT, km->self_dot, km->sd_rows, false);
+    TSVM_TRY(rows_common(km, q, out_dev, ld_out, st));
+    TSVM_LAUNCH(scatter_csr_to_wt_kernel, q, 128, 0, st, km->val, km->row_ptr, km->col, idx_dev, q, km->d, km->wt_ld,
+                km->WT, nullptr, nullptr, true);
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_km_rows_by_instances_dense(tsvm_km *km, const float *T_dev, int m, int dt, int ldt, float *out_dev,
+                                            long long ld_out, void *stream) {
+    TSVM_REQUIRE(km && T_dev && out_dev && m > 0 && dt > 0 && ldt >= dt && ld_out >= km->n,
+                 "rows_by_instances_dense: bad arguments");
+    cudaStream_t st = (cudaStream_t) stream;
+    const int chunk = km->dense ? 4096 : 1024;
+    for (int r0 = 0; r0 < m; r0 += chunk) {
+        const int mm = min(chunk, m - r0);
+        const float *T = T_dev + (size_t) r0 * ldt;
+        float *o = out_dev + (size_t) r0 * ld_out;
+        TSVM_TRY(ensure_scratch(km, mm));
+        TSVM_LAUNCH(self_dot_seq_dense_kernel, ceil_div(mm, 128), 128, 0, st, T, mm, dt, ldt, km->sd_rows);
+        if (km->dense) {
+            const bool tc = km->engine == 0;
+            TSVM_LAUNCH(stage_rows_dense_kernel, mm, 256, 0, st, T, ldt, dt, km->d, km->d_pad, mm,
+                        tc ? nullptr : km->W, tc ? km->Whi : nullptr, tc ? km->Wlo : nullptr);
+            TSVM_TRY(rows_common(km, mm, o, ld_out, st));
+        } else {
+            dim3 grid(ceil_div(km->d, 32), ceil_div(mm, 32)), block(32, 8);
+            TSVM_LAUNCH(transpose_dense_to_wt_kernel, grid, block, 0, st, T, ldt, dt, km->d, mm, km->wt_ld, km->WT,
+                        false);
+            TSVM_TRY(rows_common(km, mm, o, ld_out, st));
+            TSVM_LAUNCH(transpose_dense_to_wt_kernel, grid, block, 0, st, T, ldt, dt, km->d, mm, km->wt_ld, km->WT,
+                        true);
+        }
+    }
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_km_rows_by_instances_csr(tsvm_km *km, const float *tval_dev, const int *trow_ptr_dev,
+                                          const int *tcol_dev, int m, long long tnnz, float *out_dev,
+                                          long long ld_out, void *stream) {
+    (void) tnnz;
+    TSVM_REQUIRE(km && trow_ptr_dev && out_dev && m > 0 && ld_out >= km->n, "rows_by_instances_csr: bad arguments");
+    cudaStream_t st = (cudaStream_t) stream;
+    const int chunk = km->dense ? 4096 : 1024;
+    for (int r0 = 0; r0 < m; r0 += chunk) {
+        const int mm = min(chunk, m - r0);
+        const int *rp = trow_ptr_dev + r0;     // row_ptr entries stay absolute offsets into tval/tcol
+        float *o = out_dev + (size_t) r0 * ld_out;
+        TSVM_TRY(ensure_scratch(km, mm));
+        TSVM_LAUNCH(self_dot_seq_csr_kernel, ceil_div(mm, 128), 128, 0, st, tval_dev, rp, mm, km->sd_rows);
+        if (km->dense) {
+            const bool tc = km->engine == 0;
+            if (tc) {
+                TSVM_CUDA(cudaMemsetAsync(km->Whi, 0, sizeof(float) * (size_t) mm * km->d_pad, st));
+                TSVM_CUDA(cudaMemsetAsync(km->Wlo, 0, sizeof(float) * (size_t) mm * km->d_pad, st));
+            } else TSVM_CUDA(cudaMemsetAsync(km->W, 0, sizeof(float) * (size_t) mm * km->d_pad, st));
+            TSVM_LAUNCH(scatter_csr_to_w_kernel, mm, 128, 0, st, tval_dev, rp, tcol_dev, (const int *) nullptr, mm,
+                        km->d, km->d_pad, tc ? nullptr : km->W, tc ? km->Whi : nullptr, tc ? km->Wlo : nullptr);
+            TSVM_TRY(rows_common(km, mm, o, ld_out, st));
+        } else {
+            TSVM_LAUNCH(scatter_csr_to_wt_kernel, mm, 128, 0, st, tval_dev, rp, tcol_dev, (const int *) nullptr, mm,
+                        km->d, km->wt_ld, km->WT, (const float *) nullptr, (float *) nullptr, false);
+            TSVM_TRY(rows_common(km, mm, o, ld_out, st));
+            TSVM_LAUNCH(scatter_csr_to_wt_kernel, mm, 128, 0, st, tval_dev, rp, tcol_dev, (const int *) nullptr, mm,
+                        km->d, km->wt_ld, km->WT, (const float *) nullptr, (float *) nullptr, true);
+        }
+    }
+    return TSVM_OK;
+}
+
+}  // extern "C"

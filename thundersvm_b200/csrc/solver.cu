@@ -1,0 +1,960 @@
+// Batched SMO solver on the device: working-set selection (radix top-k over (f, id) keys),
+// the one-CTA local solver, the fused f update and the outer loop with the reference's
+// termination rules. Reference behaviour: src/thundersvm/solver/csmosolver.cpp:10-239,
+// src/thundersvm/solver/nusmosolver.cpp:9-136, src/thundersvm/kernel/smo_kernel.cu:28-315.
+#include "common.cuh"
+#include <chrono>
+#include <limits.h>
+#include <vector>
+
+namespace tsvm {
+
+// =================================================================================================
+// Working-set selection
+// =================================================================================================
+// The reference sorts all n f-values every outer iteration (smo_kernel.cu:312-315) and then walks
+// the sorted ids from both ends on the host (csmosolver.cpp:123-165). Only the first `want`
+// eligible instances of every walk can ever be taken, so the device keeps, per walk ("list"),
+// the `want` smallest 96-bit keys (f-order, id) among the eligible instances:
+//   C-SMO : list 0 = I_up ascending (f, id);      list 1 = I_low descending (f, id)
+//   nu-SMO: lists 0/1 = I_up for y>0 / y<0;       lists 2/3 = I_low for y>0 / y<0
+// found with an 8-pass 12-bit radix select, followed by a compaction.
+
+constexpr int RADIX_BITS = 12, RADIX_BINS = 1 << RADIX_BITS, RADIX_PASSES = 8, MAX_LISTS = 4;
+typedef unsigned __int128 key96_t;
+
+struct SelectState {            // one per list, lives in device memory
+    unsigned long long prefix_hi;   // bits 95..32 of the threshold key found so far
+    unsigned int prefix_lo;         // bits 31..0
+    int k_rem;                      // rank still to resolve inside the current prefix
+    int take_all;                   // fewer candidates than wanted: take every one
+    int count;                      // compaction cursor
+    int pad;
+};
+
+__device__ __forceinline__ int list_count(int solver_kind) { return solver_kind == TSVM_SOLVER_C ? 2 : 4; }
+
+// Is instance (a, y) eligible for list l?
+__device__ __forceinline__ bool in_list(int solver_kind, int l, double a, int y, double Cp, double Cn) {
+    if (solver_kind == TSVM_SOLVER_C) return l == 0 ? in_I_up(a, y, Cp, Cn) : in_I_low(a, y, Cp, Cn);
+    const bool pos = (l & 1) == 0;
+    if (pos != (y > 0)) return false;
+    return l < 2 ? in_I_up(a, y, Cp, Cn) : in_I_low(a, y, Cp, Cn);
+}
+__device__ __forceinline__ bool list_ascending(int solver_kind, int l) {
+    return solver_kind == TSVM_SOLVER_C ? l == 0 : l < 2;
+}
+__device__ __forceinline__ key96_t make_key(bool asc, double f, unsigned id) {
+    unsigned long long h = ordered_key(f);
+    if (!asc) { h = ~h; id = ~id; }
+    return ((key96_t) h << 32) | id;
+}
+
+__global__ void select_init_kernel(SelectState *st, int *hist, int *ticket, int lists, int want) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < lists * RADIX_BINS; i += gridDim.x * blockDim.x) hist[i] = 0;
+    if (blockIdx.x == 0 && threadIdx.x < lists) {
+        SelectState s;
+        s.prefix_hi = 0; s.prefix_lo = 0; s.k_rem = want; s.take_all = 0; s.count = 0; s.pad = 0;
+        st[threadIdx.x] = s;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) *ticket = 0;
+}
+
+// One radix pass: histogram of the current digit over the eligible instances that match the
+// prefix; the last block to finish picks the digit that holds the wanted rank.
+__global__ void __launch_bounds__(256)
+select_hist_kernel(int solver_kind, int pass, int n, const double *__restrict__ f, const double *__restrict__ alpha,
+                   const int *__restrict__ y, const unsigned char *__restrict__ in_ws, double Cp, double Cn,
+                   SelectState *st, int *hist, int *ticket) {
+    __shared__ int sh[RADIX_BINS];
+    __shared__ int scan[256];
+    __shared__ bool is_last;
+    const int lists = list_count(solver_kind);
+    const int shift = 96 - RADIX_BITS * (pass + 1);
+    for (int l = 0; l < lists; ++l) {
+        if (st[l].take_all) continue;
+        const key96_t prefix = ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo;
+        const bool asc = list_ascending(solver_kind, l);
+        for (int b = threadIdx.x; b < RADIX_BINS; b += 256) sh[b] = 0;
+        __syncthreads();
+        for (int j = blockIdx.x * 256 + threadIdx.x; j < n; j += gridDim.x * 256) {
+            if (in_ws && in_ws[j]) continue;
+            if (!in_list(solver_kind, l, alpha[j], y[j], Cp, Cn)) continue;
+            const key96_t k = make_key(asc, f[j], (unsigned) j);
+            if (pass > 0 && (k >> (shift + RADIX_BITS)) != (prefix >> (shift + RADIX_BITS))) continue;
+            atomicAdd(&sh[(int) (k >> shift) & (RADIX_BINS - 1)], 1);
+        }
+        __syncthreads();
+        for (int b = threadIdx.x; b < RADIX_BINS; b += 256)
+            if (sh[b]) atomicAdd(&hist[l * RADIX_BINS + b], sh[b]);
+        __syncthreads();
+    }
+    __threadfence();
+    if (threadIdx.x == 0) is_last = (atomicAdd(ticket, 1) == (int) gridDim.x - 1);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int l = 0; l < lists; ++l) {
+        if (st[l].take_all) continue;
+        volatile int *h = hist + l * RADIX_BINS;
+        // 16 consecutive bins per thread, block-wide exclusive scan of the per-thread sums
+        int local[16], sum = 0;
+#pragma unroll
+        for (int b = 0; b < 16; ++b) { local[b] = h[threadIdx.x * 16 + b]; sum += local[b]; }
+        scan[threadIdx.x] = sum;
+        __syncthreads();
+        for (int o = 1; o < 256; o <<= 1) {
+            int v = threadIdx.x >= o ? scan[threadIdx.x - o] : 0;
+            __syncthreads();
+            scan[threadIdx.x] += v;
+            __syncthreads();
+        }
+        const int total = scan[255];
+        const int before = scan[threadIdx.x] - sum;
+        const int k_rem = st[l].k_rem;
+        __syncthreads();
+        if (total < k_rem) {
+            if (threadIdx.x == 0) st[l].take_all = 1;   // can only happen in pass 0
+        } else if (before < k_rem && k_rem <= before + sum) {
+            int run = before;
+#pragma unroll
+            for (int b = 0; b < 16; ++b) {
+                if (run < k_rem && k_rem <= run + local[b]) {
+                    key96_t p = ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo;
+                    p |= (key96_t) (threadIdx.x * 16 + b) << shift;
+                    st[l].prefix_hi = (unsigned long long) (p >> 32);
+                    st[l].prefix_lo = (unsigned int) p;
+                    st[l].k_rem = k_rem - run;
+                }
+                run += local[b];
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < 16; ++b) h[threadIdx.x * 16 + b] = 0;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *ticket = 0;
+}
+
+// Compaction: every eligible instance whose key is <= the threshold goes to the list's
+// candidate array (unordered). Unused tail entries keep id -1.
+__global__ void select_collect_kernel(int solver_kind, int n, const double *__restrict__ f,
+                                      const double *__restrict__ alpha, const int *__restrict__ y,
+                                      const unsigned char *__restrict__ in_ws, double Cp, double Cn, SelectState *st,
+                                      int want, int id_offset, double *__restrict__ cand_f, int *__restrict__ cand_id) {
+    const int lists = list_count(solver_kind);
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x) {
+        if (in_ws && in_ws[j]) continue;
+        const double a = alpha[j], fj = f[j];
+        const int yj = y[j];
+        for (int l = 0; l < lists; ++l) {
+            if (!in_list(solver_kind, l, a, yj, Cp, Cn)) continue;
+            if (!st[l].take_all) {
+                const key96_t thr = ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo;
+                if (make_key(list_ascending(solver_kind, l), fj, (unsigned) j) > thr) continue;
+            }
+            const int pos = atomicAdd(&st[l].count, 1);
+            if (pos < want) { cand_f[(size_t) l * want + pos] = fj; cand_id[(size_t) l * want + pos] = j + id_offset; }
+        }
+    }
+}
+
+__global__ void fill_int_kernel(int *p, int n, int v) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
+// ---- merge: sort every candidate list, keep its first `want`, then the reference's alternating
+// walk with "already taken" checks (csmosolver.cpp:123-165 / nusmosolver.cpp:48-118). ------------
+constexpr int MERGE_THREADS = 1024, MERGE_MAX_LEN = 8192, MERGE_MAX_WANT = 1024, HASH_SLOTS = 4096;
+
+__device__ __forceinline__ bool key_less(unsigned long long ah, unsigned al, unsigned long long bh, unsigned bl) {
+    return ah < bh || (ah == bh && al < bl);
+}
+
+__global__ void __launch_bounds__(MERGE_THREADS)
+select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const int *__restrict__ cand_id, int len,
+                    int want, int *__restrict__ out_ids, int *__restrict__ out_count) {
+    extern __shared__ unsigned char smem[];
+    const int lists = list_count(solver_kind);
+    int P = 1;
+    while (P < len) P <<= 1;
+    // layout: sort keys (P x 12 B), then per list: top ids / partner positions / taken flags
+    unsigned long long *kh = reinterpret_cast<unsigned long long *>(smem);
+    unsigned int *kl = reinterpret_cast<unsigned int *>(kh + P);
+    int *top_id = reinterpret_cast<int *>(kl + P);                 // [lists][want]
+    short *partner = reinterpret_cast<short *>(top_id + MAX_LISTS * MERGE_MAX_WANT);   // [lists][want]
+    unsigned char *taken = reinterpret_cast<unsigned char *>(partner + MAX_LISTS * MERGE_MAX_WANT);
+    int *hash_id = reinterpret_cast<int *>(taken + MAX_LISTS * MERGE_MAX_WANT);        // [HASH_SLOTS]
+    short *hash_pos = reinterpret_cast<short *>(hash_id + HASH_SLOTS);
+    __shared__ int top_len[MAX_LISTS];
+    const int tid = threadIdx.x;
+
+    for (int l = 0; l < lists; ++l) {
+        const bool asc = list_ascending(solver_kind, l);
+        for (int e = tid; e < P; e += MERGE_THREADS) {
+            unsigned long long h = ~0ull;
+            unsigned lo = ~0u;
+            if (e < len) {
+                const int id = cand_id[(size_t) l * len + e];
+                if (id >= 0) {
+                    h = ordered_key(cand_f[(size_t) l * len + e]);
+                    lo = (unsigned) id;
+                    if (!asc) { h = ~h; lo = ~lo; }
+                    // keep real keys distinct from the padding key
+                }
+            }
+            kh[e] = h; kl[e] = lo;
+        }
+        __syncthreads();
+        for (int k = 2; k <= P; k <<= 1)
+            for (int j = k >> 1; j > 0; j >>= 1) {
+                for (int e = tid; e < P; e += MERGE_THREADS) {
+                    const int x = e ^ j;
+                    if (x > e) {
+                        const bool up = (e & k) == 0;
+                        const bool lt = key_less(kh[x], kl[x], kh[e], kl[e]);
+                        if (lt == up) {
+                            unsigned long long th = kh[e]; kh[e] = kh[x]; kh[x] = th;
+                            unsigned tl = kl[e]; kl[e] = kl[x]; kl[x] = tl;
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+        for (int e = tid; e < want; e += MERGE_THREADS) {
+            int id = -1;
+            if (e < P && !(kh[e] == ~0ull && kl[e] == ~0u)) id = (int) (asc ? kl[e] : ~kl[e]);
+            top_id[l * MERGE_MAX_WANT + e] = id;
+            partner[l * MERGE_MAX_WANT + e] = -1;
+            taken[l * MERGE_MAX_WANT + e] = 0;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int c = want < P ? want : P;
+            // entries are sorted, padding last: count the real ones
+            int lo = 0, hi = c;
+            while (lo < hi) { int mid = (lo + hi) >> 1; if (top_id[l * MERGE_MAX_WANT + mid] >= 0) lo = mid + 1; else hi = mid; }
+            top_len[l] = lo;
+        }
+        __syncthreads();
+    }
+
+    // partner positions: an instance can sit in an "up" list and in the "low" list of the same
+    // class. up list u pairs with low list u + lists/2.
+    const int half = lists / 2;
+    for (int u = 0; u < half; ++u) {
+        const int lw = u + half;
+        for (int s = tid; s < HASH_SLOTS; s += MERGE_THREADS) hash_id[s] = -1;
+        __syncthreads();
+        for (int e = tid; e < top_len[lw]; e += MERGE_THREADS) {
+            const int id = top_id[lw * MERGE_MAX_WANT + e];
+            unsigned s = ((unsigned) id * 2654435761u) >> 20;
+            for (;;) {
+                const int old = atomicCAS(&hash_id[s], -1, id);
+                if (old == -1) { hash_pos[s] = (short) e; break; }
+                s = (s + 1) & (HASH_SLOTS - 1);
+            }
+        }
+        __syncthreads();
+        for (int e = tid; e < top_len[u]; e += MERGE_THREADS) {
+            const int id = top_id[u * MERGE_MAX_WANT + e];
+            unsigned s = ((unsigned) id * 2654435761u) >> 20;
+            for (;;) {
+                const int cur = hash_id[s];
+                if (cur == -1) break;
+                if (cur == id) {
+                    const short p = hash_pos[s];
+                    partner[u * MERGE_MAX_WANT + e] = p;
+                    partner[lw * MERGE_MAX_WANT + p] = (short) e;
+                    break;
+                }
+                s = (s + 1) & (HASH_SLOTS - 1);
+            }
+        }
+        __syncthreads();
+    }
+
+    if (tid == 0) {
+        int ptr[MAX_LISTS] = {0, 0, 0, 0};
+        int got = 0;
+        bool progressed = true;
+        while (got < want && progressed) {
+            progressed = false;
+            for (int l = 0; l < lists && got < want; ++l) {
+                const int other = l < half ? l + half : l - half;
+                int p = ptr[l];
+                const int L = top_len[l];
+                while (p < L) {
+                    const short pp = partner[l * MERGE_MAX_WANT + p];
+                    if (pp < 0 || !taken[other * MERGE_MAX_WANT + pp]) break;
+                    ++p;
+                }
+                if (p < L) {
+                    out_ids[got++] = top_id[l * MERGE_MAX_WANT + p];
+                    taken[l * MERGE_MAX_WANT + p] = 1;
+                    ++p;
+                    progressed = true;
+                }
+                ptr[l] = p;
+            }
+        }
+        if (out_count) *out_count = got;
+        for (int r = got; r < want; ++r) out_ids[r] = -1;
+    }
+}
+
+static size_t merge_smem_bytes(int len) {
+    int P = 1;
+    while (P < len) P <<= 1;
+    return (size_t) P * 12 + (size_t) MAX_LISTS * MERGE_MAX_WANT * (4 + 2 + 1) + (size_t) HASH_SLOTS * 6 + 64;
+}
+
+// =================================================================================================
+// Local SMO (one CTA per working set)
+// =================================================================================================
+constexpr int SMO_THREADS = 256, SMO_WARPS = SMO_THREADS / 32;
+constexpr unsigned long long KEY_POS_INF = 0xfff0000000000000ull;   // ordered_key(+inf)
+constexpr int NO_SLOT = 0x7fffffff;
+
+struct RedBuf {                     // per-warp partial results of up to four simultaneous reductions
+    unsigned long long key[4][SMO_WARPS];
+    int slot[4][SMO_WARPS];
+};
+
+// Block-wide argmin of R (key, slot) pairs: one __syncthreads, result in every thread.
+template <int R>
+__device__ __forceinline__ void block_argmin(RedBuf &buf, unsigned long long (&key)[R], int (&slot)[R]) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        warp_argmin_u64(key[r], slot[r]);
+        if (lane == 0) { buf.key[r][warp] = key[r]; buf.slot[r][warp] = slot[r]; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        unsigned long long k = lane < SMO_WARPS ? buf.key[r][lane] : ~0ull;
+        int s = lane < SMO_WARPS ? buf.slot[r][lane] : NO_SLOT;
+        warp_argmin_u64(k, s);
+        key[r] = k; slot[r] = s;
+    }
+}
+
+// Local solver. Slot t of the working set is owned by thread t % 256 (register copies of f, alpha,
+// y, diag); mirrors of f / alpha / y / diag in shared memory serve the few values every thread
+// needs from the selected pair. kww is the ws x ws kernel block, so row loads are coalesced.
+// NU = false: c_smo_solve_kernel semantics of the CPU backend (smo_kernel.cpp:12-125), ties to the
+// lowest slot. NU = true: nu_smo_solve_kernel semantics of the CUDA backend
+// (smo_kernel.cu:118-252): bound held in float, float arithmetic in the curvature term.
+template <bool NU, int SLOTS>
+__global__ void __launch_bounds__(SMO_THREADS)
+local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict__ diag_ws,
+                 const int *__restrict__ y_ws, const double *__restrict__ f_ws, double *__restrict__ alpha_ws,
+                 double *__restrict__ alpha_diff, double Cp_in, double Cn_in, double eps, int max_iter,
+                 double *__restrict__ diff, const int *__restrict__ ids, double *__restrict__ alpha_global) {
+    __shared__ RedBuf red[2];
+    __shared__ double f_sm[1024], a_sm[1024];
+    __shared__ float kd_sm[1024];
+    __shared__ int y_sm[1024];
+    const double Cp = NU ? (double) (float) Cp_in : Cp_in;
+    const double Cn = NU ? Cp : Cn_in;
+    const int tid = threadIdx.x;
+    double f[SLOTS], a[SLOTS], aold[SLOTS];
+    int y[SLOTS];
+    float kd[SLOTS];
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+        const int t = tid + s * SMO_THREADS;
+        if (t < ws) {
+            f[s] = f_ws[t]; a[s] = aold[s] = alpha_ws[t]; y[s] = y_ws[t]; kd[s] = diag_ws[t];
+            f_sm[t] = f[s]; a_sm[t] = a[s]; y_sm[t] = y[s]; kd_sm[t] = kd[s];
+        } else { f[s] = 0; a[s] = aold[s] = 0; y[s] = 0; kd[s] = 0; }   // y = 0: member of no set
+    }
+    __syncthreads();
+    double local_eps = 0;
+    int it = 0;
+    for (;;) {
+        // ---- first-order selection --------------------------------------------------------
+        constexpr int R1 = NU ? 4 : 2;
+        unsigned long long key[R1];
+        int slot[R1];
+#pragma unroll
+        for (int r = 0; r < R1; ++r) { key[r] = KEY_POS_INF; slot[r] = NO_SLOT; }
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int t = tid + s * SMO_THREADS;
+            const unsigned long long kf = ordered_key(f[s]), knf = ordered_key(-f[s]);
+            if (!NU) {
+                if (in_I_up(a[s], y[s], Cp, Cn) && kf < key[0]) { key[0] = kf; slot[0] = t; }
+                if (in_I_low(a[s], y[s], Cp, Cn) && knf < key[1]) { key[1] = knf; slot[1] = t; }
+            } else {
+                if (y[s] > 0 && a[s] < Cp && kf < key[0]) { key[0] = kf; slot[0] = t; }      // up, +
+                if (y[s] < 0 && a[s] > 0 && kf < key[1]) { key[1] = kf; slot[1] = t; }       // up, -
+                if (y[s] > 0 && a[s] > 0 && knf < key[2]) { key[2] = knf; slot[2] = t; }     // low, +
+                if (y[s] < 0 && a[s] < Cp && knf < key[3]) { key[3] = knf; slot[3] = t; }    // low, -
+            }
+        }
+        block_argmin<R1>(red[0], key, slot);
+        // mirrors written only now: every thread has finished reading them for the last step
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int t = tid + s * SMO_THREADS;
+            if (t < ws) { f_sm[t] = f[s]; a_sm[t] = a[s]; }
+        }
+        const int i0 = slot[0] == NO_SLOT ? 0 : slot[0];
+        const int i1 = NU ? (slot[1] == NO_SLOT ? 0 : slot[1]) : 0;
+        const double up0 = key_to_double(key[0]);
+        const double up1 = NU ? key_to_double(key[1]) : 0.0;
+        float kI0[SLOTS], kI1[SLOTS];
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int t = tid + s * SMO_THREADS;
+            kI0[s] = t < ws ? __ldg(kww + (size_t) i0 * ws + t) : 0.0f;
+            kI1[s] = (NU && t < ws) ? __ldg(kww + (size_t) i1 * ws + t) : 0.0f;
+        }
+        double local_diff;
+        if (!NU) local_diff = -key_to_double(key[1]) - up0;
+        else local_diff = fmax(-key_to_double(key[2]) - up0, -key_to_double(key[3]) - up1);
+        if (it == 0) {
+            local_eps = NU ? fmax(eps, 0.1 * local_diff) : fmax(eps, (double) 0.1f * local_diff);
+            if (tid == 0) diff[0] = local_diff;
+        }
+        if (it > max_iter || local_diff < local_eps) break;
+
+        // ---- second-order selection ---------------------------------------------------------
+        constexpr int R2 = NU ? 2 : 1;
+        unsigned long long key2[R2];
+        int slot2[R2];
+#pragma unroll
+        for (int r = 0; r < R2; ++r) { key2[r] = KEY_POS_INF; slot2[r] = NO_SLOT; }
+        const float kd_i0 = kd_sm[i0], kd_i1 = NU ? kd_sm[i1] : 0.0f;
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int t = tid + s * SMO_THREADS;
+            if (!NU) {
+                if (-up0 > -f[s] && in_I_low(a[s], y[s], Cp, Cn)) {
+                    const double aIJ = (double) (kd_i0 + kd[s]) - 2.0 * (double) kI0[s];
+                    const double bIJ = -up0 + f[s];
+                    const unsigned long long k = ordered_key(-bIJ * bIJ / aIJ);
+                    if (k < key2[0]) { key2[0] = k; slot2[0] = t; }
+                }
+            } else {
+                if (-up0 > -f[s] && y[s] > 0 && a[s] > 0) {
+                    const double aIJ = (double) (kd_i0 + kd[s] - 2 * kI0[s]);
+                    const double bIJ = -up0 + f[s];
+                    const unsigned long long k = ordered_key(-bIJ * bIJ / aIJ);
+                    if (k < key2[0]) { key2[0] = k; slot2[0] = t; }
+                }
+                if (-up1 > -f[s] && y[s] < 0 && a[s] < Cp) {
+                    const double aIJ = (double) (kd_i1 + kd[s] - 2 * kI1[s]);
+                    const double bIJ = -up1 + f[s];
+                    const unsigned long long k = ordered_key(-bIJ * bIJ / aIJ);
+                    if (k < key2[1]) { key2[1] = k; slot2[1] = t; }
+                }
+            }
+        }
+        block_argmin<R2>(red[1], key2, slot2);
+        int i, j2;
+        double up;
+        bool use1 = false;
+        if (!NU) { i = i0; j2 = slot2[0] == NO_SLOT ? 0 : slot2[0]; up = up0; }
+        else {
+            // the positive-class pair wins only if its value is strictly smaller (smo_kernel.cu:220-233)
+            if (key_to_double(key2[0]) < key_to_double(key2[1])) { i = i0; j2 = slot2[0] == NO_SLOT ? 0 : slot2[0]; up = up0; }
+            else { i = i1; j2 = slot2[1] == NO_SLOT ? 0 : slot2[1]; up = up1; use1 = true; }
+        }
+        // ---- step length, computed redundantly by every thread ---------------------------------
+        const double ai = a_sm[i], aj = a_sm[j2], fj = f_sm[j2];
+        const int yi = y_sm[i], yj = y_sm[j2];
+        const float kij = __ldg(kww + (size_t) i * ws + j2);
+        const double alpha_i_diff = yi > 0 ? Cp - ai : ai;
+        const double curv = NU ? (double) (kd_sm[i] + kd_sm[j2] - 2 * kij)
+                               : (double) (kd_sm[i] + kd_sm[j2]) - 2.0 * (double) kij;
+        const double alpha_j_diff = fmin(yj > 0 ? aj : Cn - aj, (-up + fj) / curv);
+        const double l = fmin(alpha_i_diff, alpha_j_diff);
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int t = tid + s * SMO_THREADS;
+            if (t == i) a[s] += l * yi;
+            if (t == j2) a[s] -= l * yj;
+            if (t < ws) {
+                const float kJ = __ldg(kww + (size_t) j2 * ws + t);
+                const float kI = use1 ? kI1[s] : kI0[s];
+                if (NU) f[s] -= l * (double) (kJ - kI);
+                else f[s] -= l * ((double) kJ - (double) kI);
+            }
+        }
+        ++it;
+    }
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+        const int t = tid + s * SMO_THREADS;
+        if (t < ws) {
+            alpha_ws[t] = a[s];
+            alpha_diff[t] = -(a[s] - aold[s]) * y[s];
+            if (alpha_global) alpha_global[ids[t]] = a[s];
+        }
+    }
+    if (tid == 0) diff[1] = it;
+}
+
+// ---- gather of the working set's block and vectors ---------------------------------------------
+// Logical slot t of the working set lives in physical row phys(t) of the row buffer (the two
+// halves of the buffer swap roles every outer iteration instead of being copied).
+__device__ __forceinline__ int phys_row(int t, int q, int first_half_phys) {
+    return t < q ? first_half_phys * q + t : (1 - first_half_phys) * q + (t - q);
+}
+
+__global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *__restrict__ ids,
+                                 const float *__restrict__ rows, long long ld, const float *__restrict__ diag,
+                                 const int *__restrict__ y, const double *__restrict__ f,
+                                 const double *__restrict__ alpha, float *__restrict__ kww,
+                                 float *__restrict__ diag_ws, int *__restrict__ y_ws, double *__restrict__ f_ws,
+                                 double *__restrict__ alpha_ws) {
+    const int a = blockIdx.x;                      // logical slot of the row
+    const float *row = rows + (size_t) phys_row(a, q, first_half_phys) * ld;
+    for (int b = threadIdx.x; b < ws; b += blockDim.x) kww[(size_t) a * ws + b] = row[ids[b]];
+    if (threadIdx.x == 0) {
+        const int id = ids[a];
+        diag_ws[a] = diag[id]; y_ws[a] = y[id]; f_ws[a] = f[id]; alpha_ws[a] = alpha[id];
+    }
+}
+
+// ids[0..q) <- ids[q..ws); flags: old first half leaves the working set, old second half stays.
+__global__ void shift_ws_kernel(int *ids, int q, unsigned char *in_ws) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;   // launched as one block, q <= 512
+    if (t < q) {
+        const int leaving = ids[t], staying = ids[q + t];  // distinct instances
+        in_ws[leaving] = 0;
+        in_ws[staying] = 1;
+        ids[t] = staying;
+    }
+}
+
+// =================================================================================================
+// f update:  f[j] -= sum_t alpha_diff[t] * rows[phys(t)][j]   (smo_kernel.cu:289-310)
+// =================================================================================================
+// HBM-bound: every thread owns 4 consecutive columns and streams the rows whose alpha_diff is
+// non-zero with 16-byte loads, 8 rows in flight.
+__global__ void __launch_bounds__(128)
+update_f_kernel(double *__restrict__ f, int n, const double *__restrict__ alpha_diff, int ws, int q,
+                int first_half_phys, const float *__restrict__ rows, long long ld, int vec_ok) {
+    __shared__ double ad[1024];
+    __shared__ int prow[1024];
+    __shared__ int cnt;
+    if (threadIdx.x == 0) cnt = 0;
+    __syncthreads();
+    // order-preserving compaction of the non-zero entries (one warp, ballot scan)
+    if (threadIdx.x < 32) {
+        int base = 0;
+        for (int t0 = 0; t0 < ws; t0 += 32) {
+            const int t = t0 + threadIdx.x;
+            const double dv = t < ws ? alpha_diff[t] : 0.0;
+            const unsigned m = __ballot_sync(0xffffffffu, dv != 0.0);
+            if (dv != 0.0) {
+                const int p = base + __popc(m & ((1u << threadIdx.x) - 1));
+                ad[p] = dv;
+                prow[p] = q > 0 ? phys_row(t, q, first_half_phys) : t;
+            }
+            base += __popc(m);
+        }
+        if (threadIdx.x == 0) cnt = base;
+    }
+    __syncthreads();
+    const int m = cnt;
+    const long long j = ((long long) blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (j >= n) return;
+    double s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+    if (j + 3 < n && vec_ok) {
+        int r = 0;
+        for (; r + 8 <= m; r += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcs(reinterpret_cast<const float4 *>(rows + (size_t) prow[r + u] * ld + j));
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const double dv = ad[r + u];
+                s0 += dv * v[u].x; s1 += dv * v[u].y; s2 += dv * v[u].z; s3 += dv * v[u].w;
+            }
+        }
+        for (; r < m; ++r) {
+            const float4 v = __ldcs(reinterpret_cast<const float4 *>(rows + (size_t) prow[r] * ld + j));
+            const double dv = ad[r];
+            s0 += dv * v.x; s1 += dv * v.y; s2 += dv * v.z; s3 += dv * v.w;
+        }
+        f[j] -= s0; f[j + 1] -= s1; f[j + 2] -= s2; f[j + 3] -= s3;
+    } else {
+        for (int c = 0; c < 4 && j + c < n; ++c) {
+            double s = 0;
+            for (int r = 0; r < m; ++r) s += ad[r] * rows[(size_t) prow[r] * ld + j + c];
+            f[j + c] -= s;
+        }
+    }
+}
+
+// =================================================================================================
+// rho / objective
+// =================================================================================================
+// out[0..12] = n_free(+), sum_free f(+), n_free(-), sum_free f(-), sum of the objective terms,
+//              min f over I_up (+), max f over I_low (+), the same two for (-),
+//              max f over I_up (+), min f over I_low (+), the same two for (-).
+constexpr int RHO_VALS = 13;
+__global__ void __launch_bounds__(1024)
+rho_obj_kernel(int n, const double *__restrict__ f, const double *__restrict__ alpha, const int *__restrict__ y,
+               double Cp, double Cn, double *__restrict__ out) {
+    __shared__ double sh[32][RHO_VALS];
+    double v[RHO_VALS] = {0, 0, 0, 0, 0, INFINITY, -INFINITY, INFINITY, -INFINITY, -INFINITY, INFINITY, -INFINITY,
+                          INFINITY};
+    for (int i = threadIdx.x; i < n; i += 1024) {
+        const double a = alpha[i], fi = f[i];
+        const int yi = y[i];
+        v[4] += a - (fi + yi) * a * yi / 2;
+        const bool up = in_I_up(a, yi, Cp, Cn), low = in_I_low(a, yi, Cp, Cn);
+        if (yi > 0) {
+            if (a > 0 && a < Cp) { v[0] += 1; v[1] += fi; }
+            if (up) { v[5] = fmin(v[5], fi); v[9] = fmax(v[9], fi); }
+            if (low) { v[6] = fmax(v[6], fi); v[10] = fmin(v[10], fi); }
+        } else {
+            if (a > 0 && a < Cn) { v[2] += 1; v[3] += fi; }
+            if (up) { v[7] = fmin(v[7], fi); v[11] = fmax(v[11], fi); }
+            if (low) { v[8] = fmax(v[8], fi); v[12] = fmin(v[12], fi); }
+        }
+    }
+    auto combine = [](int k, double a, double b) -> double {
+        if (k < 5) return a + b;
+        const bool is_min = (k == 5 || k == 7 || k == 10 || k == 12);
+        return is_min ? fmin(a, b) : fmax(a, b);
+    };
+    for (int o = 16; o; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < RHO_VALS; ++k) v[k] = combine(k, v[k], __shfl_xor_sync(0xffffffffu, v[k], o));
+    if ((threadIdx.x & 31) == 0)
+        for (int k = 0; k < RHO_VALS; ++k) sh[threadIdx.x >> 5][k] = v[k];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 32; ++w)
+            for (int k = 0; k < RHO_VALS; ++k) sh[0][k] = combine(k, sh[0][k], sh[w][k]);
+        for (int k = 0; k < RHO_VALS; ++k) out[k] = sh[0][k];
+    }
+}
+
+__global__ void scale_kernel(double *a, int n, double r) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] /= r;
+}
+
+// =================================================================================================
+// host side
+// =================================================================================================
+static inline int rows_vec_ok(const float *rows, long long ld) {
+    return (((uintptr_t) rows & 15) == 0 && (ld & 3) == 0) ? 1 : 0;
+}
+
+static tsvm_status launch_local_smo(int solver_kind, int ws, const float *kww, const float *diag_ws, const int *y_ws,
+                                    const double *f_ws, double *alpha_ws, double *alpha_diff, double Cp, double Cn,
+                                    double eps, int max_iter, double *diff, const int *ids, double *alpha_global,
+                                    cudaStream_t st) {
+    const bool nu = solver_kind != TSVM_SOLVER_C;
+    const int slots = ceil_div(ws, SMO_THREADS);
+#define SMO_CASE(NU, S)                                                                                        \
+    TSVM_LAUNCH((local_smo_kernel<NU, S>), 1, SMO_THREADS, 0, st, ws, kww, diag_ws, y_ws, f_ws, alpha_ws,      \
+                alpha_diff, Cp, Cn, eps, max_iter, diff, ids, alpha_global)
+    if (!nu) {
+        if (slots <= 1) SMO_CASE(false, 1); else if (slots <= 2) SMO_CASE(false, 2); else SMO_CASE(false, 4);
+    } else {
+        if (slots <= 1) SMO_CASE(true, 1); else if (slots <= 2) SMO_CASE(true, 2); else SMO_CASE(true, 4);
+    }
+#undef SMO_CASE
+    return TSVM_OK;
+}
+
+}  // namespace tsvm
+
+using namespace tsvm;
+
+struct tsvm_ws {
+    int n_max = 0, ws_max = 0;
+    SelectState *state = nullptr;
+    int *hist = nullptr, *ticket = nullptr, *count = nullptr;
+    double *cand_f = nullptr;
+    int *cand_id = nullptr;
+};
+
+extern "C" {
+
+tsvm_status tsvm_ws_create(int n_max, int ws_max, tsvm_ws **out) {
+    TSVM_REQUIRE(out && n_max > 0 && ws_max > 0 && ws_max <= MERGE_MAX_WANT, "ws_create: bad arguments");
+    tsvm_ws *w = new tsvm_ws;
+    w->n_max = n_max; w->ws_max = ws_max;
+    tsvm_status s = dev_alloc(&w->state, MAX_LISTS);
+    if (s == TSVM_OK) s = dev_alloc(&w->hist, MAX_LISTS * RADIX_BINS);
+    if (s == TSVM_OK) s = dev_alloc(&w->ticket, 1);
+    if (s == TSVM_OK) s = dev_alloc(&w->count, 1);
+    if (s == TSVM_OK) s = dev_alloc(&w->cand_f, (size_t) MAX_LISTS * ws_max);
+    if (s == TSVM_OK) s = dev_alloc(&w->cand_id, (size_t) MAX_LISTS * ws_max);
+    if (s != TSVM_OK) { tsvm_ws_destroy(w); return s; }
+    *out = w;
+    return TSVM_OK;
+}
+
+void tsvm_ws_destroy(tsvm_ws *w) {
+    if (!w) return;
+    cudaFree(w->state); cudaFree(w->hist); cudaFree(w->ticket); cudaFree(w->count);
+    cudaFree(w->cand_f); cudaFree(w->cand_id);
+    delete w;
+}
+
+tsvm_status tsvm_ws_candidates(tsvm_ws *w, int solver_kind, int n, const double *f_dev, const double *alpha_dev,
+                               const int *y_dev, const unsigned char *in_ws_dev, double Cp, double Cn, int want,
+                               int id_offset, double *cand_f_dev, int *cand_id_dev, void *stream) {
+    TSVM_REQUIRE(w && f_dev && alpha_dev && y_dev && cand_f_dev && cand_id_dev && n > 0 && want > 0 &&
+                 want <= w->ws_max && solver_kind >= 0 && solver_kind <= 2, "ws_candidates: bad arguments");
+    cudaStream_t st = (cudaStream_t) stream;
+    const int lists = solver_kind == TSVM_SOLVER_C ? 2 : 4;
+    int grid = ceil_div(n, 256 * 4);
+    if (grid > 296) grid = 296;
+    if (grid < 1) grid = 1;
+    TSVM_LAUNCH(select_init_kernel, 16, 256, 0, st, w->state, w->hist, w->ticket, lists, want);
+    TSVM_LAUNCH(fill_int_kernel, ceil_div(lists * want, 256), 256, 0, st, cand_id_dev, lists * want, -1);
+    for (int p = 0; p < RADIX_PASSES; ++p)
+        TSVM_LAUNCH(select_hist_kernel, grid, 256, 0, st, solver_kind, p, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp,
+                    Cn, w->state, w->hist, w->ticket);
+    TSVM_LAUNCH(select_collect_kernel, grid, 256, 0, st, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn,
+                w->state, want, id_offset, cand_f_dev, cand_id_dev);
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_ws_merge(tsvm_ws *w, int solver_kind, const double *cand_f_dev, const int *cand_id_dev, int len,
+                          int want, int *out_ids_dev, void *stream) {
+    TSVM_REQUIRE(w && cand_f_dev && cand_id_dev && out_ids_dev && len > 0 && len <= MERGE_MAX_LEN && want > 0 &&
+                 want <= MERGE_MAX_WANT, "ws_merge: bad arguments (len=%d want=%d)", len, want);
+    cudaStream_t st = (cudaStream_t) stream;
+    const size_t smem = merge_smem_bytes(len);
+    static size_t configured = 0;
+    if (smem > configured) {
+        TSVM_CUDA(cudaFuncSetAttribute(select_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int) merge_smem_bytes(MERGE_MAX_LEN)));
+        configured = merge_smem_bytes(MERGE_MAX_LEN);
+    }
+    TSVM_LAUNCH(select_merge_kernel, 1, MERGE_THREADS, smem, st, solver_kind, cand_f_dev, cand_id_dev, len, want,
+                out_ids_dev, w->count);
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_select_working_set(tsvm_ws *w, int solver_kind, int n, const double *f_dev, const double *alpha_dev,
+                                    const int *y_dev, const unsigned char *in_ws_dev, double Cp, double Cn, int want,
+                                    int *out_ids_dev, void *stream) {
+    TSVM_TRY(tsvm_ws_candidates(w, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn, want, 0, w->cand_f,
+                                w->cand_id, stream));
+    return tsvm_ws_merge(w, solver_kind, w->cand_f, w->cand_id, want, want, out_ids_dev, stream);
+}
+
+tsvm_status tsvm_local_smo(int solver_kind, int ws_size, const float *kww_dev, const float *diag_ws_dev,
+                           const int *y_ws_dev, const double *f_ws_dev, double *alpha_ws_dev, double *alpha_diff_dev,
+                           double Cp, double Cn, double eps, int max_iter, double *diff_dev, void *stream) {
+    TSVM_REQUIRE(ws_size > 0 && ws_size <= 1024 && kww_dev && diag_ws_dev && y_ws_dev && f_ws_dev && alpha_ws_dev &&
+                 alpha_diff_dev && diff_dev, "local_smo: bad arguments (ws=%d)", ws_size);
+    return launch_local_smo(solver_kind, ws_size, kww_dev, diag_ws_dev, y_ws_dev, f_ws_dev, alpha_ws_dev,
+                            alpha_diff_dev, Cp, Cn, eps, max_iter, diff_dev, nullptr, nullptr, (cudaStream_t) stream);
+}
+
+tsvm_status tsvm_update_f(double *f_dev, int n, const double *alpha_diff_dev, int ws_size, const float *rows_dev,
+                          long long ld, void *stream) {
+    TSVM_REQUIRE(f_dev && alpha_diff_dev && rows_dev && n > 0 && ws_size > 0 && ws_size <= 1024 && ld >= n,
+                 "update_f: bad arguments (at most 1024 rows per call)");
+    TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, (cudaStream_t) stream, f_dev, n, alpha_diff_dev, ws_size,
+                0, 0, rows_dev, ld, rows_vec_ok(rows_dev, ld));
+    return TSVM_OK;
+}
+
+int tsvm_working_set_size(int n_instances, int n_features, size_t max_mem_bytes, size_t used_bytes) {
+    if (max_mem_bytes < used_bytes) return -1;
+    // max2power(x) = 2^floor(log2f(x)) (include/thundersvm/util/common.h:20-23)
+    auto max2power = [](double x) -> long long { return (long long) exp2(floor(log2f((float) x))); };
+    const size_t free_mem = max_mem_bytes - used_bytes;
+    long long a = max2power((double) n_instances);
+    long long b = max2power((double) (free_mem / sizeof(float) / ((size_t) n_instances + n_features)));
+    if (b > 1024) b = 1024;
+    return (int) (a < b ? a : b);
+}
+
+tsvm_status tsvm_smo_solve(tsvm_km *km, int solver_kind, const int *y_dev, double *alpha_dev, double *f_dev,
+                           double eps, double Cp, double Cn, int ws_size, int max_iter, double *rho_host,
+                           tsvm_solve_stats *stats_host, void *stream) {
+    TSVM_REQUIRE(km && y_dev && alpha_dev && f_dev && rho_host, "smo_solve: null argument");
+    TSVM_REQUIRE(solver_kind >= 0 && solver_kind <= 2, "smo_solve: unknown solver %d", solver_kind);
+    const int n = km->n;
+    TSVM_REQUIRE(ws_size >= 2 && ws_size <= 1024 && ws_size <= n && (ws_size & (ws_size - 1)) == 0,
+                 "smo_solve: working-set size %d must be a power of two in [2, min(n, 1024)]", ws_size);
+    cudaStream_t st = (cudaStream_t) stream;
+    const int q = ws_size / 2;
+    const long long ld = ((long long) n + 3) & ~3ll;
+    const long long launches0 = launch_count();
+    const auto t_begin = std::chrono::steady_clock::now();
+
+    struct Bufs {
+        int *ids = nullptr, *y_ws = nullptr;
+        float *rows = nullptr, *kww = nullptr, *diag_ws = nullptr;
+        double *f_ws = nullptr, *a_ws = nullptr, *alpha_diff = nullptr, *diff = nullptr, *red = nullptr;
+        unsigned char *in_ws = nullptr;
+        tsvm_ws *sel = nullptr;
+        double *diff_host = nullptr;
+        cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+        ~Bufs() {
+            cudaFree(ids); cudaFree(y_ws); cudaFree(rows); cudaFree(kww); cudaFree(diag_ws); cudaFree(f_ws);
+            cudaFree(a_ws); cudaFree(alpha_diff); cudaFree(diff); cudaFree(red); cudaFree(in_ws);
+            tsvm_ws_destroy(sel);
+            if (diff_host) cudaFreeHost(diff_host);
+            for (auto e : ev) if (e) cudaEventDestroy(e);
+        }
+    } B;
+    TSVM_TRY(dev_alloc(&B.ids, (size_t) ws_size));
+    TSVM_TRY(dev_alloc(&B.y_ws, (size_t) ws_size));
+    TSVM_TRY(dev_alloc(&B.rows, (size_t) ws_size * ld));
+    TSVM_TRY(dev_alloc(&B.kww, (size_t) ws_size * ws_size));
+    TSVM_TRY(dev_alloc(&B.diag_ws, (size_t) ws_size));
+    TSVM_TRY(dev_alloc(&B.f_ws, (size_t) ws_size));
+    TSVM_TRY(dev_alloc(&B.a_ws, (size_t) ws_size));
+    TSVM_TRY(dev_alloc(&B.alpha_diff, (size_t) ws_size));
+    TSVM_TRY(dev_alloc(&B.diff, 4));
+    TSVM_TRY(dev_alloc(&B.red, 16));   // >= RHO_VALS
+    TSVM_TRY(dev_alloc(&B.in_ws, (size_t) n));
+    TSVM_CUDA(cudaMemsetAsync(B.in_ws, 0, (size_t) n, st));
+    TSVM_TRY(tsvm_ws_create(n, ws_size, &B.sel));
+    TSVM_CUDA(cudaMallocHost((void **) &B.diff_host, 16 * sizeof(double)));
+    const bool timing = stats_host != nullptr;
+    if (timing) for (auto &e : B.ev) TSVM_CUDA(cudaEventCreate(&e));
+    double t_sel = 0, t_rows = 0, t_loc = 0, t_upd = 0;
+    long long rows_made = 0;
+
+    // ---- init_f (csmosolver.cpp:189-214): f -= sum over initially non-zero alphas --------------
+    {
+        std::vector<double> a_h(n);
+        std::vector<int> y_h(n);
+        TSVM_CUDA(cudaMemcpyAsync(a_h.data(), alpha_dev, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaMemcpyAsync(y_h.data(), y_dev, sizeof(int) * n, cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaStreamSynchronize(st));
+        std::vector<int> bi;
+        std::vector<double> bd;
+        auto flush = [&]() -> tsvm_status {
+            if (bi.empty()) return TSVM_OK;
+            const int m = (int) bi.size();
+            TSVM_CUDA(cudaMemcpyAsync(B.ids, bi.data(), sizeof(int) * m, cudaMemcpyHostToDevice, st));
+            TSVM_CUDA(cudaMemcpyAsync(B.alpha_diff, bd.data(), sizeof(double) * m, cudaMemcpyHostToDevice, st));
+            TSVM_TRY(tsvm_km_rows_by_index(km, B.ids, m, B.rows, ld, st));
+            TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f_dev, n, B.alpha_diff, m, 0, 0, B.rows, ld, rows_vec_ok(B.rows, ld));
+            TSVM_CUDA(cudaStreamSynchronize(st));
+            rows_made += m;
+            bi.clear(); bd.clear();
+            return TSVM_OK;
+        };
+        for (int i = 0; i < n; ++i) {
+            if (a_h[i] != 0) { bi.push_back(i); bd.push_back(-a_h[i] * y_h[i]); }
+            if ((int) bi.size() == ws_size) TSVM_TRY(flush());
+        }
+        TSVM_TRY(flush());
+    }
+
+    // local iteration cap: max(100000, 100 * ws) (csmosolver.cpp:49)
+    const int local_max_iter = ws_size > INT_MAX / 100 ? INT_MAX : (100 * ws_size > 100000 ? 100 * ws_size : 100000);
+    long long local_iter = 0;
+    int same_cnt = 0, swap_cnt = 0;
+    double prev = INFINITY, last = INFINITY, second_last = INFINITY, diff0 = 0;
+    long long iter = 0;
+    for (;; ++iter) {
+        const int first_half_phys = (int) (iter & 1);   // iteration 0 fills both halves in logical order
+        if (timing) TSVM_CUDA(cudaEventRecord(B.ev[0], st));
+        if (iter == 0) {
+            TSVM_TRY(tsvm_select_working_set(B.sel, solver_kind, n, f_dev, alpha_dev, y_dev, nullptr, Cp, Cn, ws_size,
+                                             B.ids, st));
+            if (timing) TSVM_CUDA(cudaEventRecord(B.ev[1], st));
+            TSVM_TRY(tsvm_km_rows_by_index(km, B.ids, ws_size, B.rows, ld, st));
+            rows_made += ws_size;
+        } else {
+            TSVM_LAUNCH(shift_ws_kernel, ceil_div(q, 1024), 1024, 0, st, B.ids, q, B.in_ws);
+            TSVM_TRY(tsvm_select_working_set(B.sel, solver_kind, n, f_dev, alpha_dev, y_dev, B.in_ws, Cp, Cn, q,
+                                             B.ids + q, st));
+            if (timing) TSVM_CUDA(cudaEventRecord(B.ev[1], st));
+            TSVM_TRY(tsvm_km_rows_by_index(km, B.ids + q, q, B.rows + (size_t) (1 - first_half_phys) * q * ld, ld, st));
+            rows_made += q;
+        }
+        if (timing) TSVM_CUDA(cudaEventRecord(B.ev[2], st));
+        TSVM_LAUNCH(gather_ws_kernel, ws_size, 256, 0, st, ws_size, q, first_half_phys, B.ids, B.rows, ld, km->diag,
+                    y_dev, f_dev, alpha_dev, B.kww, B.diag_ws, B.y_ws, B.f_ws, B.a_ws);
+        TSVM_TRY(launch_local_smo(solver_kind, ws_size, B.kww, B.diag_ws, B.y_ws, B.f_ws, B.a_ws, B.alpha_diff, Cp, Cn,
+                                  eps, local_max_iter, B.diff, B.ids, alpha_dev, st));
+        if (timing) TSVM_CUDA(cudaEventRecord(B.ev[3], st));
+        TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f_dev, n, B.alpha_diff, ws_size, q, first_half_phys,
+                    B.rows, ld, rows_vec_ok(B.rows, ld));
+        if (timing) TSVM_CUDA(cudaEventRecord(B.ev[4], st));
+        TSVM_CUDA(cudaMemcpyAsync(B.diff_host, B.diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaMemcpyAsync(km->status_host, km->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaStreamSynchronize(st));
+        if (km->status_host[0] != 0) {
+            set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", km->status_host[0]);
+            return TSVM_ERR_DEVICE;
+        }
+        if (timing) {
+            float ms;
+            cudaEventElapsedTime(&ms, B.ev[0], B.ev[1]); t_sel += ms;
+            cudaEventElapsedTime(&ms, B.ev[1], B.ev[2]); t_rows += ms;
+            cudaEventElapsedTime(&ms, B.ev[2], B.ev[3]); t_loc += ms;
+            cudaEventElapsedTime(&ms, B.ev[3], B.ev[4]); t_upd += ms;
+        }
+        diff0 = B.diff_host[0];
+        local_iter += (long long) B.diff_host[1];
+        // termination rules of csmosolver.cpp:86-111
+        if (fabs(diff0 - prev) < eps * 0.001) same_cnt++;
+        else { same_cnt = 0; prev = diff0; }
+        if (fabs(diff0 - second_last) < eps * 0.001) swap_cnt++;
+        else swap_cnt = 0;
+        second_last = last;
+        last = diff0;
+        if ((same_cnt >= 10 && fabs(diff0 - 2.0) > eps) || diff0 < eps || (max_iter != -1 && iter == max_iter) ||
+            (swap_cnt >= 10 && fabs(diff0 - 2.0) > eps))
+            break;
+    }
+
+    // ---- rho and objective (csmosolver.cpp:167-187,227-239; nusmosolver.cpp:9-46,120-126) -----------
+    TSVM_LAUNCH(rho_obj_kernel, 1, 1024, 0, st, n, f_dev, alpha_dev, y_dev, Cp, Cn, B.red);
+    TSVM_CUDA(cudaMemcpyAsync(B.diff_host, B.red, RHO_VALS * sizeof(double), cudaMemcpyDeviceToHost, st));
+    TSVM_CUDA(cudaStreamSynchronize(st));
+    const double *R = B.diff_host;
+    const double obj = -R[4];
+    double rho;
+    if (solver_kind == TSVM_SOLVER_C) {
+        const double nfree = R[0] + R[2];
+        rho = nfree != 0 ? (R[1] + R[3]) / nfree : -(fmin(R[5], R[7]) + fmax(R[6], R[8])) / 2;
+    } else {
+        // nusmosolver.cpp:9-46 works with -f: r = -(min_{I_up}(-f) + max_{I_low}(-f)) / 2
+        //                                       =  (max_{I_up} f + min_{I_low} f) / 2
+        const double r1 = R[0] != 0 ? R[1] / R[0] : (R[9] + R[10]) / 2;
+        const double r2 = R[2] != 0 ? -R[3] / R[2] : (R[11] + R[12]) / 2;
+        rho = (r1 - r2) / 2;
+        if (solver_kind == TSVM_SOLVER_NU_SVC) {
+            const double r = (r1 + r2) / 2;
+            TSVM_LAUNCH(scale_kernel, ceil_div(n, 256), 256, 0, st, alpha_dev, n, r);
+            TSVM_CUDA(cudaStreamSynchronize(st));
+            rho /= r;
+        }
+    }
+    *rho_host = rho;
+    if (stats_host) {
+        stats_host->outer_iters = iter + 1;
+        stats_host->local_iters = local_iter;
+        stats_host->final_diff = diff0;
+        stats_host->objective = obj;
+        stats_host->seconds_select = t_sel * 1e-3;
+        stats_host->seconds_rows = t_rows * 1e-3;
+        stats_host->seconds_local = t_loc * 1e-3;
+        stats_host->seconds_update = t_upd * 1e-3;
+        stats_host->seconds_total =
+            std::chrono::duration<double>(std::chrono::steady_clock::now() - t_begin).count();
+        stats_host->kernel_rows = rows_made;
+        stats_host->gpu_launches = launch_count() - launches0;
+    }
+    return TSVM_OK;
+}
+
+}  // extern "C"
