@@ -99,8 +99,9 @@ tsvm_status tsvm_km_rows_by_instances_csr(tsvm_km *km, const float *tval_dev, co
                                           const int *tcol_dev, int m, long long tnnz, float *out_dev,
                                           long long ld_out, void *stream);
 
-/* Selects the dense kernel-row engine: 0 = tcgen05 tensor-core tiles (default),
- * 1 = plain FP32 CUDA-core tiles (diagnostic cross-check only). */
+/* Selects the dense kernel-row engine: 0 = automatic (default: tcgen05 tensor-core tiles, FP32
+ * CUDA-core tiles when there are at most 32 features, where a k loop of one slab gives the
+ * tensor core nothing to pipeline), 1 = FP32 CUDA-core tiles, 2 = tcgen05 tiles. */
 tsvm_status tsvm_km_set_dense_engine(tsvm_km *km, int engine);
 
 /* ------------------------------------------------------------------------------------------
@@ -128,6 +129,19 @@ typedef struct {
 tsvm_status tsvm_smo_solve(tsvm_km *km, int solver_kind, const int *y_dev, double *alpha_dev, double *f_dev,
                            double eps, double Cp, double Cn, int ws_size, int max_iter, double *rho_host,
                            tsvm_solve_stats *stats_host, void *stream);
+
+/* The same solver as an object, for callers that drive the outer loop themselves: create
+ * (allocates the row buffer and runs init_f, csmosolver.cpp:189-214), iterate n outer iterations
+ * (stops early and sets *done_host when the termination rules of csmosolver.cpp:86-111 fire),
+ * finish (rho, objective, statistics; nu-SVC scaling), destroy. */
+typedef struct tsvm_solver tsvm_solver;
+tsvm_status tsvm_solver_create(tsvm_km *km, int solver_kind, const int *y_dev, double *alpha_dev, double *f_dev,
+                               double eps, double Cp, double Cn, int ws_size, void *stream, tsvm_solver **out);
+tsvm_status tsvm_solver_iterate(tsvm_solver *solver, int n_iters, int *done_host);
+tsvm_status tsvm_solver_finish(tsvm_solver *solver, double *rho_host, tsvm_solve_stats *stats_host);
+/* Counters and phase times so far (objective is not evaluated: NaN). */
+tsvm_status tsvm_solver_get_stats(const tsvm_solver *solver, tsvm_solve_stats *stats_host);
+void tsvm_solver_destroy(tsvm_solver *solver);
 
 /* SvmModel::get_working_set_size (src/thundersvm/model/svmmodel.cpp:437-451) with the
  * memory budget in bytes. Returns the working-set size, or -1 when the budget is already

@@ -22,7 +22,8 @@ EXPORTS = [
     "tsvm_last_error", "tsvm_abi_version", "tsvm_km_create_dense", "tsvm_km_create_csr", "tsvm_km_destroy",
     "tsvm_km_n_instances", "tsvm_km_n_features", "tsvm_km_nnz", "tsvm_km_is_dense", "tsvm_km_diag_dev",
     "tsvm_km_self_dot_dev", "tsvm_km_rows_by_index", "tsvm_km_rows_by_instances_dense",
-    "tsvm_km_rows_by_instances_csr", "tsvm_km_set_dense_engine", "tsvm_smo_solve", "tsvm_working_set_size",
+    "tsvm_km_rows_by_instances_csr", "tsvm_km_set_dense_engine", "tsvm_smo_solve", "tsvm_solver_create",
+    "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_destroy", "tsvm_working_set_size",
     "tsvm_ws_create", "tsvm_ws_destroy", "tsvm_ws_candidates", "tsvm_ws_merge", "tsvm_select_working_set",
     "tsvm_local_smo", "tsvm_update_f", "tsvm_predict_dec", "tsvm_vote",
 ]
@@ -75,6 +76,12 @@ def lib():
     L.tsvm_km_rows_by_instances_csr.argtypes = [vp, vp, vp, vp, i, ll, vp, ll, vp]
     L.tsvm_km_set_dense_engine.argtypes = [vp, i]
     L.tsvm_smo_solve.argtypes = [vp, i, vp, vp, vp, d, d, d, i, i, C.POINTER(d), C.POINTER(SolveStats), vp]
+    L.tsvm_solver_create.argtypes = [vp, i, vp, vp, vp, d, d, d, i, vp, C.POINTER(vp)]
+    L.tsvm_solver_iterate.argtypes = [vp, i, C.POINTER(i)]
+    L.tsvm_solver_finish.argtypes = [vp, C.POINTER(d), C.POINTER(SolveStats)]
+    L.tsvm_solver_get_stats.argtypes = [vp, C.POINTER(SolveStats)]
+    L.tsvm_solver_destroy.argtypes = [vp]
+    L.tsvm_solver_destroy.restype = None
     L.tsvm_working_set_size.argtypes = [i, i, sz, sz]
     L.tsvm_working_set_size.restype = i
     L.tsvm_ws_create.argtypes = [i, i, C.POINTER(vp)]
@@ -112,7 +119,7 @@ class _DeviceView:
     """float32 device memory owned by the library, exposed through __cuda_array_interface__."""
 
     def __init__(self, ptr, n):
-        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (int(ptr), True), "version": 2}
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (int(ptr), False), "version": 2}
 
 
 class KernelMatrix:
@@ -165,7 +172,7 @@ class KernelMatrix:
         return self._h
 
     def set_dense_engine(self, engine):
-        check(lib().tsvm_km_set_dense_engine(self._h, {"tensor": 0, "simt": 1}.get(engine, engine)))
+        check(lib().tsvm_km_set_dense_engine(self._h, {"auto": 0, "simt": 1, "tensor": 2}.get(engine, engine)))
 
     def _vec(self, fn):
         view = _DeviceView(fn(self._h), self.n)
@@ -228,6 +235,43 @@ def smo_solve(km, y, alpha, f, eps, Cp, Cn, ws_size, max_iter=-1, solver="c"):
     check(lib().tsvm_smo_solve(km.handle, SOLVERS[solver], _ptr(y), _ptr(alpha), _ptr(f), eps, Cp, Cn, ws_size,
                                max_iter, C.byref(rho), C.byref(st), _stream()))
     return rho.value, st.as_dict()
+
+
+class Solver:
+    """Stepping form of the solver (tsvm_solver_*): iterate(k) runs k outer iterations."""
+
+    def __init__(self, km, y, alpha, f, eps, Cp, Cn, ws_size, solver="c"):
+        self._h = C.c_void_p(0)
+        self._keep = (km, y, alpha, f)
+        check(lib().tsvm_solver_create(km.handle, SOLVERS[solver], _ptr(y), _ptr(alpha), _ptr(f), eps, Cp, Cn,
+                                       ws_size, _stream(), C.byref(self._h)))
+
+    def iterate(self, n_iters):
+        done = C.c_int(0)
+        check(lib().tsvm_solver_iterate(self._h, n_iters, C.byref(done)))
+        return bool(done.value)
+
+    def stats(self):
+        st = SolveStats()
+        check(lib().tsvm_solver_get_stats(self._h, C.byref(st)))
+        return st.as_dict()
+
+    def finish(self):
+        rho = C.c_double(0)
+        st = SolveStats()
+        check(lib().tsvm_solver_finish(self._h, C.byref(rho), C.byref(st)))
+        return rho.value, st.as_dict()
+
+    def close(self):
+        if self._h:
+            lib().tsvm_solver_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class WorkingSetSelector:

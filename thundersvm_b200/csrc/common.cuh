@@ -58,8 +58,10 @@ inline int ceil_div(long long a, long long b) { return (int) ((a + b - 1) / b); 
 
 // ---- device helpers ------------------------------------------------------------------
 
-// Monotone map double -> uint64 (ascending). -0.0 and +0.0 map to neighbouring keys.
+// Monotone map double -> uint64 (ascending); -0.0 is folded onto +0.0 so that equal values
+// get equal keys.
 __host__ __device__ __forceinline__ unsigned long long ordered_key(double v) {
+    if (v == 0.0) v = 0.0;
 #ifdef __CUDA_ARCH__
     unsigned long long b = (unsigned long long) __double_as_longlong(v);
 #else
@@ -145,7 +147,7 @@ struct tsvm_km {
     long long nnz = 0;
     bool dense = true;
     tsvm::KernelFn fn{};
-    int engine = 0;                 // 0 = tcgen05, 1 = CUDA-core FP32
+    int engine = 0;                 // 0 = automatic, 1 = CUDA-core FP32, 2 = tcgen05
     // dense storage: row-major, row stride ldx floats (multiple of 4)
     const float *X = nullptr;
     int ldx = 0;

@@ -3,22 +3,28 @@
 //     out[i][j] = kfn( sum_k W[i][k] * X[j][k] ),   i < m requested rows, j < n instances
 //
 // as an error-compensated 3xTF32 contraction. Both operands are stored split into two TF32
-// planes (x = hi + lo); every k-step issues three tcgen05.mma (hi*hi, hi*lo, lo*hi) into one
+// planes (x = hi + lo); every k-step issues three tcgen05.mma (lo*hi, hi*lo, hi*hi) into an
 // FP32 accumulator in tensor memory. Operand tiles travel HBM/L2 -> shared memory by TMA
-// (128-byte swizzle, zero fill outside the matrices), the accumulator is read back with
-// tcgen05.ld and the kernel function (RBF / polynomial / sigmoid / linear, with the self-dot
-// norms) is applied in the epilogue before the only store to HBM.
+// (128-byte swizzle, zero fill outside the matrices).
+//
+// The tensor core adds into its accumulator with truncation (measured: about half an ulp of the
+// accumulator lost per MMA, always towards zero), which on long same-sign sums is far outside
+// the 1e-5 bound on kernel values. Tensor memory therefore only ever holds the partial sum of
+// ONE 32-wide k slab: the two 256-column accumulators alternate slab by slab, and the epilogue
+// warps move every finished slab into FP32 registers (tcgen05.ld + round-to-nearest adds on the
+// CUDA cores) while the tensor core works on the next slab. The kernel function (RBF /
+// polynomial / sigmoid / linear, with the self-dot norms) is applied to the register sums
+// before the only store to HBM.
 //
 // Replaces the reference's cublasSgemm + separate RBF pass
 // (src/thundersvm/kernel/kernelmatrix_kernel.cu:311-330, 58-67; kernelmatrix.cpp:318-343).
 //
-// CTA layout (192 threads, one CTA per SM, persistent over tiles):
+// CTA layout (320 threads, one CTA per SM, persistent over tiles):
 //   warp 0      : TMA producer (one elected lane)
 //   warp 1      : allocates tensor memory, issues the MMAs (one elected lane)
-//   warps 2..5  : epilogue; warp w reads tensor-memory lanes 32*(w%4) .. +31
-// Tile: 128 instances (MMA M, tensor-memory lanes) x 256 requested rows (MMA N, columns);
-// two accumulators (2 x 256 columns) so that the epilogue of one tile overlaps the MMAs of the
-// next. k advances in slabs of 32 floats (one 128-byte swizzle row) through a 2-stage ring.
+//   warps 2..9  : slab promotion + epilogue; warp w owns tensor-memory lanes 32*(w%4) .. +31 and
+//                 columns 128*((w-2)/4) .. +127 (128 FP32 sums per thread)
+// Tile: 128 instances (MMA M, tensor-memory lanes) x 256 requested rows (MMA N, columns).
 // Every wait is bounded; on expiry the kernel records a status word and winds down.
 #include "common.cuh"
 #include <cuda.h>
@@ -31,7 +37,7 @@ constexpr uint32_t A_BYTES = BM * BK * 4;          // 16 KB per plane
 constexpr uint32_t B_BYTES = BN * BK * 4;          // 32 KB per plane
 constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // 96 KB
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320, EPI_WARPS = 8, COLS_PER_THREAD = 128;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr long long WAIT_NS = 2000000000ll;        // 2 s budget for any single wait
 // tcgen05 instruction descriptor: D=F32, A=B=TF32, both K-major, N=256, M=128
@@ -139,7 +145,7 @@ dense_rows_tc_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar + 8 * a, 1); mbar_init(tempty_bar + 8 * a, 128); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar + 8 * a, 1); mbar_init(tempty_bar + 8 * a, EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -173,67 +179,75 @@ dense_rows_tc_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_c
                     }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
+        // ---------------- MMA issuer: one k slab per tensor-memory accumulator ----------------
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x)
-                for (int nb = 0; nb < n_blocks && ok; ++nb) {
-                    if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, 2)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int nb = 0; nb < n_blocks && ok; ++nb)
                     for (int kb = 0; kb < k_blocks; ++kb) {
+                        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, 2)) { ok = false; break; }
                         if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
                         tc_fence_after();
+                        const uint32_t d_tmem = tmem_base + acc * BN;
                         const uint32_t base = ring + stage * STAGE_BYTES;
+                        // the two small cross terms first, while the accumulator is still tiny
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
                             const uint32_t koff = k * UMMA_K * 4;
-                            const uint64_t a_hi = smem_desc_sw128(base + koff);
-                            const uint64_t a_lo = smem_desc_sw128(base + A_BYTES + koff);
-                            const uint64_t b_hi = smem_desc_sw128(base + 2 * A_BYTES + koff);
-                            const uint64_t b_lo = smem_desc_sw128(base + 2 * A_BYTES + B_BYTES + koff);
-                            umma_tf32(d_tmem, a_lo, b_hi, (kb | k) != 0);
-                            umma_tf32(d_tmem, a_hi, b_lo, 1);
-                            umma_tf32(d_tmem, a_hi, b_hi, 1);
+                            umma_tf32(d_tmem, smem_desc_sw128(base + A_BYTES + koff),
+                                      smem_desc_sw128(base + 2 * A_BYTES + koff), k != 0);
+                            umma_tf32(d_tmem, smem_desc_sw128(base + koff),
+                                      smem_desc_sw128(base + 2 * A_BYTES + B_BYTES + koff), 1);
                         }
-                        umma_commit(empty_bar + 8 * stage);      // stage reusable once these MMAs retire
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint32_t koff = k * UMMA_K * 4;
+                            umma_tf32(d_tmem, smem_desc_sw128(base + koff), smem_desc_sw128(base + 2 * A_BYTES + koff), 1);
+                        }
+                        umma_commit(empty_bar + 8 * stage);      // smem stage reusable once these MMAs retire
+                        umma_commit(tfull_bar + 8 * acc);        // slab sum complete in tensor memory
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                     }
-                    if (!ok) break;
-                    umma_commit(tfull_bar + 8 * acc);            // accumulator complete
-                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-                }
         }
     } else {
-        // ---------------- epilogue ----------------
-        const int quarter = warp & 3;
+        // ---------------- slab promotion + epilogue ----------------
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
             const int j = mt * BM + quarter * 32 + lane;
             const float sdj = j < n ? sd[j] : 0.0f;
             for (int nb = 0; nb < n_blocks && ok; ++nb) {
-                if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t) (quarter * 32) << 16) + acc * BN;
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    const int i0 = nb * BN + c0;
-                    if (i0 >= m) break;                      // warp-uniform
-                    uint32_t v[32];
-                    tmem_ld32(taddr + c0, v);
-                    if (j < n) {
+                float sum[COLS_PER_THREAD];
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            const int i = i0 + c;
-                            if (i < m)
-                                out[(size_t) i * ld_out + j] = apply_kernel(fn, __uint_as_float(v[c]), __ldg(sd_rows + i), sdj);
-                        }
+                for (int c = 0; c < COLS_PER_THREAD; ++c) sum[c] = 0.0f;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t taddr = tmem_base + ((uint32_t) (quarter * 32) << 16) + acc * BN + half * COLS_PER_THREAD;
+#pragma unroll
+                    for (int c0 = 0; c0 < COLS_PER_THREAD; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(taddr + c0, v);
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) sum[c0 + c] += __uint_as_float(v[c]);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                }
+                if (!ok) break;
+                if (j < n) {
+                    const int i0 = nb * BN + half * COLS_PER_THREAD;
+#pragma unroll
+                    for (int c = 0; c < COLS_PER_THREAD; ++c) {
+                        const int i = i0 + c;
+                        if (i < m) out[(size_t) i * ld_out + j] = apply_kernel(fn, sum[c], __ldg(sd_rows + i), sdj);
                     }
                 }
-                tc_fence_before();
-                mbar_arrive(tempty_bar + 8 * acc);
-                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
         }
     }

@@ -352,10 +352,15 @@ static tsvm_status finish_create(tsvm_km *km, cudaStream_t st) {
     return TSVM_OK;
 }
 
+// engine: 0 = automatic, 1 = CUDA cores, 2 = tensor cores
+static inline bool use_tensor_engine(const tsvm_km *km) {
+    return km->engine == 2 || (km->engine == 0 && km->d_pad > 32);
+}
+
 static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
     // W / WT and sd_rows are staged; run the engine.
     if (km->dense) {
-        if (km->engine == 0) return launch_dense_tc(km, m, out, ld_out, st);
+        if (use_tensor_engine(km)) return launch_dense_tc(km, m, out, ld_out, st);
         dim3 grid(ceil_div(km->n, 64), ceil_div(m, 64));
         TSVM_LAUNCH(dense_rows_simt_kernel, grid, 256, 0, st, km->X, km->ldx, km->n, km->W, km->d_pad, m, km->d_pad,
                     km->self_dot, km->sd_rows, km->fn, out, ld_out);
@@ -477,7 +482,7 @@ const float *tsvm_km_diag_dev(const tsvm_km *km) { return km ? km->diag : nullpt
 const float *tsvm_km_self_dot_dev(const tsvm_km *km) { return km ? km->self_dot : nullptr; }
 
 tsvm_status tsvm_km_set_dense_engine(tsvm_km *km, int engine) {
-    TSVM_REQUIRE(km && (engine == 0 || engine == 1), "set_dense_engine: bad arguments");
+    TSVM_REQUIRE(km && engine >= 0 && engine <= 2, "set_dense_engine: bad arguments");
     km->engine = engine;
     return TSVM_OK;
 }
@@ -488,7 +493,7 @@ tsvm_status tsvm_km_rows_by_index(tsvm_km *km, const int *idx_dev, int q, float 
     cudaStream_t st = (cudaStream_t) stream;
     TSVM_TRY(ensure_scratch(km, q));
     if (km->dense) {
-        const bool tc = km->engine == 0;
+        const bool tc = use_tensor_engine(km);
         TSVM_LAUNCH(gather_rows_dense_kernel, q, 256, 0, st, km->X, km->ldx, km->d, km->d_pad, idx_dev, q,
                     km->self_dot, tc ? nullptr : km->W, tc ? km->Whi : nullptr, tc ? km->Wlo : nullptr, km->sd_rows);
         return rows_common(km, q, out_dev, ld_out, st);
@@ -515,7 +520,7 @@ tsvm_status tsvm_km_rows_by_instances_dense(tsvm_km *km, const float *T_dev, int
         TSVM_TRY(ensure_scratch(km, mm));
         TSVM_LAUNCH(self_dot_seq_dense_kernel, ceil_div(mm, 128), 128, 0, st, T, mm, dt, ldt, km->sd_rows);
         if (km->dense) {
-            const bool tc = km->engine == 0;
+            const bool tc = use_tensor_engine(km);
             TSVM_LAUNCH(stage_rows_dense_kernel, mm, 256, 0, st, T, ldt, dt, km->d, km->d_pad, mm,
                         tc ? nullptr : km->W, tc ? km->Whi : nullptr, tc ? km->Wlo : nullptr);
             TSVM_TRY(rows_common(km, mm, o, ld_out, st));
@@ -545,7 +550,7 @@ tsvm_status tsvm_km_rows_by_instances_csr(tsvm_km *km, const float *tval_dev, co
         TSVM_TRY(ensure_scratch(km, mm));
         TSVM_LAUNCH(self_dot_seq_csr_kernel, ceil_div(mm, 128), 128, 0, st, tval_dev, rp, mm, km->sd_rows);
         if (km->dense) {
-            const bool tc = km->engine == 0;
+            const bool tc = use_tensor_engine(km);
             if (tc) {
                 TSVM_CUDA(cudaMemsetAsync(km->Whi, 0, sizeof(float) * (size_t) mm * km->d_pad, st));
                 TSVM_CUDA(cudaMemsetAsync(km->Wlo, 0, sizeof(float) * (size_t) mm * km->d_pad, st));

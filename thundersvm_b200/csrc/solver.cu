@@ -779,71 +779,79 @@ int tsvm_working_set_size(int n_instances, int n_features, size_t max_mem_bytes,
     return (int) (a < b ? a : b);
 }
 
-tsvm_status tsvm_smo_solve(tsvm_km *km, int solver_kind, const int *y_dev, double *alpha_dev, double *f_dev,
-                           double eps, double Cp, double Cn, int ws_size, int max_iter, double *rho_host,
-                           tsvm_solve_stats *stats_host, void *stream) {
-    TSVM_REQUIRE(km && y_dev && alpha_dev && f_dev && rho_host, "smo_solve: null argument");
-    TSVM_REQUIRE(solver_kind >= 0 && solver_kind <= 2, "smo_solve: unknown solver %d", solver_kind);
-    const int n = km->n;
-    TSVM_REQUIRE(ws_size >= 2 && ws_size <= 1024 && ws_size <= n && (ws_size & (ws_size - 1)) == 0,
-                 "smo_solve: working-set size %d must be a power of two in [2, min(n, 1024)]", ws_size);
-    cudaStream_t st = (cudaStream_t) stream;
-    const int q = ws_size / 2;
-    const long long ld = ((long long) n + 3) & ~3ll;
-    const long long launches0 = launch_count();
-    const auto t_begin = std::chrono::steady_clock::now();
+}  // extern "C"
 
-    struct Bufs {
-        int *ids = nullptr, *y_ws = nullptr;
-        float *rows = nullptr, *kww = nullptr, *diag_ws = nullptr;
-        double *f_ws = nullptr, *a_ws = nullptr, *alpha_diff = nullptr, *diff = nullptr, *red = nullptr;
-        unsigned char *in_ws = nullptr;
-        tsvm_ws *sel = nullptr;
-        double *diff_host = nullptr;
-        cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
-        ~Bufs() {
-            cudaFree(ids); cudaFree(y_ws); cudaFree(rows); cudaFree(kww); cudaFree(diag_ws); cudaFree(f_ws);
-            cudaFree(a_ws); cudaFree(alpha_diff); cudaFree(diff); cudaFree(red); cudaFree(in_ws);
-            tsvm_ws_destroy(sel);
-            if (diff_host) cudaFreeHost(diff_host);
-            for (auto e : ev) if (e) cudaEventDestroy(e);
-        }
-    } B;
-    TSVM_TRY(dev_alloc(&B.ids, (size_t) ws_size));
-    TSVM_TRY(dev_alloc(&B.y_ws, (size_t) ws_size));
-    TSVM_TRY(dev_alloc(&B.rows, (size_t) ws_size * ld));
-    TSVM_TRY(dev_alloc(&B.kww, (size_t) ws_size * ws_size));
-    TSVM_TRY(dev_alloc(&B.diag_ws, (size_t) ws_size));
-    TSVM_TRY(dev_alloc(&B.f_ws, (size_t) ws_size));
-    TSVM_TRY(dev_alloc(&B.a_ws, (size_t) ws_size));
-    TSVM_TRY(dev_alloc(&B.alpha_diff, (size_t) ws_size));
-    TSVM_TRY(dev_alloc(&B.diff, 4));
-    TSVM_TRY(dev_alloc(&B.red, 16));   // >= RHO_VALS
-    TSVM_TRY(dev_alloc(&B.in_ws, (size_t) n));
-    TSVM_CUDA(cudaMemsetAsync(B.in_ws, 0, (size_t) n, st));
-    TSVM_TRY(tsvm_ws_create(n, ws_size, &B.sel));
-    TSVM_CUDA(cudaMallocHost((void **) &B.diff_host, 16 * sizeof(double)));
-    const bool timing = stats_host != nullptr;
-    if (timing) for (auto &e : B.ev) TSVM_CUDA(cudaEventCreate(&e));
+// Solver state that persists across outer iterations.
+struct tsvm_solver {
+    tsvm_km *km = nullptr;
+    int kind = 0, ws = 0, q = 0, n = 0;
+    const int *y = nullptr;
+    double *alpha = nullptr, *f = nullptr;
+    double eps = 0, Cp = 0, Cn = 0;
+    long long ld = 0;
+    cudaStream_t st = nullptr;
+    // device buffers
+    int *ids = nullptr, *y_ws = nullptr;
+    float *rows = nullptr, *kww = nullptr, *diag_ws = nullptr;
+    double *f_ws = nullptr, *a_ws = nullptr, *alpha_diff = nullptr, *diff = nullptr, *red = nullptr;
+    unsigned char *in_ws = nullptr;
+    tsvm_ws *sel = nullptr;
+    double *diff_host = nullptr;
+    cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    // iteration state (csmosolver.cpp:51-57)
+    long long iter = 0, local_iter = 0, rows_made = 0, launches0 = 0;
+    int same_cnt = 0, swap_cnt = 0, local_max_iter = 0;
+    double prev = INFINITY, last = INFINITY, second_last = INFINITY, diff0 = 0;
     double t_sel = 0, t_rows = 0, t_loc = 0, t_upd = 0;
-    long long rows_made = 0;
+    bool done = false;
+    std::chrono::steady_clock::time_point t_begin;
 
-    // ---- init_f (csmosolver.cpp:189-214): f -= sum over initially non-zero alphas --------------
-    {
+    ~tsvm_solver() {
+        cudaFree(ids); cudaFree(y_ws); cudaFree(rows); cudaFree(kww); cudaFree(diag_ws); cudaFree(f_ws);
+        cudaFree(a_ws); cudaFree(alpha_diff); cudaFree(diff); cudaFree(red); cudaFree(in_ws);
+        tsvm_ws_destroy(sel);
+        if (diff_host) cudaFreeHost(diff_host);
+        for (auto e : ev) if (e) cudaEventDestroy(e);
+    }
+
+    tsvm_status init() {
+        TSVM_TRY(dev_alloc(&ids, (size_t) ws));
+        TSVM_TRY(dev_alloc(&y_ws, (size_t) ws));
+        TSVM_TRY(dev_alloc(&rows, (size_t) ws * ld));
+        TSVM_TRY(dev_alloc(&kww, (size_t) ws * ws));
+        TSVM_TRY(dev_alloc(&diag_ws, (size_t) ws));
+        TSVM_TRY(dev_alloc(&f_ws, (size_t) ws));
+        TSVM_TRY(dev_alloc(&a_ws, (size_t) ws));
+        TSVM_TRY(dev_alloc(&alpha_diff, (size_t) ws));
+        TSVM_TRY(dev_alloc(&diff, 4));
+        TSVM_TRY(dev_alloc(&red, 16));   // >= RHO_VALS
+        TSVM_TRY(dev_alloc(&in_ws, (size_t) n));
+        TSVM_CUDA(cudaMemsetAsync(in_ws, 0, (size_t) n, st));
+        TSVM_TRY(tsvm_ws_create(n, ws, &sel));
+        TSVM_CUDA(cudaMallocHost((void **) &diff_host, 16 * sizeof(double)));
+        for (auto &e : ev) TSVM_CUDA(cudaEventCreate(&e));
+        // local iteration cap: max(100000, 100 * ws) (csmosolver.cpp:49)
+        local_max_iter = ws > INT_MAX / 100 ? INT_MAX : (100 * ws > 100000 ? 100 * ws : 100000);
+        return init_f();
+    }
+
+    // init_f (csmosolver.cpp:189-214): f -= sum over the initially non-zero alphas
+    tsvm_status init_f() {
         std::vector<double> a_h(n);
         std::vector<int> y_h(n);
-        TSVM_CUDA(cudaMemcpyAsync(a_h.data(), alpha_dev, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
-        TSVM_CUDA(cudaMemcpyAsync(y_h.data(), y_dev, sizeof(int) * n, cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaMemcpyAsync(a_h.data(), alpha, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaMemcpyAsync(y_h.data(), y, sizeof(int) * n, cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaStreamSynchronize(st));
         std::vector<int> bi;
         std::vector<double> bd;
         auto flush = [&]() -> tsvm_status {
             if (bi.empty()) return TSVM_OK;
             const int m = (int) bi.size();
-            TSVM_CUDA(cudaMemcpyAsync(B.ids, bi.data(), sizeof(int) * m, cudaMemcpyHostToDevice, st));
-            TSVM_CUDA(cudaMemcpyAsync(B.alpha_diff, bd.data(), sizeof(double) * m, cudaMemcpyHostToDevice, st));
-            TSVM_TRY(tsvm_km_rows_by_index(km, B.ids, m, B.rows, ld, st));
-            TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f_dev, n, B.alpha_diff, m, 0, 0, B.rows, ld, rows_vec_ok(B.rows, ld));
+            TSVM_CUDA(cudaMemcpyAsync(ids, bi.data(), sizeof(int) * m, cudaMemcpyHostToDevice, st));
+            TSVM_CUDA(cudaMemcpyAsync(alpha_diff, bd.data(), sizeof(double) * m, cudaMemcpyHostToDevice, st));
+            TSVM_TRY(tsvm_km_rows_by_index(km, ids, m, rows, ld, st));
+            TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, m, 0, 0, rows, ld,
+                        rows_vec_ok(rows, ld));
             TSVM_CUDA(cudaStreamSynchronize(st));
             rows_made += m;
             bi.clear(); bd.clear();
@@ -851,110 +859,166 @@ tsvm_status tsvm_smo_solve(tsvm_km *km, int solver_kind, const int *y_dev, doubl
         };
         for (int i = 0; i < n; ++i) {
             if (a_h[i] != 0) { bi.push_back(i); bd.push_back(-a_h[i] * y_h[i]); }
-            if ((int) bi.size() == ws_size) TSVM_TRY(flush());
+            if ((int) bi.size() == ws) TSVM_TRY(flush());
         }
-        TSVM_TRY(flush());
+        return flush();
     }
 
-    // local iteration cap: max(100000, 100 * ws) (csmosolver.cpp:49)
-    const int local_max_iter = ws_size > INT_MAX / 100 ? INT_MAX : (100 * ws_size > 100000 ? 100 * ws_size : 100000);
-    long long local_iter = 0;
-    int same_cnt = 0, swap_cnt = 0;
-    double prev = INFINITY, last = INFINITY, second_last = INFINITY, diff0 = 0;
-    long long iter = 0;
-    for (;; ++iter) {
+    // One outer iteration of csmosolver.cpp:59-120. Sets `done` by the reference's rules
+    // (csmosolver.cpp:86-111) except the iteration cap, which the caller applies.
+    tsvm_status outer_iteration() {
         const int first_half_phys = (int) (iter & 1);   // iteration 0 fills both halves in logical order
-        if (timing) TSVM_CUDA(cudaEventRecord(B.ev[0], st));
+        TSVM_CUDA(cudaEventRecord(ev[0], st));
         if (iter == 0) {
-            TSVM_TRY(tsvm_select_working_set(B.sel, solver_kind, n, f_dev, alpha_dev, y_dev, nullptr, Cp, Cn, ws_size,
-                                             B.ids, st));
-            if (timing) TSVM_CUDA(cudaEventRecord(B.ev[1], st));
-            TSVM_TRY(tsvm_km_rows_by_index(km, B.ids, ws_size, B.rows, ld, st));
-            rows_made += ws_size;
+            TSVM_TRY(tsvm_select_working_set(sel, kind, n, f, alpha, y, nullptr, Cp, Cn, ws, ids, st));
+            TSVM_CUDA(cudaEventRecord(ev[1], st));
+            TSVM_TRY(tsvm_km_rows_by_index(km, ids, ws, rows, ld, st));
+            rows_made += ws;
         } else {
-            TSVM_LAUNCH(shift_ws_kernel, ceil_div(q, 1024), 1024, 0, st, B.ids, q, B.in_ws);
-            TSVM_TRY(tsvm_select_working_set(B.sel, solver_kind, n, f_dev, alpha_dev, y_dev, B.in_ws, Cp, Cn, q,
-                                             B.ids + q, st));
-            if (timing) TSVM_CUDA(cudaEventRecord(B.ev[1], st));
-            TSVM_TRY(tsvm_km_rows_by_index(km, B.ids + q, q, B.rows + (size_t) (1 - first_half_phys) * q * ld, ld, st));
+            TSVM_LAUNCH(shift_ws_kernel, 1, 1024, 0, st, ids, q, in_ws);
+            TSVM_TRY(tsvm_select_working_set(sel, kind, n, f, alpha, y, in_ws, Cp, Cn, q, ids + q, st));
+            TSVM_CUDA(cudaEventRecord(ev[1], st));
+            TSVM_TRY(tsvm_km_rows_by_index(km, ids + q, q, rows + (size_t) (1 - first_half_phys) * q * ld, ld, st));
             rows_made += q;
         }
-        if (timing) TSVM_CUDA(cudaEventRecord(B.ev[2], st));
-        TSVM_LAUNCH(gather_ws_kernel, ws_size, 256, 0, st, ws_size, q, first_half_phys, B.ids, B.rows, ld, km->diag,
-                    y_dev, f_dev, alpha_dev, B.kww, B.diag_ws, B.y_ws, B.f_ws, B.a_ws);
-        TSVM_TRY(launch_local_smo(solver_kind, ws_size, B.kww, B.diag_ws, B.y_ws, B.f_ws, B.a_ws, B.alpha_diff, Cp, Cn,
-                                  eps, local_max_iter, B.diff, B.ids, alpha_dev, st));
-        if (timing) TSVM_CUDA(cudaEventRecord(B.ev[3], st));
-        TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f_dev, n, B.alpha_diff, ws_size, q, first_half_phys,
-                    B.rows, ld, rows_vec_ok(B.rows, ld));
-        if (timing) TSVM_CUDA(cudaEventRecord(B.ev[4], st));
-        TSVM_CUDA(cudaMemcpyAsync(B.diff_host, B.diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaEventRecord(ev[2], st));
+        TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st, ws, q, first_half_phys, ids, rows, ld, km->diag, y, f, alpha, kww,
+                    diag_ws, y_ws, f_ws, a_ws);
+        TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter,
+                                  diff, ids, alpha, st));
+        TSVM_CUDA(cudaEventRecord(ev[3], st));
+        TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows, ld,
+                    rows_vec_ok(rows, ld));
+        TSVM_CUDA(cudaEventRecord(ev[4], st));
+        TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaMemcpyAsync(km->status_host, km->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaStreamSynchronize(st));
         if (km->status_host[0] != 0) {
             set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", km->status_host[0]);
             return TSVM_ERR_DEVICE;
         }
-        if (timing) {
-            float ms;
-            cudaEventElapsedTime(&ms, B.ev[0], B.ev[1]); t_sel += ms;
-            cudaEventElapsedTime(&ms, B.ev[1], B.ev[2]); t_rows += ms;
-            cudaEventElapsedTime(&ms, B.ev[2], B.ev[3]); t_loc += ms;
-            cudaEventElapsedTime(&ms, B.ev[3], B.ev[4]); t_upd += ms;
-        }
-        diff0 = B.diff_host[0];
-        local_iter += (long long) B.diff_host[1];
-        // termination rules of csmosolver.cpp:86-111
+        float ms;
+        cudaEventElapsedTime(&ms, ev[0], ev[1]); t_sel += ms;
+        cudaEventElapsedTime(&ms, ev[1], ev[2]); t_rows += ms;
+        cudaEventElapsedTime(&ms, ev[2], ev[3]); t_loc += ms;
+        cudaEventElapsedTime(&ms, ev[3], ev[4]); t_upd += ms;
+        diff0 = diff_host[0];
+        local_iter += (long long) diff_host[1];
         if (fabs(diff0 - prev) < eps * 0.001) same_cnt++;
         else { same_cnt = 0; prev = diff0; }
         if (fabs(diff0 - second_last) < eps * 0.001) swap_cnt++;
         else swap_cnt = 0;
         second_last = last;
         last = diff0;
-        if ((same_cnt >= 10 && fabs(diff0 - 2.0) > eps) || diff0 < eps || (max_iter != -1 && iter == max_iter) ||
-            (swap_cnt >= 10 && fabs(diff0 - 2.0) > eps))
-            break;
+        if ((same_cnt >= 10 && fabs(diff0 - 2.0) > eps) || diff0 < eps || (swap_cnt >= 10 && fabs(diff0 - 2.0) > eps))
+            done = true;
+        ++iter;
+        return TSVM_OK;
     }
 
-    // ---- rho and objective (csmosolver.cpp:167-187,227-239; nusmosolver.cpp:9-46,120-126) -----------
-    TSVM_LAUNCH(rho_obj_kernel, 1, 1024, 0, st, n, f_dev, alpha_dev, y_dev, Cp, Cn, B.red);
-    TSVM_CUDA(cudaMemcpyAsync(B.diff_host, B.red, RHO_VALS * sizeof(double), cudaMemcpyDeviceToHost, st));
-    TSVM_CUDA(cudaStreamSynchronize(st));
-    const double *R = B.diff_host;
-    const double obj = -R[4];
-    double rho;
-    if (solver_kind == TSVM_SOLVER_C) {
-        const double nfree = R[0] + R[2];
-        rho = nfree != 0 ? (R[1] + R[3]) / nfree : -(fmin(R[5], R[7]) + fmax(R[6], R[8])) / 2;
-    } else {
-        // nusmosolver.cpp:9-46 works with -f: r = -(min_{I_up}(-f) + max_{I_low}(-f)) / 2
-        //                                       =  (max_{I_up} f + min_{I_low} f) / 2
-        const double r1 = R[0] != 0 ? R[1] / R[0] : (R[9] + R[10]) / 2;
-        const double r2 = R[2] != 0 ? -R[3] / R[2] : (R[11] + R[12]) / 2;
-        rho = (r1 - r2) / 2;
-        if (solver_kind == TSVM_SOLVER_NU_SVC) {
-            const double r = (r1 + r2) / 2;
-            TSVM_LAUNCH(scale_kernel, ceil_div(n, 256), 256, 0, st, alpha_dev, n, r);
-            TSVM_CUDA(cudaStreamSynchronize(st));
-            rho /= r;
+    void fill_stats(tsvm_solve_stats *out, double obj) const {
+        out->outer_iters = iter;
+        out->local_iters = local_iter;
+        out->final_diff = diff0;
+        out->objective = obj;
+        out->seconds_select = t_sel * 1e-3;
+        out->seconds_rows = t_rows * 1e-3;
+        out->seconds_local = t_loc * 1e-3;
+        out->seconds_update = t_upd * 1e-3;
+        out->seconds_total = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_begin).count();
+        out->kernel_rows = rows_made;
+        out->gpu_launches = launch_count() - launches0;
+    }
+
+    // rho and objective (csmosolver.cpp:167-187,227-239; nusmosolver.cpp:9-46,120-126)
+    tsvm_status finish(double *rho_host, tsvm_solve_stats *stats_host) {
+        TSVM_LAUNCH(rho_obj_kernel, 1, 1024, 0, st, n, f, alpha, y, Cp, Cn, red);
+        TSVM_CUDA(cudaMemcpyAsync(diff_host, red, RHO_VALS * sizeof(double), cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaStreamSynchronize(st));
+        const double *R = diff_host;
+        const double obj = -R[4];
+        double rho;
+        if (kind == TSVM_SOLVER_C) {
+            const double nfree = R[0] + R[2];
+            rho = nfree != 0 ? (R[1] + R[3]) / nfree : -(fmin(R[5], R[7]) + fmax(R[6], R[8])) / 2;
+        } else {
+            // nusmosolver.cpp:9-46 works with -f: r = -(min_{I_up}(-f) + max_{I_low}(-f)) / 2
+            //                                       =  (max_{I_up} f + min_{I_low} f) / 2
+            const double r1 = R[0] != 0 ? R[1] / R[0] : (R[9] + R[10]) / 2;
+            const double r2 = R[2] != 0 ? -R[3] / R[2] : (R[11] + R[12]) / 2;
+            rho = (r1 - r2) / 2;
+            if (kind == TSVM_SOLVER_NU_SVC) {
+                const double r = (r1 + r2) / 2;
+                TSVM_LAUNCH(scale_kernel, ceil_div(n, 256), 256, 0, st, alpha, n, r);
+                TSVM_CUDA(cudaStreamSynchronize(st));
+                rho /= r;
+            }
         }
+        *rho_host = rho;
+        if (stats_host) fill_stats(stats_host, obj);
+        return TSVM_OK;
     }
-    *rho_host = rho;
-    if (stats_host) {
-        stats_host->outer_iters = iter + 1;
-        stats_host->local_iters = local_iter;
-        stats_host->final_diff = diff0;
-        stats_host->objective = obj;
-        stats_host->seconds_select = t_sel * 1e-3;
-        stats_host->seconds_rows = t_rows * 1e-3;
-        stats_host->seconds_local = t_loc * 1e-3;
-        stats_host->seconds_update = t_upd * 1e-3;
-        stats_host->seconds_total =
-            std::chrono::duration<double>(std::chrono::steady_clock::now() - t_begin).count();
-        stats_host->kernel_rows = rows_made;
-        stats_host->gpu_launches = launch_count() - launches0;
-    }
+};
+
+extern "C" {
+
+// ---- the solver as an object: create / iterate / finish -------------------------------------------
+tsvm_status tsvm_solver_create(tsvm_km *km, int solver_kind, const int *y_dev, double *alpha_dev, double *f_dev,
+                               double eps, double Cp, double Cn, int ws_size, void *stream, tsvm_solver **out) {
+    TSVM_REQUIRE(out && km && y_dev && alpha_dev && f_dev, "solver_create: null argument");
+    TSVM_REQUIRE(solver_kind >= 0 && solver_kind <= 2, "solver_create: unknown solver %d", solver_kind);
+    const int n = km->n;
+    TSVM_REQUIRE(ws_size >= 2 && ws_size <= 1024 && ws_size <= n && (ws_size & (ws_size - 1)) == 0,
+                 "solver_create: working-set size %d must be a power of two in [2, min(n, 1024)]", ws_size);
+    *out = nullptr;
+    tsvm_solver *S = new tsvm_solver;
+    S->km = km; S->kind = solver_kind; S->y = y_dev; S->alpha = alpha_dev; S->f = f_dev;
+    S->eps = eps; S->Cp = Cp; S->Cn = Cn; S->ws = ws_size; S->q = ws_size / 2; S->n = n;
+    S->ld = ((long long) n + 3) & ~3ll;
+    S->st = (cudaStream_t) stream;
+    S->launches0 = launch_count();
+    S->t_begin = std::chrono::steady_clock::now();
+    tsvm_status s = S->init();
+    if (s != TSVM_OK) { delete S; return s; }
+    *out = S;
     return TSVM_OK;
+}
+
+tsvm_status tsvm_solver_iterate(tsvm_solver *S, int n_iters, int *done_host) {
+    TSVM_REQUIRE(S && n_iters > 0, "solver_iterate: bad arguments");
+    for (int it = 0; it < n_iters && !S->done; ++it) TSVM_TRY(S->outer_iteration());
+    if (done_host) *done_host = S->done ? 1 : 0;
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_solver_finish(tsvm_solver *S, double *rho_host, tsvm_solve_stats *stats_host) {
+    TSVM_REQUIRE(S && rho_host, "solver_finish: null argument");
+    return S->finish(rho_host, stats_host);
+}
+
+tsvm_status tsvm_solver_get_stats(const tsvm_solver *S, tsvm_solve_stats *stats_host) {
+    TSVM_REQUIRE(S && stats_host, "solver_get_stats: null argument");
+    S->fill_stats(stats_host, NAN);
+    return TSVM_OK;
+}
+
+void tsvm_solver_destroy(tsvm_solver *S) { delete S; }
+
+tsvm_status tsvm_smo_solve(tsvm_km *km, int solver_kind, const int *y_dev, double *alpha_dev, double *f_dev,
+                           double eps, double Cp, double Cn, int ws_size, int max_iter, double *rho_host,
+                           tsvm_solve_stats *stats_host, void *stream) {
+    TSVM_REQUIRE(rho_host, "smo_solve: null argument");
+    tsvm_solver *S = nullptr;
+    TSVM_TRY(tsvm_solver_create(km, solver_kind, y_dev, alpha_dev, f_dev, eps, Cp, Cn, ws_size, stream, &S));
+    tsvm_status s = TSVM_OK;
+    // max_iter = k stops after outer iteration k, i.e. k + 1 iterations (csmosolver.cpp:110)
+    while (s == TSVM_OK && !S->done) {
+        s = S->outer_iteration();
+        if (s == TSVM_OK && max_iter != -1 && S->iter - 1 == max_iter) break;
+    }
+    if (s == TSVM_OK) s = S->finish(rho_host, stats_host);
+    delete S;
+    return s;
 }
 
 }  // extern "C"
