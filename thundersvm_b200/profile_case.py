@@ -1,0 +1,62 @@
+"""Small, bounded invocations of single hot-path kernels, for profilers.
+
+    python -m thundersvm_b200.profile_case dense_rows --rows 20000 --reps 3
+    python -m thundersvm_b200.profile_case csr_rows   --rows 20242 --reps 3
+    python -m thundersvm_b200.profile_case solver     --rows 20000 --steps 5
+
+Each case builds seeded synthetic data of the benchmark's shape at a reduced row count (larger than
+L2, a few hundred MB on the device), runs the kernel `reps` times and prints CUDA-event timings.
+"""
+import argparse
+
+import numpy as np
+import torch
+
+from . import capi, synth
+
+
+def _time(fn, reps):
+    out = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record(); e1.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["dense_rows", "csr_rows", "solver"])
+    ap.add_argument("--rows", type=int, default=20000)
+    ap.add_argument("--q", type=int, default=512)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=5)
+    args = ap.parse_args()
+    capi.lib()
+    if args.case in ("dense_rows", "solver"):
+        prob = synth.config5(args.rows)
+        km = capi.KernelMatrix(dense=torch.from_numpy(prob["X"]).cuda(), gamma=prob["gamma"])
+    else:
+        prob = synth.config4(args.rows)
+        val, rp, col = prob["csr"]
+        km = capi.KernelMatrix(csr=(torch.from_numpy(val).cuda(), torch.from_numpy(rp).cuda(),
+                                    torch.from_numpy(col).cuda()), d=prob["d"], gamma=prob["gamma"])
+    n = km.n
+    if args.case == "solver":
+        y = torch.from_numpy(np.where(prob["y"] > 0, 1, -1).astype(np.int32)).cuda()
+        alpha = torch.zeros(n, dtype=torch.float64, device="cuda")
+        f = -y.to(torch.float64)
+        sv = capi.Solver(km, y, alpha, f, 1e-3, prob["C"], prob["C"], 1024)
+        ms = _time(lambda: sv.iterate(1), args.steps)
+        print("solver steps (ms):", ["%.3f" % t for t in ms], sv.stats())
+        return
+    idx = torch.from_numpy(np.random.default_rng(0).choice(n, args.q, replace=False).astype(np.int32)).cuda()
+    out = torch.empty((args.q, n), dtype=torch.float32, device="cuda")
+    km.get_rows(idx, out)
+    torch.cuda.synchronize()
+    ms = _time(lambda: km.get_rows(idx, out), args.reps)
+    print("%s n=%d d=%d q=%d: ms per call %s" % (args.case, n, km.d, args.q, ["%.3f" % t for t in ms]))
+
+
+if __name__ == "__main__":
+    main()
