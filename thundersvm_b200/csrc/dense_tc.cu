@@ -28,7 +28,6 @@
 // Every wait is bounded; on expiry the kernel records a status word and winds down.
 #include "common.cuh"
 #include <cuda.h>
-#include <stdlib.h>
 
 namespace tsvm {
 
@@ -129,7 +128,7 @@ __global__ void __launch_bounds__(tc::THREADS, 1)
 dense_rows_tc_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
                      const __grid_constant__ CUtensorMap map_whi, const __grid_constant__ CUtensorMap map_wlo,
                      int n, int m, int d_pad, const float *__restrict__ sd, const float *__restrict__ sd_rows,
-                     KernelFn fn, float *__restrict__ out, long long ld_out, int *__restrict__ status, int dbg) {
+                     KernelFn fn, float *__restrict__ out, long long ld_out, int *__restrict__ status) {
     using namespace tc;
     extern __shared__ uint8_t smem_raw[];
     // operand ring, 1024-byte aligned (swizzle atom = 8 rows x 128 B)
@@ -195,7 +194,6 @@ dense_rows_tc_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_c
                         // the two small cross terms first, while the accumulator is still tiny
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
-                            if (dbg & 2) break;
                             const uint32_t koff = k * UMMA_K * 4;
                             umma_tf32(d_tmem, smem_desc_sw128(base + A_BYTES + koff),
                                       smem_desc_sw128(base + 2 * A_BYTES + koff), k != 0);
@@ -205,7 +203,7 @@ dense_rows_tc_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_c
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
                             const uint32_t koff = k * UMMA_K * 4;
-                            umma_tf32(d_tmem, smem_desc_sw128(base + koff), smem_desc_sw128(base + 2 * A_BYTES + koff), (dbg & 2) ? (k != 0) : 1);
+                            umma_tf32(d_tmem, smem_desc_sw128(base + koff), smem_desc_sw128(base + 2 * A_BYTES + koff), 1);
                         }
                         umma_commit(empty_bar + 8 * stage);      // smem stage reusable once these MMAs retire
                         umma_commit(tfull_bar + 8 * acc);        // slab sum complete in tensor memory
@@ -231,7 +229,6 @@ dense_rows_tc_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_c
                     const uint32_t taddr = tmem_base + ((uint32_t) (quarter * 32) << 16) + acc * BN + half * COLS_PER_THREAD;
 #pragma unroll
                     for (int c0 = 0; c0 < COLS_PER_THREAD; c0 += 32) {
-                        if ((dbg & 1) && c0 > 0) continue;
                         uint32_t v[32];
                         tmem_ld32(taddr + c0, v);
 #pragma unroll
@@ -320,8 +317,7 @@ tsvm_status launch_dense_tc(tsvm_km *km, int m, float *out, long long ld_out, cu
     const int m_tiles = ceil_div(km->n, tc::BM);
     const int grid = m_tiles < sms ? m_tiles : sms;
     TSVM_LAUNCH(dense_rows_tc_kernel, grid, tc::THREADS, tc::SMEM_BYTES, st, mxh, mxl, mwh, mwl, km->n, m, km->d_pad,
-                km->self_dot, km->sd_rows, km->fn, out, ld_out, km->status_dev,
-                getenv("TSVM_TC_DEBUG") ? atoi(getenv("TSVM_TC_DEBUG")) : 0);
+                km->self_dot, km->sd_rows, km->fn, out, ld_out, km->status_dev);
     return TSVM_OK;
 }
 
