@@ -175,6 +175,24 @@ tsvm_status tsvm_select_working_set(tsvm_ws *w, int solver_kind, int n, const do
                                     const double *alpha_dev, const int *y_dev, const unsigned char *in_ws_dev,
                                     double Cp, double Cn, int want, int *out_ids_dev, void *stream);
 
+/* Allocation-free working-set selection. Same result as tsvm_select_working_set, but needs no tsvm_ws
+ * and calls neither cudaMalloc / cudaFree nor any other allocating routine: its scratch (selection
+ * state, radix histograms, candidate lists; about 114 KB) is a fixed array inside the library image,
+ * resident on every GPU that loads the library. It has no counterpart in the reference. It is meant
+ * for callers that must not allocate at the point where they pick a working set: a solver loop that
+ * has handed all device memory to its own pool (a later cudaMalloc would fail or fragment it), or a
+ * latency-sensitive loop sharing the GPU with other streams, which a cudaMalloc would stall because
+ * allocation synchronises the whole device.
+ * Limits and rules: want <= 1024 (TSVM_ERR_INVALID with a message otherwise; n is unlimited). The
+ * first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current) - make that first call outside any stream capture. All calls on a device share
+ * the one array: it still holds the previous call's contents when a call starts (the entry point
+ * clears what must start at zero itself), and two calls that overlap on the GPU - from different
+ * streams or threads - race on it; serialise them. */
+tsvm_status tsvm_select_working_set_static(int solver_kind, int n, const double *f_dev, const double *alpha_dev,
+                                           const int *y_dev, const unsigned char *in_ws_dev, double Cp,
+                                           double Cn, int want, int *out_ids_dev, void *stream);
+
 /* Local SMO on one working set: svm_kernel::c_smo_solve / nu_smo_solve
  * (smo_kernel.cu:28-287). kww_dev is the ws x ws block K(x_ws[a], x_ws[b]) (row-major,
  * stride ws); y/f/alpha/diag_ws_dev hold the working set's values in slot order. Outputs:

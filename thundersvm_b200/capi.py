@@ -25,6 +25,7 @@ EXPORTS = [
     "tsvm_km_rows_by_instances_csr", "tsvm_km_set_dense_engine", "tsvm_smo_solve", "tsvm_solver_create",
     "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_destroy", "tsvm_working_set_size",
     "tsvm_ws_create", "tsvm_ws_destroy", "tsvm_ws_candidates", "tsvm_ws_merge", "tsvm_select_working_set",
+    "tsvm_select_working_set_static",
     "tsvm_local_smo", "tsvm_update_f", "tsvm_predict_dec", "tsvm_vote",
 ]
 
@@ -90,6 +91,7 @@ def lib():
     L.tsvm_ws_candidates.argtypes = [vp, i, i, vp, vp, vp, vp, d, d, i, i, vp, vp, vp]
     L.tsvm_ws_merge.argtypes = [vp, i, vp, vp, i, i, vp, vp]
     L.tsvm_select_working_set.argtypes = [vp, i, i, vp, vp, vp, vp, d, d, i, vp, vp]
+    L.tsvm_select_working_set_static.argtypes = [i, i, vp, vp, vp, vp, d, d, i, vp, vp]
     L.tsvm_local_smo.argtypes = [i, i, vp, vp, vp, vp, vp, vp, d, d, d, i, vp, vp]
     L.tsvm_update_f.argtypes = [vp, i, vp, i, vp, ll, vp]
     L.tsvm_predict_dec.argtypes = [vp, vp, C.POINTER(i), vp, i, i, vp, i, i, vp, vp, vp, ll, vp, sz, vp]
@@ -310,6 +312,16 @@ class WorkingSetSelector:
             self.close()
         except Exception:
             pass
+
+
+def select_working_set_static(f, alpha, y, Cp, Cn, want, in_ws=None, solver="c", out=None):
+    """tsvm_select_working_set_static: working-set selection that allocates nothing inside the library.
+    Pass a preallocated int32 `out` tensor to keep the Python side allocation-free as well."""
+    if out is None:
+        out = torch.empty(want, dtype=torch.int32, device="cuda")
+    check(lib().tsvm_select_working_set_static(SOLVERS[solver], f.numel(), _ptr(f), _ptr(alpha), _ptr(y),
+                                               _ptr(in_ws), Cp, Cn, want, _ptr(out), _stream()))
+    return out
 
 
 def local_smo(kww, diag_ws, y_ws, f_ws, alpha_ws, Cp, Cn, eps, max_iter=100000, solver="c"):

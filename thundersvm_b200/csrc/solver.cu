@@ -750,6 +750,59 @@ tsvm_status tsvm_select_working_set(tsvm_ws *w, int solver_kind, int n, const do
     return tsvm_ws_merge(w, solver_kind, w->cand_f, w->cand_id, want, want, out_ids_dev, stream);
 }
 
+// ---- working-set selection without any allocation --------------------------------------------------
+// Scratch of tsvm_select_working_set_static: the per-list selection state, the radix histograms, the
+// ticket / count words and the candidate lists for up to TSVM_STATIC_WS_MAX wanted ids and four
+// lists. It is a fixed part of the library image: every GPU that loads the library holds these
+// bytes until the process exits.
+constexpr int STATIC_WS_MAX = 1024;
+constexpr size_t STATIC_OFF_STATE = 0;                                                   // SelectState[4]
+constexpr size_t STATIC_OFF_HIST = 256;                                                  // int[4 * 4096]
+constexpr size_t STATIC_OFF_TICKET = STATIC_OFF_HIST + sizeof(int) * MAX_LISTS * RADIX_BINS;   // int
+constexpr size_t STATIC_OFF_COUNT = STATIC_OFF_TICKET + 128;                             // int
+constexpr size_t STATIC_OFF_CAND_F = STATIC_OFF_COUNT + 128;                             // double[4 * 1024]
+constexpr size_t STATIC_OFF_CAND_ID = STATIC_OFF_CAND_F + sizeof(double) * MAX_LISTS * STATIC_WS_MAX;
+constexpr size_t STATIC_SCRATCH_BYTES = STATIC_OFF_CAND_ID + sizeof(int) * MAX_LISTS * STATIC_WS_MAX;
+static_assert(sizeof(SelectState) * MAX_LISTS <= STATIC_OFF_HIST, "selection state does not fit its slot");
+static __device__ __align__(256) unsigned char g_static_select_scratch[STATIC_SCRATCH_BYTES];
+
+// In host code the array's name is only a stand-in for the symbol, not a device address: the address
+// is asked from the runtime once per device (with that device current) and remembered.
+constexpr int STATIC_MAX_DEVICES = 64;
+static unsigned char *g_static_scratch_addr[STATIC_MAX_DEVICES] = {nullptr};
+
+tsvm_status tsvm_select_working_set_static(int solver_kind, int n, const double *f_dev, const double *alpha_dev,
+                                           const int *y_dev, const unsigned char *in_ws_dev, double Cp, double Cn,
+                                           int want, int *out_ids_dev, void *stream) {
+    TSVM_REQUIRE(f_dev && alpha_dev && y_dev && out_ids_dev && n > 0 && want > 0 && solver_kind >= 0 &&
+                 solver_kind <= 2, "select_working_set_static: bad arguments");
+    TSVM_REQUIRE(want <= STATIC_WS_MAX,
+                 "select_working_set_static: %d ids wanted, the built-in scratch holds at most %d "
+                 "(use tsvm_select_working_set with a tsvm_ws for more)", want, STATIC_WS_MAX);
+    int dev = 0;
+    TSVM_CUDA(cudaGetDevice(&dev));
+    TSVM_REQUIRE(dev >= 0 && dev < STATIC_MAX_DEVICES, "select_working_set_static: device ordinal %d not supported", dev);
+    if (!g_static_scratch_addr[dev]) {
+        void *p = nullptr;
+        TSVM_CUDA(cudaGetSymbolAddress(&p, g_static_select_scratch));
+        g_static_scratch_addr[dev] = static_cast<unsigned char *>(p);
+    }
+    unsigned char *base = g_static_scratch_addr[dev];
+    tsvm_ws view;                      // a view over the static array; owns nothing, frees nothing
+    view.n_max = n;
+    view.ws_max = STATIC_WS_MAX;
+    view.state = reinterpret_cast<SelectState *>(base + STATIC_OFF_STATE);
+    view.hist = reinterpret_cast<int *>(base + STATIC_OFF_HIST);
+    view.ticket = reinterpret_cast<int *>(base + STATIC_OFF_TICKET);
+    view.count = reinterpret_cast<int *>(base + STATIC_OFF_COUNT);
+    view.cand_f = reinterpret_cast<double *>(base + STATIC_OFF_CAND_F);
+    view.cand_id = reinterpret_cast<int *>(base + STATIC_OFF_CAND_ID);
+    // select_init_kernel zeroes the state, histograms and ticket and fill_int_kernel resets the candidate
+    // ids on every call, so nothing of an earlier call's contents is read.
+    return tsvm_select_working_set(&view, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn, want,
+                                   out_ids_dev, stream);
+}
+
 tsvm_status tsvm_local_smo(int solver_kind, int ws_size, const float *kww_dev, const float *diag_ws_dev,
                            const int *y_ws_dev, const double *f_ws_dev, double *alpha_ws_dev, double *alpha_diff_dev,
                            double Cp, double Cn, double eps, int max_iter, double *diff_dev, void *stream) {
