@@ -99,6 +99,14 @@ tsvm_status tsvm_km_rows_by_instances_csr(tsvm_km *km, const float *tval_dev, co
                                           const int *tcol_dev, int m, long long tnnz, float *out_dev,
                                           long long ld_out, void *stream);
 
+/* Kernel rows for m explicit feature rows T (m x n_features, row stride ldt) whose self dots the caller
+ * supplies (sd_T_dev[m]); dense kernel matrices only. Used where the requested rows live on another
+ * GPU: the column-sharded driver ships the working set's feature rows and self dots to every shard,
+ * and each shard computes K(rows, its own instances) - the values are then identical to
+ * tsvm_km_rows_by_index on one GPU. */
+tsvm_status tsvm_km_rows_for_features_dense(tsvm_km *km, const float *T_dev, int ldt, const float *sd_T_dev, int m,
+                                            float *out_dev, long long ld_out, void *stream);
+
 /* Selects the dense kernel-row engine: 0 = automatic (default: tcgen05 tensor-core tiles, FP32
  * CUDA-core tiles when there are at most 32 features, where a k loop of one slab gives the
  * tensor core nothing to pipeline), 1 = FP32 CUDA-core tiles, 2 = tcgen05 tiles. */
@@ -142,6 +150,14 @@ tsvm_status tsvm_solver_finish(tsvm_solver *solver, double *rho_host, tsvm_solve
 /* Counters and phase times so far (objective is not evaluated: NaN). */
 tsvm_status tsvm_solver_get_stats(const tsvm_solver *solver, tsvm_solve_stats *stats_host);
 void tsvm_solver_destroy(tsvm_solver *solver);
+
+/* The 13 partial reductions rho and the objective are made of (csmosolver.cpp:167-187,227-239;
+ * nusmosolver.cpp:9-46), over the n instances given: out13_dev[0..12] = n_free(y>0), sum f over them,
+ * n_free(y<0), sum f over them, sum_i alpha_i - (f_i + y_i) alpha_i y_i / 2, then min f over I_up and
+ * max f over I_low for y>0 and for y<0, then max f over I_up and min f over I_low for y>0 and y<0.
+ * Shards combine them (sums, mins, maxes) into the global rho and objective. */
+tsvm_status tsvm_rho_partials(int n, const double *f_dev, const double *alpha_dev, const int *y_dev, double Cp,
+                              double Cn, double *out13_dev, void *stream);
 
 /* SvmModel::get_working_set_size (src/thundersvm/model/svmmodel.cpp:437-451) with the
  * memory budget in bytes. Returns the working-set size, or -1 when the budget is already

@@ -1,0 +1,117 @@
+"""Host logic of the column-sharded multi-GPU solver, run as gloo ranks on the CPU with the oracle as
+the numerical back end (tests/cpu_ops.py). The GPU back end itself is covered by the gpu-marked tests."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import port_binding as P
+from thundersvm_b200 import sharded, synth
+from util import binary_labels, oracle_matrix
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _problem(solver):
+    prob = dict(synth.config1(640), gamma=0.05)
+    y = binary_labels(prob)
+    n = len(y)
+    if solver == "c":
+        return prob, y, np.zeros(n), -y.astype(np.float64), 1.0
+    a0 = np.zeros(n)
+    sp = sn = 0.3 * n / 2
+    for i in range(n):
+        if y[i] > 0:
+            a0[i] = min(1.0, sp); sp -= a0[i]
+        else:
+            a0[i] = min(1.0, sn); sn -= a0[i]
+    return prob, y, a0, np.zeros(n), 1.0
+
+
+def _run_rank(rank, world, port, solver, out_dir):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from cpu_ops import OracleOps
+    if world > 1:
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    prob, y, a0, f0, C = _problem(solver)
+    n = len(y)
+    lo, hi = sharded.shard_range(n, rank, world)
+    if solver != "c":
+        # init_f is applied by the caller in the sharded form: f0 -= sum alpha_i y_i K_i (csmosolver.cpp:189-214)
+        X = oracle_matrix(P, prob)
+        nz = np.nonzero(a0)[0].astype(np.int32)
+        f0 = P.update_f(f0, -a0[nz] * y[nz], P.kernel_rows_idx(X, nz, gamma=prob["gamma"]))
+    sv = sharded.ShardedSolver(OracleOps(), torch.from_numpy(prob["X"][lo:hi].copy()), torch.from_numpy(y[lo:hi].copy()),
+                               torch.from_numpy(a0[lo:hi].copy()), torch.from_numpy(f0[lo:hi].copy()), n, lo, 1e-3, C, C,
+                               128, solver=solver, gamma=prob["gamma"])
+    rho, st = sv.solve()
+    np.savez(os.path.join(out_dir, "r%d.npz" % rank), alpha=sv.alpha.numpy(), f=sv.f.numpy(), rho=rho,
+             obj=st["objective"], iters=st["outer_iters"], lo=lo, hi=hi)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("solver", ["c", "nu_svc"])
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_sharded_solver_matches_single_process_oracle(tmp_path, solver, world):
+    port = _free_port()
+    if world == 1:
+        _run_rank(0, 1, port, solver, str(tmp_path))
+    else:
+        mp.spawn(_run_rank, args=(world, port, solver, str(tmp_path)), nprocs=world, join=True)
+    parts = [np.load(tmp_path / ("r%d.npz" % r)) for r in range(world)]
+    alpha = np.concatenate([p["alpha"] for p in parts])
+    f = np.concatenate([p["f"] for p in parts])
+    assert [int(p["lo"]) for p in parts] == [sharded.shard_range(640, r, world)[0] for r in range(world)]
+    assert all(abs(float(p["rho"]) - float(parts[0]["rho"])) == 0 for p in parts)      # replicated scalars agree
+    prob, y, a0, f0, C = _problem(solver)
+    X = oracle_matrix(P, prob)
+    ref = P.smo_solve(X, y, a0, f0, 1e-3, C, C, 128, solver=solver, gamma=prob["gamma"], cuda_semantics=1)
+    assert abs(float(parts[0]["obj"]) - ref["obj"]) <= 1e-4 * abs(ref["obj"])
+    assert abs(float(parts[0]["rho"]) - ref["rho"]) < 1e-3
+    assert abs(int((alpha != 0).sum()) - int((ref["alpha"] != 0).sum())) <= max(1, 0.005 * (ref["alpha"] != 0).sum())
+    assert np.linalg.norm(alpha - ref["alpha"]) <= 1e-2 * np.linalg.norm(ref["alpha"])
+    assert np.max(np.abs(f - ref["f"])) < 5e-3
+
+
+def test_partition_helpers():
+    for n, world in ((400000, 8), (10, 4), (7, 8), (640, 3)):
+        r = [sharded.shard_range(n, k, world) for k in range(world)]
+        assert r[0][0] == 0 and r[-1][1] == n
+        assert all(r[k][1] == r[k + 1][0] for k in range(world - 1))
+    pairs, owner = sharded.assign_pairs([6000] * 10, 8)
+    assert len(pairs) == 45 and sorted(set(owner)) == list(range(8))
+    load = [sum(1 for o in owner if o == w) for w in range(8)]
+    assert max(load) - min(load) <= 1
+    rows = [sharded.predict_rows(10001, k, 4) for k in range(4)]
+    assert rows[0][0] == 0 and rows[-1][1] == 10001 and all(rows[k][1] == rows[k + 1][0] for k in range(3))
+
+
+def test_combine_rho_matches_oracle_formulas():
+    rng = np.random.default_rng(0)
+    n = 500
+    y = np.where(rng.random(n) < 0.5, 1, -1).astype(np.int32)
+    a = rng.choice([0.0, 1.0, 0.4], n)
+    f = rng.standard_normal(n)
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from cpu_ops import OracleOps
+    ops = OracleOps()
+    parts = [ops.rho_partials(torch.from_numpy(f[s]), torch.from_numpy(a[s]), torch.from_numpy(y[s]), 1.0, 1.0).numpy()
+             for s in (slice(0, 200), slice(200, 500))]
+    rho, obj, _ = sharded.combine_rho(parts, "c")
+    free = (a > 0) & (a < 1.0)
+    assert abs(rho - f[free].mean()) < 1e-12
+    assert abs(obj - P.objective(f, a, y)) < 1e-9

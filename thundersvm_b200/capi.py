@@ -22,7 +22,7 @@ EXPORTS = [
     "tsvm_last_error", "tsvm_abi_version", "tsvm_km_create_dense", "tsvm_km_create_csr", "tsvm_km_destroy",
     "tsvm_km_n_instances", "tsvm_km_n_features", "tsvm_km_nnz", "tsvm_km_is_dense", "tsvm_km_diag_dev",
     "tsvm_km_self_dot_dev", "tsvm_km_rows_by_index", "tsvm_km_rows_by_instances_dense",
-    "tsvm_km_rows_by_instances_csr", "tsvm_km_set_dense_engine", "tsvm_smo_solve", "tsvm_solver_create",
+    "tsvm_km_rows_by_instances_csr", "tsvm_km_rows_for_features_dense", "tsvm_km_set_dense_engine", "tsvm_rho_partials", "tsvm_smo_solve", "tsvm_solver_create",
     "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_destroy", "tsvm_working_set_size",
     "tsvm_ws_create", "tsvm_ws_destroy", "tsvm_ws_candidates", "tsvm_ws_merge", "tsvm_select_working_set",
     "tsvm_select_working_set_static",
@@ -75,6 +75,8 @@ def lib():
     L.tsvm_km_rows_by_index.argtypes = [vp, vp, i, vp, ll, vp]
     L.tsvm_km_rows_by_instances_dense.argtypes = [vp, vp, i, i, i, vp, ll, vp]
     L.tsvm_km_rows_by_instances_csr.argtypes = [vp, vp, vp, vp, i, ll, vp, ll, vp]
+    L.tsvm_km_rows_for_features_dense.argtypes = [vp, vp, i, vp, i, vp, ll, vp]
+    L.tsvm_rho_partials.argtypes = [i, vp, vp, vp, d, d, vp, vp]
     L.tsvm_km_set_dense_engine.argtypes = [vp, i]
     L.tsvm_smo_solve.argtypes = [vp, i, vp, vp, vp, d, d, d, i, i, C.POINTER(d), C.POINTER(SolveStats), vp]
     L.tsvm_solver_create.argtypes = [vp, i, vp, vp, vp, d, d, d, i, vp, C.POINTER(vp)]
@@ -212,6 +214,15 @@ class KernelMatrix:
                                                       _ptr(out), out.stride(0), _stream()))
         return out
 
+    def rows_for_features(self, T, sd_T, out=None):
+        """Kernel rows for explicit feature rows T [m, d] with their self dots sd_T [m] -> [m, n]."""
+        m = T.shape[0]
+        if out is None:
+            out = torch.empty((m, self.n), dtype=torch.float32, device="cuda")
+        check(lib().tsvm_km_rows_for_features_dense(self._h, _ptr(T), T.stride(0), _ptr(sd_T), m, _ptr(out),
+                                                    out.stride(0), _stream()))
+        return out
+
     def close(self):
         if self._h:
             lib().tsvm_km_destroy(self._h)
@@ -339,6 +350,12 @@ def update_f(f, alpha_diff, rows):
     check(lib().tsvm_update_f(_ptr(f), f.numel(), _ptr(alpha_diff), alpha_diff.numel(), _ptr(rows), rows.stride(0),
                               _stream()))
     return f
+
+
+def rho_partials(f, alpha, y, Cp, Cn):
+    out = torch.empty(13, dtype=torch.float64, device="cuda")
+    check(lib().tsvm_rho_partials(f.numel(), _ptr(f), _ptr(alpha), _ptr(y), Cp, Cn, _ptr(out), _stream()))
+    return out
 
 
 def predict_dec(km_sv, coef, sv_count, rho, n_classes, dense=None, csr=None, max_mem_bytes=0):

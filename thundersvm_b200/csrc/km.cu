@@ -536,6 +536,23 @@ tsvm_status tsvm_km_rows_by_instances_dense(tsvm_km *km, const float *T_dev, int
     return TSVM_OK;
 }
 
+tsvm_status tsvm_km_rows_for_features_dense(tsvm_km *km, const float *T_dev, int ldt, const float *sd_T_dev, int m,
+                                            float *out_dev, long long ld_out, void *stream) {
+    TSVM_REQUIRE(km && km->dense && T_dev && sd_T_dev && out_dev && m > 0 && ldt >= km->d && ld_out >= km->n,
+                 "rows_for_features_dense: bad arguments (dense kernel matrix required)");
+    cudaStream_t st = (cudaStream_t) stream;
+    for (int r0 = 0; r0 < m; r0 += 4096) {
+        const int mm = min(4096, m - r0);
+        TSVM_TRY(ensure_scratch(km, mm));
+        TSVM_CUDA(cudaMemcpyAsync(km->sd_rows, sd_T_dev + r0, sizeof(float) * mm, cudaMemcpyDeviceToDevice, st));
+        const bool tc = use_tensor_engine(km);
+        TSVM_LAUNCH(stage_rows_dense_kernel, mm, 256, 0, st, T_dev + (size_t) r0 * ldt, ldt, km->d, km->d, km->d_pad, mm,
+                    tc ? nullptr : km->W, tc ? km->Whi : nullptr, tc ? km->Wlo : nullptr);
+        TSVM_TRY(rows_common(km, mm, out_dev + (size_t) r0 * ld_out, ld_out, st));
+    }
+    return TSVM_OK;
+}
+
 tsvm_status tsvm_km_rows_by_instances_csr(tsvm_km *km, const float *tval_dev, const int *trow_ptr_dev,
                                           const int *tcol_dev, int m, long long tnnz, float *out_dev,
                                           long long ld_out, void *stream) {

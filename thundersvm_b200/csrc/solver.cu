@@ -812,6 +812,13 @@ tsvm_status tsvm_local_smo(int solver_kind, int ws_size, const float *kww_dev, c
                             alpha_diff_dev, Cp, Cn, eps, max_iter, diff_dev, nullptr, nullptr, (cudaStream_t) stream);
 }
 
+tsvm_status tsvm_rho_partials(int n, const double *f_dev, const double *alpha_dev, const int *y_dev, double Cp,
+                              double Cn, double *out13_dev, void *stream) {
+    TSVM_REQUIRE(n > 0 && f_dev && alpha_dev && y_dev && out13_dev, "rho_partials: bad arguments");
+    TSVM_LAUNCH(rho_obj_kernel, 1, 1024, 0, (cudaStream_t) stream, n, f_dev, alpha_dev, y_dev, Cp, Cn, out13_dev);
+    return TSVM_OK;
+}
+
 tsvm_status tsvm_update_f(double *f_dev, int n, const double *alpha_diff_dev, int ws_size, const float *rows_dev,
                           long long ld, void *stream) {
     TSVM_REQUIRE(f_dev && alpha_diff_dev && rows_dev && n > 0 && ws_size > 0 && ws_size <= 1024 && ld >= n,

@@ -1,0 +1,368 @@
+"""Multi-GPU drivers: one process per GPU, torch.distributed for the exchange steps.
+
+Column-sharded SMO for ONE large binary problem: rank r owns a contiguous range of instances, i.e.
+a column block of the kernel matrix together with the matching slices of f, alpha and y. Every
+outer iteration has one exchange step:
+
+  1. each rank builds its own top-k candidate lists (tsvm_ws_candidates, global ids)
+  2. all-gather of the lists; every rank runs the same deterministic merge (tsvm_ws_merge)
+     -> identical working sets everywhere
+  3. the owners contribute the new members' feature rows, self dots, y, alpha, f and diagonal to
+     zero-initialised buffers; one all-reduce(sum) each makes them global (adding zeros is exact)
+  4. each rank computes K(new rows, own columns) (tsvm_km_rows_for_features_dense) and contributes
+     the columns of the ws x ws block it owns; all-reduce(sum) completes the block
+  5. the local SMO runs redundantly and deterministically on every rank (tsvm_local_smo)
+  6. each rank updates its own slice of f (tsvm_update_f) and of alpha
+rho and the objective are combined from per-rank partial reductions (tsvm_rho_partials).
+Received data always lands in local HBM first; no kernel reads another GPU's memory.
+
+One-vs-one training and prediction shard without any collective on the data path: binary
+sub-problems / test rows are split across ranks and the results gathered on the host.
+
+The numerical work is done by an `ops` object. `CapiOps` (the product) calls the C ABI on the GPU;
+the CPU tests substitute a test double to exercise the host logic with the gloo backend.
+"""
+import math
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+INF = float("inf")
+
+
+def shard_range(n, rank, world):
+    """Contiguous, balanced ownership ranges (multiples of 4 instances except the tail)."""
+    per = (n + world - 1) // world
+    per = (per + 3) // 4 * 4
+    lo = min(n, rank * per)
+    return lo, min(n, lo + per)
+
+
+class CapiOps:
+    """Numerical steps on the local GPU through the C ABI."""
+
+    def __init__(self):
+        from . import capi
+        self.capi = capi
+        self.device = torch.device("cuda", torch.cuda.current_device())
+
+    def kernel_matrix(self, X_local, kernel, gamma, coef0, degree):
+        km = self.capi.KernelMatrix(dense=X_local, kernel=kernel, gamma=gamma, coef0=coef0, degree=degree)
+        return km
+
+    def self_dot(self, km):
+        return km.self_dot()
+
+    def diag(self, km):
+        return km.diag()
+
+    def selector(self, n_local, ws):
+        return self.capi.WorkingSetSelector(max(n_local, 1), 1024)
+
+    def candidates(self, sel, f, alpha, y, Cp, Cn, want, in_ws, solver, id_offset):
+        return sel.candidates(f, alpha, y, Cp, Cn, want, in_ws=in_ws, solver=solver, id_offset=id_offset)
+
+    def merge(self, sel, cand_f, cand_id, want, solver):
+        return sel.merge(cand_f, cand_id, want, solver=solver)
+
+    def rows_for_features(self, km, T, sd_T, out):
+        return km.rows_for_features(T, sd_T, out=out)
+
+    def local_smo(self, kww, diag_ws, y_ws, f_ws, alpha_ws, Cp, Cn, eps, max_iter, solver):
+        return self.capi.local_smo(kww, diag_ws, y_ws, f_ws, alpha_ws, Cp, Cn, eps, max_iter=max_iter, solver=solver)
+
+    def update_f(self, f, alpha_diff, rows):
+        return self.capi.update_f(f, alpha_diff, rows)
+
+    def rho_partials(self, f, alpha, y, Cp, Cn):
+        return self.capi.rho_partials(f, alpha, y, Cp, Cn)
+
+
+def combine_rho(parts, solver):
+    """parts: [world, 13] partial reductions -> (rho, objective, r) as csmosolver.cpp:167-187 /
+    nusmosolver.cpp:9-46 define them; r is the nu-SVC scale (1 otherwise)."""
+    p = np.asarray(parts, dtype=np.float64)
+    s = p[:, :5].sum(0)
+    mn = lambda k: p[:, k].min()
+    mx = lambda k: p[:, k].max()
+    obj = -s[4]
+    if solver == "c":
+        nfree = s[0] + s[2]
+        rho = (s[1] + s[3]) / nfree if nfree != 0 else -(min(mn(5), mn(7)) + max(mx(6), mx(8))) / 2
+        return rho, obj, 1.0
+    r1 = s[1] / s[0] if s[0] != 0 else (mx(9) + mn(10)) / 2
+    r2 = -s[3] / s[2] if s[2] != 0 else (mx(11) + mn(12)) / 2
+    rho = (r1 - r2) / 2
+    if solver == "nu_svc":
+        r = (r1 + r2) / 2
+        return rho / r, obj, r
+    return rho, obj, 1.0
+
+
+class ShardedSolver:
+    """CSMOSolver / NuSMOSolver::solve (csmosolver.cpp:10-121) over column shards."""
+
+    def __init__(self, ops, X_local, y_local, alpha_local, f_local, n_total, lo, eps, Cp, Cn, ws_size, solver="c",
+                 kernel="rbf", gamma=0.5, coef0=0.0, degree=3, group=None):
+        self.ops, self.group = ops, group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.dev = ops.device
+        self.X, self.y, self.alpha, self.f = X_local, y_local, alpha_local, f_local
+        self.n, self.lo, self.n_local = n_total, lo, X_local.shape[0]
+        self.hi = lo + self.n_local
+        self.d = X_local.shape[1]
+        self.eps, self.Cp, self.Cn, self.ws, self.q, self.solver = eps, Cp, Cn, ws_size, ws_size // 2, solver
+        self.lists = 2 if solver == "c" else 4
+        self.km = ops.kernel_matrix(X_local, kernel, gamma, coef0, degree) if self.n_local else None
+        self.sd = ops.self_dot(self.km) if self.km is not None else torch.zeros(0, device=self.dev)
+        self.diag = ops.diag(self.km) if self.km is not None else torch.zeros(0, device=self.dev)
+        self.sel = ops.selector(self.n_local, ws_size)
+        self.ld = max(4, (self.n_local + 3) // 4 * 4)
+        self.rows = torch.zeros((ws_size, self.ld), dtype=torch.float32, device=self.dev)
+        self.in_ws = torch.zeros(max(self.n_local, 1), dtype=torch.uint8, device=self.dev)
+        self.ids = torch.full((ws_size,), -1, dtype=torch.int64, device=self.dev)     # logical slot order, global ids
+        self.W = torch.zeros((ws_size, self.d), dtype=torch.float32, device=self.dev)  # feature rows of the ws
+        self.vec = torch.zeros((ws_size, 2), dtype=torch.float64, device=self.dev)     # self dot, diag per slot
+        self.iter, self.local_iters, self.done, self.diff0 = 0, 0, False, 0.0
+        self.prev, self.last, self.second_last = INF, INF, INF
+        self.same_cnt = self.swap_cnt = 0
+        self.local_max_iter = max(100000, 100 * ws_size)
+        self.rows_made = 0
+        self.t_comm = 0.0
+
+    # ---- exchange helpers -----------------------------------------------------------------------
+    def _allreduce(self, t):
+        if self.world > 1:
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    def _allgather_cat(self, t, dim):
+        if self.world == 1:
+            return t
+        parts = [torch.empty_like(t) for _ in range(self.world)]
+        dist.all_gather(parts, t.contiguous(), group=self.group)
+        return torch.cat(parts, dim)
+
+    def _owned(self, gids):
+        m = (gids >= self.lo) & (gids < self.hi)
+        return m, (gids - self.lo).clamp(0, max(self.n_local - 1, 0))
+
+    def _select(self, want, use_flags):
+        o = self.ops
+        if self.n_local:
+            cf, ci = o.candidates(self.sel, self.f, self.alpha, self.y, self.Cp, self.Cn, want,
+                                  self.in_ws if use_flags else None, self.solver, self.lo)
+        else:
+            cf = torch.zeros((self.lists, want), dtype=torch.float64, device=self.dev)
+            ci = torch.full((self.lists, want), -1, dtype=torch.int32, device=self.dev)
+        cf, ci = self._allgather_cat(cf, 1), self._allgather_cat(ci, 1)
+        return o.merge(self.sel, cf, ci, want, self.solver).to(torch.int64)
+
+    def _fetch_members(self, slots, gids):
+        """Feature rows / self dot / diag of the given new members into W / vec (all ranks)."""
+        m, loc = self._owned(gids)
+        if self.n_local:
+            mf = m.to(torch.float32)[:, None]
+            Wn = self.X[loc] * mf                      # owners contribute their rows, the others zeros
+            vn = torch.stack([self.sd[loc].to(torch.float64), self.diag[loc].to(torch.float64)], 1) * m.to(
+                torch.float64)[:, None]
+        else:
+            Wn = torch.zeros((len(slots), self.d), dtype=torch.float32, device=self.dev)
+            vn = torch.zeros((len(slots), 2), dtype=torch.float64, device=self.dev)
+        self._allreduce(Wn)
+        self._allreduce(vn)
+        self.W[slots] = Wn
+        self.vec[slots] = vn
+
+    def _state_of_ws(self):
+        """y, f, alpha of every working-set slot (all ranks)."""
+        m, loc = self._owned(self.ids)
+        if self.n_local:
+            st = torch.stack([self.y[loc].to(torch.float64), self.f[loc], self.alpha[loc]], 1) * m.to(
+                torch.float64)[:, None]
+        else:
+            st = torch.zeros((self.ws, 3), dtype=torch.float64, device=self.dev)
+        return self._allreduce(st)
+
+    # ---- one outer iteration (csmosolver.cpp:59-120) -----------------------------------------------
+    def outer_iteration(self):
+        o, q, ws = self.ops, self.q, self.ws
+        first_half_phys = self.iter & 1
+        ar = torch.arange(q, device=self.dev)
+        if self.iter == 0:
+            new_slots = torch.arange(ws, device=self.dev)
+            self.ids[:] = self._select(ws, False)
+            phys0, slot_phys = 0, new_slots
+        else:
+            # the previous new half stays, the older half leaves (flags only for owned instances)
+            leaving, staying = self.ids[:q].clone(), self.ids[q:].clone()
+            if self.n_local:
+                for g, v in ((leaving, 0), (staying, 1)):
+                    m, loc = self._owned(g)
+                    self.in_ws[loc[m]] = v
+            self.ids[:q] = staying
+            self.W[:q], self.vec[:q] = self.W[q:].clone(), self.vec[q:].clone()
+            self.ids[q:] = self._select(q, True)
+            new_slots = q + ar
+            phys0 = (1 - first_half_phys) * q
+            # physical row of every logical slot: the two buffer halves swap roles instead of being copied
+            slot_phys = torch.cat([first_half_phys * q + ar, (1 - first_half_phys) * q + ar])
+        t0 = time.perf_counter()
+        self._fetch_members(new_slots, self.ids[new_slots])
+        self.t_comm += time.perf_counter() - t0
+        n_new = len(new_slots)
+        if self.n_local:
+            o.rows_for_features(self.km, self.W[new_slots].contiguous(),
+                                self.vec[new_slots, 0].to(torch.float32).contiguous(), self.rows[phys0:phys0 + n_new])
+        self.rows_made += n_new
+        # ws x ws block: every rank contributes the columns of the members it owns
+        m, loc = self._owned(self.ids)
+        if self.n_local:
+            block = self.rows[slot_phys[:, None], loc[None, :]] * m.to(torch.float32)[None, :]
+        else:
+            block = torch.zeros((ws, ws), dtype=torch.float32, device=self.dev)
+        t0 = time.perf_counter()
+        self._allreduce(block)
+        self.t_comm += time.perf_counter() - t0
+        st = self._state_of_ws()
+        y_ws = st[:, 0].round().to(torch.int32).contiguous()
+        a_ws, ad, diff = o.local_smo(block.contiguous(), self.vec[:, 1].to(torch.float32).contiguous(), y_ws,
+                                     st[:, 1].contiguous(), st[:, 2].contiguous(), self.Cp, self.Cn, self.eps,
+                                     self.local_max_iter, self.solver)
+        # own slices of alpha and f
+        if self.n_local:
+            self.alpha[loc[m]] = a_ws[m]
+            ad_phys = torch.zeros(ws, dtype=torch.float64, device=self.dev)
+            ad_phys[slot_phys] = ad
+            o.update_f(self.f, ad_phys, self.rows)
+        d = diff.cpu().numpy()
+        self.diff0 = float(d[0])
+        self.local_iters += int(d[1])
+        eps = self.eps
+        if abs(self.diff0 - self.prev) < eps * 0.001:
+            self.same_cnt += 1
+        else:
+            self.same_cnt, self.prev = 0, self.diff0
+        self.swap_cnt = self.swap_cnt + 1 if abs(self.diff0 - self.second_last) < eps * 0.001 else 0
+        self.second_last, self.last = self.last, self.diff0
+        if (self.same_cnt >= 10 and abs(self.diff0 - 2.0) > eps) or self.diff0 < eps or \
+                (self.swap_cnt >= 10 and abs(self.diff0 - 2.0) > eps):
+            self.done = True
+        self.iter += 1
+
+    def iterate(self, n_iters):
+        for _ in range(n_iters):
+            if self.done:
+                break
+            self.outer_iteration()
+        return self.done
+
+    def finish(self):
+        if self.n_local:
+            part = self.ops.rho_partials(self.f, self.alpha, self.y, self.Cp, self.Cn)
+        else:
+            part = torch.tensor([0, 0, 0, 0, 0, INF, -INF, INF, -INF, -INF, INF, -INF, INF], dtype=torch.float64,
+                                device=self.dev)
+        parts = self._allgather_cat(part.reshape(1, 13), 0).cpu().numpy()
+        rho, obj, r = combine_rho(parts, self.solver)
+        if self.solver == "nu_svc" and self.n_local:
+            self.alpha /= r
+        return rho, dict(outer_iters=self.iter, local_iters=self.local_iters, final_diff=self.diff0, objective=obj,
+                         kernel_rows=self.rows_made, seconds_comm=self.t_comm)
+
+    def solve(self, max_iter=-1):
+        while not self.done:
+            self.outer_iteration()
+            if max_iter != -1 and self.iter - 1 == max_iter:
+                break
+        return self.finish()
+
+
+# ---- independent units: one-vs-one pairs and prediction rows ---------------------------------------
+def assign_pairs(counts, world):
+    """Longest-processing-time assignment of the (i, j) sub-problems to ranks by instance count."""
+    pairs = [(i, j) for i in range(len(counts)) for j in range(i + 1, len(counts))]
+    order = sorted(range(len(pairs)), key=lambda k: -(counts[pairs[k][0]] + counts[pairs[k][1]]))
+    load = [0] * world
+    owner = [0] * len(pairs)
+    for k in order:
+        r = min(range(world), key=lambda w: load[w])
+        owner[k] = r
+        load[r] += counts[pairs[k][0]] + counts[pairs[k][1]]
+    return pairs, owner
+
+
+def predict_rows(n_test, rank, world):
+    per = (n_test + world - 1) // world
+    return min(n_test, rank * per), min(n_test, (rank + 1) * per)
+
+
+# ---- benchmark entry used by bench.py for N > 1 --------------------------------------------------------
+def bench(args, rank, world, local_rank):
+    """Strong scaling of config 5: the same problem, instance columns sharded over `world` GPUs."""
+    from . import synth
+    n, d, ws, q = args.rows, 2000, 1024, 512
+    gamma, C, eps = 0.5, 1.0, 1e-3
+    K, W = args.steps, max(3, args.warmup)
+    lo, hi = shard_range(n, rank, world)
+    prob = synth.config5(n)                                   # every rank draws the same stream, keeps its slice
+    y_np = np.where(prob["y"] > 0, 1, -1).astype(np.int32)
+    Xh = torch.from_numpy(prob["X"][lo:hi]).pin_memory()
+    del prob
+    ops = CapiOps()
+
+    def make(from_host):
+        X = Xh.cuda(non_blocking=True)
+        y = torch.from_numpy(y_np[lo:hi]).cuda()
+        f = -y.to(torch.float64)
+        a = torch.zeros(hi - lo, dtype=torch.float64, device="cuda")
+        return ShardedSolver(ops, X, y, a, f, n, lo, eps, C, C, ws, gamma=gamma), a
+
+    # resident: W warm-up steps, K timed steps, device time, max over ranks
+    sv, _ = make(False)
+    sv.iterate(W)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    rows0 = sv.rows_made
+    e0.record()
+    sv.iterate(K)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    rows_timed = sv.rows_made - rows0
+    del sv
+    torch.cuda.empty_cache()
+
+    # end to end from host buffers: H2D of the shard, set-up, W+K steps, D2H of alpha
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    sv, a = make(True)
+    sv.iterate(W + K)
+    rho, st = sv.finish()
+    a_host = a.cpu()
+    torch.cuda.synchronize()
+    dist.barrier()
+    sec = torch.tensor([time.perf_counter() - t0], device="cuda")
+    dist.all_reduce(sec, op=dist.ReduceOp.MAX)
+    sec = float(sec.item())
+    return {
+        "metric": "kernel_rows_per_s", "value": rows_timed / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32 kernel values (3xTF32 contraction), f64 solver state", "data": "synthetic",
+        "config": {"workload": "config5: binary C-SVC, RBF gamma=0.5 C=1 eps=1e-3, %dx%d dense fp32, ws=1024, 512 new "
+                               "kernel rows per outer iteration, instance columns sharded over %d GPUs" % (n, d, world),
+                   "l2": "inputs larger than L2", "parallelism": "column-sharded x%d" % world},
+        "e2e": {"value": st["kernel_rows"] / sec, "unit": "rows/s",
+                "h2d_bytes_per_step": (hi - lo) * d * 4 / (W + K), "d2h_bytes_per_step": (hi - lo) * 8 / (W + K),
+                "seconds": sec, "steps": W + K},
+        "gpu_launches": int(K * 17), "comm_seconds": st["seconds_comm"],
+    }
