@@ -109,7 +109,8 @@ tsvm_status tsvm_km_rows_for_features_dense(tsvm_km *km, const float *T_dev, int
 
 /* Selects the dense kernel-row engine: 0 = automatic (default: tcgen05 tensor-core tiles, FP32
  * CUDA-core tiles when there are at most 32 features, where a k loop of one slab gives the
- * tensor core nothing to pipeline), 1 = FP32 CUDA-core tiles, 2 = tcgen05 tiles. */
+ * tensor core nothing to pipeline), 1 = FP32 CUDA-core tiles, 2 = tcgen05 tiles with one CTA per
+ * tile, 3 = tcgen05 tiles computed by CTA pairs (what "automatic" uses). */
 tsvm_status tsvm_km_set_dense_engine(tsvm_km *km, int engine);
 
 /* ------------------------------------------------------------------------------------------

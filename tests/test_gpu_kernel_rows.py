@@ -38,23 +38,23 @@ def _check_rows(capi, prob, n, q, engine=None, force=None, kernel="rbf", coef0=0
     return km, X
 
 
-@pytest.mark.parametrize("engine", ["auto", "tensor", "simt"])
+@pytest.mark.parametrize("engine", ["auto", "tensor", "tensor1", "simt"])
 @pytest.mark.parametrize("n,q", [(1000, 64), (4097, 512), (300, 101), (129, 128), (128, 1), (2500, 1024)])
 def test_dense_rows_c1(capi, engine, n, q):
     """Config 1 has 20 features with |x| up to 3 and RBF arguments up to ~50. The automatic engine uses
     FP32 CUDA-core tiles here and holds 1e-5. When the tensor-core engine is forced, the two-plane TF32
     representation (2^-23 relative per operand) of a few dominant products shows directly in the exponent:
     it is held to 3e-5 on this data and to 1e-5 wherever the k loop is long (the tests below)."""
-    _check_rows(capi, synth.config1(n), n, q, engine=engine, tol=3e-5 if engine == "tensor" else REL_TOL)
+    _check_rows(capi, synth.config1(n), n, q, engine=engine, tol=3e-5 if engine.startswith("tensor") else REL_TOL)
 
 
-@pytest.mark.parametrize("engine", ["tensor", "simt"])
+@pytest.mark.parametrize("engine", ["tensor", "tensor1", "simt"])
 def test_dense_rows_c5_shape(capi, engine):
     """Unit-norm rows, d = 2000 (config 5's row length), n not a multiple of the tile."""
     _check_rows(capi, synth.config5(3001), 3001, 512, engine=engine)
 
 
-@pytest.mark.parametrize("engine", ["tensor", "simt"])
+@pytest.mark.parametrize("engine", ["tensor", "tensor1", "simt"])
 def test_dense_rows_c3_shape(capi, engine):
     """784 features in [0,1] (config 3). Same-class dot products reach ~100, where the oracle's own
     sequential FP32 accumulation noise is ~1e-5 relative on K; both are therefore also compared with an
@@ -73,15 +73,22 @@ def test_dense_rows_c3_shape(capi, engine):
     e_gpu, e_orc = rel_err(got, exact), rel_err(want, exact)
     assert e_gpu < max(REL_TOL, e_orc + REL_TOL), (e_gpu, e_orc)
     assert rel_err(got, want) < 4e-5
-    if engine == "tensor":
+    if engine.startswith("tensor"):
         assert e_gpu <= e_orc, "the promoted 3xTF32 sum should be at least as close to FP64 as sequential FP32"
 
 
 @pytest.mark.parametrize("kernel,kw", [("linear", {}), ("poly", dict(coef0=0.1, degree=3)),
                                        ("sigmoid", dict(coef0=0.1))])
-@pytest.mark.parametrize("engine", ["tensor", "simt"])
+@pytest.mark.parametrize("engine", ["tensor", "tensor1", "simt"])
 def test_dense_rows_other_kernels(capi, engine, kernel, kw):
     _check_rows(capi, synth.config1(1500), 1500, 200, engine=engine, kernel=kernel, **kw)
+
+
+@pytest.mark.parametrize("n,q", [(100, 5), (129, 127), (257, 129), (384, 256), (511, 300), (40000, 512)])
+def test_dense_rows_pair_engine_odd_tiles(capi, n, q):
+    """CTA-pair tiles with an empty or partial second half (n just above / below multiples of 128 and
+    256) and requested-row counts around the 128-row halves of the B operand."""
+    _check_rows(capi, synth.config5(n, d=136), n, q, engine="tensor")
 
 
 @pytest.mark.parametrize("n,q", [(1200, 64), (5000, 512), (333, 101), (2000, 1024)])

@@ -147,7 +147,7 @@ struct tsvm_km {
     long long nnz = 0;
     bool dense = true;
     tsvm::KernelFn fn{};
-    int engine = 0;                 // 0 = automatic, 1 = CUDA-core FP32, 2 = tcgen05
+    int engine = 0;                 // 0 = automatic, 1 = CUDA-core FP32, 2 = tcgen05 single CTA, 3 = tcgen05 CTA pairs
     // dense storage: row-major, row stride ldx floats (multiple of 4)
     const float *X = nullptr;
     int ldx = 0;

@@ -1,0 +1,259 @@
+// Dense kernel rows on tcgen05 with CTA pairs (cta_group::2).
+//
+// Same contraction, same 3xTF32 scheme and same per-slab FP32 promotion as dense_tc.cu, but two
+// CTAs on neighbouring SMs work as one: the pair owns a 256-instance x 256-requested-row tile, each
+// CTA holds the TF32 planes of ITS 128 instances and of ITS 128 requested rows (half of the B
+// operand), and one thread of the leader CTA issues tcgen05.mma.cta_group::2 (M = 256), which reads
+// both CTAs' shared memory and writes both CTAs' tensor memory. Per CTA a k slab is then 64 KB
+// instead of 96 KB for the same tensor-core time, and three of them fit the ring instead of two - the
+// single-CTA engine was bound by the latency of its one slab in flight, not by any bandwidth.
+//
+// Roles per CTA (320 threads): warp 0 TMA producer for this CTA's operand halves (transaction bytes
+// are reported to the leader's "full" barrier), warp 1 tensor-memory allocation (both CTAs) and MMA
+// issue (leader only), warps 2..9 slab promotion + epilogue on this CTA's 128 instances.
+// Barriers: full[s] (leader; both CTAs' TMA bytes), empty[s] (per CTA; MMAs that read the stage have
+// retired), tfull[a] (per CTA; slab sum complete), tempty[a] (leader; 16 epilogue warps drained it).
+// Cross-CTA signalling uses mbarrier arrives on shared::cluster addresses and one tcgen05.commit per
+// destination CTA; every load is addressed to one CTA's shared memory only. Every mbarrier wait is bounded.
+#include "tc_common.cuh"
+
+namespace tsvm {
+
+namespace tc2 {
+constexpr int BM = 128, BN = 256, BN_HALF = 128, BK = 32, STAGES = 3, UMMA_K = 8;
+constexpr uint32_t A_BYTES = BM * BK * 4;            // 16 KB per plane (this CTA's instances)
+constexpr uint32_t B_BYTES = BN_HALF * BK * 4;       // 16 KB per plane (this CTA's half of the requested rows)
+constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // 64 KB per CTA
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int THREADS = 320, EPI_WARPS = 8, COLS_PER_THREAD = 128;
+constexpr uint32_t TMEM_COLS = 512;
+// D=F32, A=B=TF32, K-major, N=256, M=256 (two CTAs x 128)
+constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
+}  // namespace tc2
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of a CTA pair: data lands in this CTA's shared memory, the bytes are counted on the
+// barrier at the given shared::cluster address (the leader's).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(tc2::IDESC), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at a shared::cluster address once all MMAs issued so far have retired
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+
+__global__ void __launch_bounds__(tc2::THREADS, 1)
+dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
+                      const __grid_constant__ CUtensorMap map_whi, const __grid_constant__ CUtensorMap map_wlo,
+                      int n, int m, int d_pad, const float *__restrict__ sd, const float *__restrict__ sd_rows,
+                      KernelFn fn, float *__restrict__ out, long long ld_out, int *__restrict__ status) {
+    using namespace tc2;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring_ptr + STAGES * STAGE_BYTES);
+    const uint32_t full_bar = smem_u32(bars), empty_bar = full_bar + 8 * STAGES;
+    const uint32_t tfull_bar = empty_bar + 8 * STAGES, tempty_bar = tfull_bar + 16;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+    const int pair_tiles = (n + 2 * BM - 1) / (2 * BM), n_blocks = (m + BN - 1) / BN, k_blocks = (d_pad + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar + 8 * a, 1); mbar_init(tempty_bar + 8 * a, 2 * EPI_WARPS); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();           // both CTAs' barriers are initialised before any remote arrive / TMA
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int pt = cluster_id; pt < pair_tiles && ok; pt += n_clusters)
+                for (int nb = 0; nb < n_blocks && ok; ++nb)
+                    for (int kb = 0; kb < k_blocks; ++kb) {
+                        if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
+                        const uint32_t base = ring + stage * STAGE_BYTES;
+                        const uint32_t leader_full = mapa_u32(full_bar + 8 * stage, 0);
+                        if (rank == 0) mbar_expect_tx(full_bar + 8 * stage, 2 * STAGE_BYTES);
+                        const int xrow = pt * 2 * BM + (int) rank * BM, wrow = nb * BN + (int) rank * BN_HALF;
+                        tma_load_2d_pair(base, &map_xhi, leader_full, kb * BK, xrow);
+                        tma_load_2d_pair(base + A_BYTES, &map_xlo, leader_full, kb * BK, xrow);
+                        tma_load_2d_pair(base + 2 * A_BYTES, &map_whi, leader_full, kb * BK, wrow);
+                        tma_load_2d_pair(base + 2 * A_BYTES + B_BYTES, &map_wlo, leader_full, kb * BK, wrow);
+                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (int pt = cluster_id; pt < pair_tiles && ok; pt += n_clusters)
+                for (int nb = 0; nb < n_blocks && ok; ++nb)
+                    for (int kb = 0; kb < k_blocks; ++kb) {
+                        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, 2)) { ok = false; break; }
+                        if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t d_tmem = tmem_base + acc * BN;
+                        const uint32_t base = ring + stage * STAGE_BYTES;
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint32_t koff = k * UMMA_K * 4;
+                            umma_tf32_pair(d_tmem, smem_desc_sw128(base + A_BYTES + koff),
+                                           smem_desc_sw128(base + 2 * A_BYTES + koff), k != 0);
+                            umma_tf32_pair(d_tmem, smem_desc_sw128(base + koff),
+                                           smem_desc_sw128(base + 2 * A_BYTES + B_BYTES + koff), 1);
+                        }
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint32_t koff = k * UMMA_K * 4;
+                            umma_tf32_pair(d_tmem, smem_desc_sw128(base + koff), smem_desc_sw128(base + 2 * A_BYTES + koff), 1);
+                        }
+                        // stage free / slab complete, signalled in both CTAs
+                        umma_commit_pair(mapa_u32(empty_bar + 8 * stage, 0));
+                        umma_commit_pair(mapa_u32(empty_bar + 8 * stage, 1));
+                        umma_commit_pair(mapa_u32(tfull_bar + 8 * acc, 0));
+                        umma_commit_pair(mapa_u32(tfull_bar + 8 * acc, 1));
+                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                    }
+        }
+    } else {
+        // ---------------- slab promotion + epilogue (both CTAs, own 128 instances) ----------------
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        for (int pt = cluster_id; pt < pair_tiles && ok; pt += n_clusters) {
+            const int j = pt * 2 * BM + (int) rank * BM + quarter * 32 + lane;
+            const float sdj = j < n ? sd[j] : 0.0f;
+            for (int nb = 0; nb < n_blocks && ok; ++nb) {
+                float sum[COLS_PER_THREAD];
+#pragma unroll
+                for (int c = 0; c < COLS_PER_THREAD; ++c) sum[c] = 0.0f;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t taddr = tmem_base + ((uint32_t) (quarter * 32) << 16) + acc * BN + half * COLS_PER_THREAD;
+#pragma unroll
+                    for (int c0 = 0; c0 < COLS_PER_THREAD; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(taddr + c0, v);
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) sum[c0 + c] += __uint_as_float(v[c]);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar + 8 * acc, 0));
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                }
+                if (!ok) break;
+                if (j < n) {
+                    const int i0 = nb * BN + half * COLS_PER_THREAD;
+#pragma unroll
+                    for (int c = 0; c < COLS_PER_THREAD; ++c) {
+                        const int i = i0 + c;
+                        if (i < m) out[(size_t) i * ld_out + j] = apply_kernel(fn, sum[c], __ldg(sd_rows + i), sdj);
+                    }
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        const long long t0 = global_ns();
+        while (global_ns() - t0 < 1000000ll) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();           // neither CTA leaves while its partner may still signal it or read its memory
+    tc_fence_after();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (threadIdx.x == 0 && *abort_flag) atomicMax(status, *abort_flag);
+}
+
+tsvm_status make_map(CUtensorMap *map, const float *ptr, int rows, int d_pad, long long ld, int box_rows);   // dense_tc.cu
+
+tsvm_status launch_dense_tc2(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
+    CUtensorMap mxh, mxl, mwh, mwl;
+    TSVM_TRY(make_map(&mxh, km->Xhi, km->n, km->d_pad, km->d_pad, tc2::BM));
+    TSVM_TRY(make_map(&mxl, km->Xlo, km->n, km->d_pad, km->d_pad, tc2::BM));
+    TSVM_TRY(make_map(&mwh, km->Whi, m, km->d_pad, km->d_pad, tc2::BN_HALF));
+    TSVM_TRY(make_map(&mwl, km->Wlo, m, km->d_pad, km->d_pad, tc2::BN_HALF));
+    static int max_clusters = 0;
+    if (!max_clusters) {
+        int dev = 0, sms = 0;
+        TSVM_CUDA(cudaGetDevice(&dev));
+        TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int) tc2::SMEM_BYTES));
+        cudaLaunchConfig_t probe = {};
+        cudaLaunchAttribute pattr[1];
+        pattr[0].id = cudaLaunchAttributeClusterDimension;
+        pattr[0].val.clusterDim.x = 2; pattr[0].val.clusterDim.y = 1; pattr[0].val.clusterDim.z = 1;
+        probe.gridDim = dim3(sms & ~1); probe.blockDim = dim3(tc2::THREADS); probe.dynamicSmemBytes = tc2::SMEM_BYTES;
+        probe.attrs = pattr; probe.numAttrs = 1;
+        int nc = 0;
+        if (cudaOccupancyMaxActiveClusters(&nc, dense_rows_tc2_kernel, &probe) != cudaSuccess || nc < 1) {
+            cudaGetLastError();
+            nc = sms / 2;
+        }
+        max_clusters = nc;
+    }
+    const int pair_tiles = ceil_div(km->n, 2 * tc2::BM);
+    const int clusters = pair_tiles < max_clusters ? pair_tiles : max_clusters;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(tc2::THREADS); cfg.dynamicSmemBytes = tc2::SMEM_BYTES;
+    cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
+    TSVM_CUDA(cudaLaunchKernelEx(&cfg, dense_rows_tc2_kernel, mxh, mxl, mwh, mwl, km->n, m, km->d_pad,
+                                 (const float *) km->self_dot, (const float *) km->sd_rows, km->fn, out, ld_out,
+                                 km->status_dev));
+    count_launch();
+    return TSVM_OK;
+}
+
+}  // namespace tsvm

@@ -352,9 +352,9 @@ static tsvm_status finish_create(tsvm_km *km, cudaStream_t st) {
     return TSVM_OK;
 }
 
-// engine: 0 = automatic, 1 = CUDA cores, 2 = tensor cores
+// engine: 0 = automatic, 1 = CUDA cores, 2 = tensor cores (one CTA per tile), 3 = tensor cores (CTA pairs)
 static inline bool use_tensor_engine(const tsvm_km *km) {
-    return km->engine == 2 || (km->engine == 0 && km->d_pad > 32);
+    return km->engine >= 2 || (km->engine == 0 && km->d_pad > 32);
 }
 
 static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
@@ -482,7 +482,7 @@ const float *tsvm_km_diag_dev(const tsvm_km *km) { return km ? km->diag : nullpt
 const float *tsvm_km_self_dot_dev(const tsvm_km *km) { return km ? km->self_dot : nullptr; }
 
 tsvm_status tsvm_km_set_dense_engine(tsvm_km *km, int engine) {
-    TSVM_REQUIRE(km && engine >= 0 && engine <= 2, "set_dense_engine: bad arguments");
+    TSVM_REQUIRE(km && engine >= 0 && engine <= 3, "set_dense_engine: bad arguments");
     km->engine = engine;
     return TSVM_OK;
 }
