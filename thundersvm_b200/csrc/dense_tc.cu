@@ -43,6 +43,7 @@ constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t) (BN 
                            ((uint32_t) (BM >> 4) << 24);
 }  // namespace tc
 
+template <int EPI>
 __global__ void __launch_bounds__(tc::THREADS, 1)
 dense_rows_tc_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
                      const __grid_constant__ CUtensorMap map_whi, const __grid_constant__ CUtensorMap map_wlo,
@@ -164,7 +165,7 @@ dense_rows_tc_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_c
 #pragma unroll
                     for (int c = 0; c < COLS_PER_THREAD; ++c) {
                         const int i = i0 + c;
-                        if (i < m) out[(size_t) i * ld_out + j] = apply_kernel(fn, sum[c], __ldg(sd_rows + i), sdj);
+                        if (i < m) out[(size_t) i * ld_out + j] = epilogue_value<EPI>(fn, sum[c], __ldg(sd_rows + i), sdj);
                     }
                 }
             }
@@ -234,13 +235,24 @@ tsvm_status launch_dense_tc(tsvm_km *km, int m, float *out, long long ld_out, cu
         int dev = 0;
         TSVM_CUDA(cudaGetDevice(&dev));
         TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc_kernel<EPI_RBF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int) tc::SMEM_BYTES));
+        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc_kernel<EPI_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int) tc::SMEM_BYTES));
+        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc_kernel<EPI_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int) tc::SMEM_BYTES));
     }
     const int m_tiles = ceil_div(km->n, tc::BM);
     const int grid = m_tiles < sms ? m_tiles : sms;
-    TSVM_LAUNCH(dense_rows_tc_kernel, grid, tc::THREADS, tc::SMEM_BYTES, st, mxh, mxl, mwh, mwl, km->n, m, km->d_pad,
-                km->self_dot, km->sd_rows, km->fn, out, ld_out, km->status_dev);
+#define TC_LAUNCH(E)                                                                                              \
+    TSVM_LAUNCH(dense_rows_tc_kernel<E>, grid, tc::THREADS, tc::SMEM_BYTES, st, mxh, mxl, mwh, mwl, km->n, m,     \
+                km->d_pad, km->self_dot, km->sd_rows, km->fn, out, ld_out, km->status_dev)
+    switch (epilogue_kind(km->fn)) {
+        case EPI_RBF: TC_LAUNCH(EPI_RBF); break;
+        case EPI_LINEAR: TC_LAUNCH(EPI_LINEAR); break;
+        default: TC_LAUNCH(EPI_GENERIC); break;
+    }
+#undef TC_LAUNCH
     return TSVM_OK;
 }
 

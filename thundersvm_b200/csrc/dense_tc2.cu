@@ -66,6 +66,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
 }
 
+template <int EPI>
 __global__ void __launch_bounds__(tc2::THREADS, 1)
 dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
                       const __grid_constant__ CUtensorMap map_whi, const __grid_constant__ CUtensorMap map_wlo,
@@ -193,7 +194,7 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
 #pragma unroll
                     for (int c = 0; c < COLS_PER_THREAD; ++c) {
                         const int i = i0 + c;
-                        if (i < m) out[(size_t) i * ld_out + j] = apply_kernel(fn, sum[c], __ldg(sd_rows + i), sdj);
+                        if (i < m) out[(size_t) i * ld_out + j] = epilogue_value<EPI>(fn, sum[c], __ldg(sd_rows + i), sdj);
                     }
                 }
             }
@@ -226,7 +227,11 @@ tsvm_status launch_dense_tc2(tsvm_km *km, int m, float *out, long long ld_out, c
         int dev = 0, sms = 0;
         TSVM_CUDA(cudaGetDevice(&dev));
         TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc2_kernel<EPI_RBF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int) tc2::SMEM_BYTES));
+        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc2_kernel<EPI_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int) tc2::SMEM_BYTES));
+        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc2_kernel<EPI_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int) tc2::SMEM_BYTES));
         cudaLaunchConfig_t probe = {};
         cudaLaunchAttribute pattr[1];
@@ -235,7 +240,7 @@ tsvm_status launch_dense_tc2(tsvm_km *km, int m, float *out, long long ld_out, c
         probe.gridDim = dim3(sms & ~1); probe.blockDim = dim3(tc2::THREADS); probe.dynamicSmemBytes = tc2::SMEM_BYTES;
         probe.attrs = pattr; probe.numAttrs = 1;
         int nc = 0;
-        if (cudaOccupancyMaxActiveClusters(&nc, dense_rows_tc2_kernel, &probe) != cudaSuccess || nc < 1) {
+        if (cudaOccupancyMaxActiveClusters(&nc, dense_rows_tc2_kernel<EPI_RBF>, &probe) != cudaSuccess || nc < 1) {
             cudaGetLastError();
             nc = sms / 2;
         }
@@ -249,9 +254,16 @@ tsvm_status launch_dense_tc2(tsvm_km *km, int m, float *out, long long ld_out, c
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(tc2::THREADS); cfg.dynamicSmemBytes = tc2::SMEM_BYTES;
     cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
-    TSVM_CUDA(cudaLaunchKernelEx(&cfg, dense_rows_tc2_kernel, mxh, mxl, mwh, mwl, km->n, m, km->d_pad,
-                                 (const float *) km->self_dot, (const float *) km->sd_rows, km->fn, out, ld_out,
-                                 km->status_dev));
+#define TC2_LAUNCH(E)                                                                                            \
+    TSVM_CUDA(cudaLaunchKernelEx(&cfg, dense_rows_tc2_kernel<E>, mxh, mxl, mwh, mwl, km->n, m, km->d_pad,           \
+                                 (const float *) km->self_dot, (const float *) km->sd_rows, km->fn, out, ld_out,   \
+                                 km->status_dev))
+    switch (epilogue_kind(km->fn)) {
+        case EPI_RBF: TC2_LAUNCH(EPI_RBF); break;
+        case EPI_LINEAR: TC2_LAUNCH(EPI_LINEAR); break;
+        default: TC2_LAUNCH(EPI_GENERIC); break;
+    }
+#undef TC2_LAUNCH
     count_launch();
     return TSVM_OK;
 }

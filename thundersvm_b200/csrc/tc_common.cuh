@@ -91,4 +91,35 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 }
 
 
+// ---- epilogue: kernel function applied to the register sums -------------------------------------
+// The epilogue is unrolled 128 times (the sums live in registers), so its body has to stay small:
+// with the library expf / powf / tanhf inlined 128 times the code outgrew the instruction cache
+// and one tile's epilogue took as long as two thirds of its main loop. The RBF path therefore uses
+// a 6-instruction exponential: exp(x) = 2^y (1 + r ln2) with y = fl(x log2e) and r the rounding
+// residual of that product (FMA) plus x times the representation error of log2e; ex2.approx is
+// accurate to 2^-22.5 relative, the total stays below 3e-7 relative for |x| <= 100.
+enum { EPI_RBF = 0, EPI_LINEAR = 1, EPI_GENERIC = 2 };
+
+__device__ __forceinline__ float exp_compact(float x) {
+    const float y = x * 1.4426950408889634f;
+    float r = fmaf(x, 1.4426950408889634f, -y);
+    r = fmaf(x, 1.925963033500e-8f, r);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y));
+    return fmaf(e, r * 0.6931471805599453f, e);
+}
+
+template <int EPI>
+__device__ __forceinline__ float epilogue_value(const KernelFn &fn, float dot, float sd_i, float sd_j) {
+    if (EPI == EPI_RBF) return exp_compact(-(sd_i + sd_j - dot * 2.0f) * fn.gamma);
+    if (EPI == EPI_LINEAR) return dot;
+    return apply_kernel(fn, dot, sd_i, sd_j);
+}
+
+__host__ inline int epilogue_kind(const KernelFn &fn) {
+    if (fn.type == TSVM_RBF || fn.type == TSVM_PRECOMPUTED) return EPI_RBF;
+    if (fn.type == TSVM_LINEAR) return EPI_LINEAR;
+    return EPI_GENERIC;
+}
+
 }  // namespace tsvm
