@@ -45,9 +45,9 @@ def build(force=False, verbose=False):
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(
                 [os.path.getmtime(src)] + [os.path.getmtime(h) for h in headers()]):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-I",
-                                                                                 os.path.join(HERE, "..", "include"),
-                                                                                 "-c", src, "-o", obj]
+            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
+                "-x", "cu", "-I", os.path.join(HERE, "..", "include"), "-I", os.path.join(CSRC, "host", "include"),
+                "-c", src, "-o", obj]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, p in procs:
@@ -58,7 +58,19 @@ def build(force=False, verbose=False):
     if failed:
         raise RuntimeError("nvcc failed")
     subprocess.check_call([nvcc, "-shared", "-o", LIB] + objs + ["-lcudart", "-Xcompiler", "-fopenmp"])
+    build_cli(nvcc)
     return LIB
+
+
+def build_cli(nvcc):
+    """thundersvm-train / thundersvm-predict next to the library (rpath $ORIGIN/..)."""
+    bindir = os.path.join(HERE, "bin")
+    os.makedirs(bindir, exist_ok=True)
+    for name in ("thundersvm-train", "thundersvm-predict"):
+        src = os.path.join(HERE, "cli", name + ".cpp")
+        subprocess.check_call([nvcc, "-O2", "-std=c++17", "-I", os.path.join(CSRC, "host", "include"), src, "-o",
+                               os.path.join(bindir, name), "-L", HERE, "-lthundersvm_b200", "-Xlinker",
+                               "-rpath=$ORIGIN/.."])
 
 
 if __name__ == "__main__":
