@@ -8,7 +8,7 @@ instances, 512 new kernel rows of length n, the local solver on the 1024-wide wo
 f update. The metric is kernel rows per second (rows of length n = 400,000):
   value : K timed steps with the data already resident in HBM (CUDA events, max over ranks)
   e2e   : the same K-step job through the C ABI starting from pinned HOST buffers - the
-          host->device copy of X / y / alpha / f, the TF32 split, the solver set-up and the
+          host->device copy of X / y / alpha / f, the operand-plane split, the solver set-up and the
           device->host read of alpha / f / rho are inside the timed region
 plus, when --full-train is on (default at N=1), the whole training run to eps = 1e-3.
 `--impl reference` times the reference's own CPU implementation (oracle/_ref, built from the
@@ -30,6 +30,7 @@ sys.path.insert(0, ROOT)
 
 N_FULL, D_FULL, WS, Q = 400000, 2000, 1024, 512
 GAMMA, C_SVC, EPS = 0.5, 1.0, 1e-3
+TRAFFIC_37888 = None   # bytes (dram read + write) of one 37,888-instance launch, from profiles/
 
 
 def parse():
@@ -151,25 +152,31 @@ class ClockSampler:
         return out
 
 
-def measure_tf32_peak(torch):
-    """Dense TF32 GEMM throughput of this GPU (torch.matmul 8192^3, best of 10), the denominator for
-    the 3xTF32 kernel-row contraction."""
-    old = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = True
+def measure_f16_peak(torch):
+    """Dense FP16 GEMM throughput of this GPU (torch.matmul 8192^3, best of 10): the in-run cross-check
+    of the driver-measured tensor peak the kernel-row contraction is reported against."""
+    a = torch.randn(8192, 8192, device="cuda", dtype=torch.float16)
+    b = torch.randn(8192, 8192, device="cuda", dtype=torch.float16)
+    for _ in range(3):
+        a @ b
+    best = 1e9
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); a @ b; e1.record(); e1.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    del a, b
+    return 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+
+
+def measured_peaks():
+    """(burst, sustained, source) dense 16-bit tensor TFLOP/s: the driver-written file at the repo root,
+    else the pool's earlier measurement."""
     try:
-        a = torch.randn(8192, 8192, device="cuda")
-        b = torch.randn(8192, 8192, device="cuda")
-        for _ in range(3):
-            a @ b
-        best = 1e9
-        for _ in range(10):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); a @ b; e1.record(); e1.synchronize()
-            best = min(best, e0.elapsed_time(e1))
-        return 2 * 8192 ** 3 / (best * 1e-3) / 1e12
-    finally:
-        torch.backends.cuda.matmul.allow_tf32 = old
-        del a, b
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            m = json.load(fh)
+        return float(m["bf16_tflops"]), float(m["bf16_tflops_sustained"]), "of measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except Exception:
+        return 1590.0, 1400.0, "of fallback (1.59 PFLOP/s burst)"
 
 
 def run_b200_arm(args):
@@ -209,7 +216,8 @@ def run_b200_arm(args):
     fh = torch.from_numpy(-y_np.astype(np.float64)).pin_memory()
     ah = torch.zeros(n, dtype=torch.float64).pin_memory()
 
-    tf32_peak = measure_tf32_peak(torch)
+    f16_peak_in_run = measure_f16_peak(torch)
+    peak, peak_sustained, peak_src = measured_peaks()
 
     # ---- (1) resident: K timed steps ------------------------------------------------------------
     Xd = Xh.cuda(non_blocking=True)
@@ -240,13 +248,19 @@ def run_b200_arm(args):
               for k in ("select", "rows", "local", "update")}
     flops = 2.0 * Q * n * d
     achieved = flops / t_rows / 1e12
-    roofline = {"bound": "tensor", "kernel": "dense_rows_tc_kernel (3xTF32 tcgen05, fused RBF epilogue)",
-                "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
-                "issued_frac": 3 * achieved / tf32_peak, "traffic": None,
-                "peak_source": "dense TF32 torch.matmul 8192^3 best-of-10 measured in this run (MEASURED_PEAKS.json "
-                               "holds bf16 only); achieved = algorithmic 2*q*n*d flops per launch / mean CUDA-event "
-                               "time of the kernel-row phase; the 3-pass scheme issues 3x these flops",
-                "ms_per_launch": t_rows * 1e3}
+    # DRAM traffic per launch: ncu capture of a 37,888-instance launch of the same kernel (same d, same q),
+    # scaled by the instances (the X planes and the output grow with n; the planes of the 512 rows do not)
+    traffic = TRAFFIC_37888 * n / 37888.0 if TRAFFIC_37888 else None
+    roofline = {"bound": "tensor",
+                "kernel": "dense_rows_tc2_kernel<EPI_RBF, F16> (tcgen05 CTA pairs, two row-scaled FP16 planes, "
+                          "3 MMAs per product, per-slab FP32 promotion, fused RBF epilogue)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "issued_frac": 3 * achieved / peak, "traffic": traffic,
+                "peak_source": peak_src + "; sustained figure %.0f; torch.matmul fp16 8192^3 best-of-10 in this run "
+                               "%.0f. achieved = algorithmic 2*q*n*d flops per launch / mean CUDA-event time of the "
+                               "kernel-row phase; the two-plane scheme issues 3x these flops (issued_frac)"
+                               % (peak_sustained, f16_peak_in_run),
+                "peak_in_run": f16_peak_in_run, "ms_per_launch": t_rows * 1e3}
     solver.close()
     km.close()
     del Xd, km, solver
@@ -280,7 +294,7 @@ def run_b200_arm(args):
     d2h = n * 16 + 8
     e2e = {"value": st_e2e["kernel_rows"] / sec_e2e, "unit": "rows/s", "h2d_bytes_per_step": h2d / (W + K),
            "d2h_bytes_per_step": d2h / (W + K), "seconds": sec_e2e, "steps": W + K,
-           "note": "one K+W-step job through the C ABI from pinned host buffers: H2D of X/y/alpha/f, TF32 split, "
+           "note": "one K+W-step job through the C ABI from pinned host buffers: H2D of X/y/alpha/f, operand-plane split, "
                    "solver set-up, steps, D2H of alpha/f/rho all inside the timed region"}
 
     # ---- (3) the whole training run to eps --------------------------------------------------------
@@ -304,10 +318,10 @@ def run_b200_arm(args):
     line = {
         "metric": "kernel_rows_per_s", "value": value, "unit": "rows/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f32 kernel values (3xTF32 contraction), f64 solver state", "data": "synthetic",
+        "dtype": "f32 kernel values (two-plane FP16 tensor-core contraction with FP32 accumulation), f64 solver state", "data": "synthetic",
         "config": {"workload": "config5: binary C-SVC, RBF gamma=0.5 C=1 eps=1e-3, %dx%d dense fp32, ws=1024, "
                                "512 new kernel rows per outer iteration" % (n, d),
-                   "l2": "inputs larger than L2 (X planes %.1f GB, row buffer %.1f GB)" % (2 * n * d * 4 / 1e9,
+                   "l2": "inputs larger than L2 (X planes %.1f GB, row buffer %.1f GB)" % (2 * n * d * 2 / 1e9,
                                                                                           WS * n * 4 / 1e9)},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
         "phase_ms_per_step": phases, "train_to_eps": train,

@@ -107,10 +107,13 @@ tsvm_status tsvm_km_rows_by_instances_csr(tsvm_km *km, const float *tval_dev, co
 tsvm_status tsvm_km_rows_for_features_dense(tsvm_km *km, const float *T_dev, int ldt, const float *sd_T_dev, int m,
                                             float *out_dev, long long ld_out, void *stream);
 
-/* Selects the dense kernel-row engine: 0 = automatic (default: tcgen05 tensor-core tiles, FP32
- * CUDA-core tiles when there are at most 32 features, where a k loop of one slab gives the
- * tensor core nothing to pipeline), 1 = FP32 CUDA-core tiles, 2 = tcgen05 tiles with one CTA per
- * tile, 3 = tcgen05 tiles computed by CTA pairs (what "automatic" uses). */
+/* Selects the dense kernel-row engine: 0 = automatic (default: engine 4, or FP32 CUDA-core tiles when
+ * there are at most 32 features, where a k loop of one slab gives the tensor core nothing to
+ * pipeline), 1 = FP32 CUDA-core tiles, 2 = tcgen05 tiles on two TF32 planes with one CTA per tile,
+ * 3 = the same planes with CTA pairs, 4 = tcgen05 CTA pairs on two row-scaled FP16 planes (every row
+ * is multiplied by a power of two that brings its largest magnitude to [2^14, 2^15) before the split;
+ * same accuracy class as engine 3 at twice the tensor-core rate and half the operand bytes). The
+ * operand planes are built on the first call that needs them; changing the engine rebuilds them. */
 tsvm_status tsvm_km_set_dense_engine(tsvm_km *km, int engine);
 
 /* ------------------------------------------------------------------------------------------

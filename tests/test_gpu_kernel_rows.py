@@ -38,7 +38,7 @@ def _check_rows(capi, prob, n, q, engine=None, force=None, kernel="rbf", coef0=0
     return km, X
 
 
-@pytest.mark.parametrize("engine", ["auto", "tensor", "tensor1", "simt"])
+@pytest.mark.parametrize("engine", ["auto", "tensor", "tensor2", "tensor1", "simt"])
 @pytest.mark.parametrize("n,q", [(1000, 64), (4097, 512), (300, 101), (129, 128), (128, 1), (2500, 1024)])
 def test_dense_rows_c1(capi, engine, n, q):
     """Config 1 has 20 features with |x| up to 3 and RBF arguments up to ~50. The automatic engine uses
@@ -48,13 +48,13 @@ def test_dense_rows_c1(capi, engine, n, q):
     _check_rows(capi, synth.config1(n), n, q, engine=engine, tol=3e-5 if engine.startswith("tensor") else REL_TOL)
 
 
-@pytest.mark.parametrize("engine", ["tensor", "tensor1", "simt"])
+@pytest.mark.parametrize("engine", ["tensor", "tensor2", "tensor1", "simt"])
 def test_dense_rows_c5_shape(capi, engine):
     """Unit-norm rows, d = 2000 (config 5's row length), n not a multiple of the tile."""
     _check_rows(capi, synth.config5(3001), 3001, 512, engine=engine)
 
 
-@pytest.mark.parametrize("engine", ["tensor", "tensor1", "simt"])
+@pytest.mark.parametrize("engine", ["tensor", "tensor2", "tensor1", "simt"])
 def test_dense_rows_c3_shape(capi, engine):
     """784 features in [0,1] (config 3). Same-class dot products reach ~100, where the oracle's own
     sequential FP32 accumulation noise is ~1e-5 relative on K; both are therefore also compared with an
@@ -79,16 +79,45 @@ def test_dense_rows_c3_shape(capi, engine):
 
 @pytest.mark.parametrize("kernel,kw", [("linear", {}), ("poly", dict(coef0=0.1, degree=3)),
                                        ("sigmoid", dict(coef0=0.1))])
-@pytest.mark.parametrize("engine", ["tensor", "tensor1", "simt"])
+@pytest.mark.parametrize("engine", ["tensor", "tensor2", "tensor1", "simt"])
 def test_dense_rows_other_kernels(capi, engine, kernel, kw):
     _check_rows(capi, synth.config1(1500), 1500, 200, engine=engine, kernel=kernel, **kw)
 
 
+@pytest.mark.parametrize("engine", ["tensor", "tensor2"])
 @pytest.mark.parametrize("n,q", [(100, 5), (129, 127), (257, 129), (384, 256), (511, 300), (40000, 512)])
-def test_dense_rows_pair_engine_odd_tiles(capi, n, q):
+def test_dense_rows_pair_engine_odd_tiles(capi, engine, n, q):
     """CTA-pair tiles with an empty or partial second half (n just above / below multiples of 128 and
-    256) and requested-row counts around the 128-row halves of the B operand."""
-    _check_rows(capi, synth.config5(n, d=136), n, q, engine="tensor")
+    256) and requested-row counts around the 128-row halves of the B operand. d = 136 is a multiple of 8
+    but not of the 32- or 64-element k slab; d = 133 makes the FP16 planes wider than the FP32 rows."""
+    _check_rows(capi, synth.config5(n, d=136), n, q, engine=engine)
+    if n <= 511:
+        _check_rows(capi, synth.config5(n, d=133), n, q, engine=engine)
+
+
+@pytest.mark.parametrize("engine", ["tensor", "tensor2", "simt"])
+def test_dense_rows_row_magnitudes(capi, engine):
+    """Rows whose magnitudes span 16 decades and whose features span 6 decades inside a row (linear
+    kernel, so nothing hides in an exponent). The FP16-plane engine scales every row by a power of two;
+    the result must be as close to FP64 as FP32 arithmetic allows, relative to the two rows' norms."""
+    import torch
+    rng = np.random.default_rng(5)
+    n, d, q = 1500, 300, 256
+    X0 = rng.random((n, d)) * 10.0 ** rng.uniform(-6, 0, size=(n, d))
+    X0 /= np.linalg.norm(X0, axis=1, keepdims=True)
+    s = 10.0 ** rng.uniform(-8, 8, size=n)
+    s[:4] = [0.0, 1e-15, 1e15, 1.0]               # an all-zero row, a tiny and a huge one (products stay FP32-normal)
+    X = (X0 * s[:, None]).astype(np.float32)
+    km = capi.KernelMatrix(dense=torch.from_numpy(X).cuda(), kernel="linear", gamma=1.0)
+    km.set_dense_engine(engine)
+    idx = np.concatenate([np.arange(4), rng.choice(n, q - 4, replace=False)]).astype(np.int32)
+    got = km.get_rows(torch.from_numpy(idx).cuda()).cpu().numpy().astype(np.float64)
+    D = X.astype(np.float64)
+    exact = D[idx] @ D.T
+    norms = np.maximum(np.linalg.norm(D, axis=1), 1e-100)
+    err = np.abs(got - exact) / (norms[idx][:, None] * norms[None, :])
+    assert np.isfinite(got).all()
+    assert err.max() < (4e-6 if engine == "simt" else 2e-6), err.max()
 
 
 @pytest.mark.parametrize("n,q", [(1200, 64), (5000, 512), (333, 101), (2000, 1024)])

@@ -176,7 +176,7 @@ class KernelMatrix:
         return self._h
 
     def set_dense_engine(self, engine):
-        check(lib().tsvm_km_set_dense_engine(self._h, {"auto": 0, "simt": 1, "tensor1": 2, "tensor": 3, "tensor2": 3}.get(engine, engine)))
+        check(lib().tsvm_km_set_dense_engine(self._h, {"auto": 0, "simt": 1, "tensor1": 2, "tensor2": 3, "tensor_tf32": 3, "tensor": 4, "tensor_f16": 4}.get(engine, engine)))
 
     def _vec(self, fn):
         view = _DeviceView(fn(self._h), self.n)

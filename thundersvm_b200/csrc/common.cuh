@@ -147,12 +147,18 @@ struct tsvm_km {
     long long nnz = 0;
     bool dense = true;
     tsvm::KernelFn fn{};
-    int engine = 0;                 // 0 = automatic, 1 = CUDA-core FP32, 2 = tcgen05 single CTA, 3 = tcgen05 CTA pairs
+    // 0 = automatic, 1 = CUDA-core FP32, 2 = tcgen05 TF32 planes single CTA, 3 = tcgen05 TF32 planes CTA pairs,
+    // 4 = tcgen05 row-scaled FP16 planes CTA pairs
+    int engine = 0;
     // dense storage: row-major, row stride ldx floats (multiple of 4)
     const float *X = nullptr;
     int ldx = 0;
     float *X_owned = nullptr;
-    float *Xhi = nullptr, *Xlo = nullptr;   // TF32 split of X, row stride d_pad
+    // Two-plane split of X for the tensor engines, built on first use: TF32 words (plane_kind 1, row
+    // stride d_pad) or row-scaled FP16 halves (plane_kind 2, row stride plane_ld = round_up(d, 8)).
+    float *Xhi = nullptr, *Xlo = nullptr;
+    int plane_kind = 0, plane_ld = 0;
+    float *x_unscale = nullptr;     // FP16 planes: 1 / (power-of-two scale) of every instance row [n]
     int d_pad = 0;
     // CSR storage
     const float *val = nullptr;
@@ -163,7 +169,8 @@ struct tsvm_km {
     // scratch for the rows whose kernel values are requested
     int w_cap = 0;                  // rows the scratch below can hold
     float *W = nullptr;             // dense engines: w_cap x d_pad (row-major), FP32
-    float *Whi = nullptr, *Wlo = nullptr;   // TF32 split of W
+    float *Whi = nullptr, *Wlo = nullptr;   // two-plane split of W, same kind as the X planes
+    float *w_unscale = nullptr;     // FP16 planes: 1 / scale of every requested row [w_cap]
     float *WT = nullptr;            // CSR engine: d x wt_ld, column = requested row
     int wt_ld = 0;
     float *sd_rows = nullptr;       // self dots of the requested rows [w_cap]

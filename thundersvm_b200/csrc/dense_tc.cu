@@ -204,17 +204,19 @@ static encode_fn_t get_encode() {
     return fn;
 }
 
-// rows x d_pad FP32 matrix with row stride ld floats; box = 32 floats x box_rows rows.
-tsvm_status make_map(CUtensorMap *map, const float *ptr, int rows, int d_pad, long long ld, int box_rows) {
+// rows x row_len matrix of 32-bit words (or FP16 halves) with row stride ld elements; box = one 128-byte
+// swizzle row (32 words / 64 halves) x box_rows rows.
+tsvm_status make_map(CUtensorMap *map, const void *ptr, int rows, int row_len, long long ld, int box_rows, bool f16) {
     encode_fn_t enc = get_encode();
     if (!enc) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return TSVM_ERR_CUDA; }
-    cuuint64_t dims[2] = {(cuuint64_t) d_pad, (cuuint64_t) rows};
-    cuuint64_t strides[1] = {(cuuint64_t) ld * sizeof(float)};
-    cuuint32_t box[2] = {(cuuint32_t) tc::BK, (cuuint32_t) box_rows};
+    const size_t esz = f16 ? 2 : 4;
+    cuuint64_t dims[2] = {(cuuint64_t) row_len, (cuuint64_t) rows};
+    cuuint64_t strides[1] = {(cuuint64_t) ld * esz};
+    cuuint32_t box[2] = {(cuuint32_t) (128 / esz), (cuuint32_t) box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *) ptr, dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *) ptr, dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int) r); return TSVM_ERR_CUDA; }
     return TSVM_OK;
 }
@@ -225,11 +227,12 @@ tsvm_status launch_dense_tc2(tsvm_km *km, int m, float *out, long long ld_out, c
 tsvm_status launch_dense_tc(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
     // engine 2 forces the single-CTA tiles; otherwise CTA pairs (also for one tile: the second CTA idles)
     if (km->engine != 2) return launch_dense_tc2(km, m, out, ld_out, st);
+    TSVM_REQUIRE(km->plane_kind == 1, "single-CTA tensor engine needs TF32 planes");
     CUtensorMap mxh, mxl, mwh, mwl;
-    TSVM_TRY(make_map(&mxh, km->Xhi, km->n, km->d_pad, km->d_pad, tc::BM));
-    TSVM_TRY(make_map(&mxl, km->Xlo, km->n, km->d_pad, km->d_pad, tc::BM));
-    TSVM_TRY(make_map(&mwh, km->Whi, m, km->d_pad, km->d_pad, tc::BN));
-    TSVM_TRY(make_map(&mwl, km->Wlo, m, km->d_pad, km->d_pad, tc::BN));
+    TSVM_TRY(make_map(&mxh, km->Xhi, km->n, km->d_pad, km->d_pad, tc::BM, false));
+    TSVM_TRY(make_map(&mxl, km->Xlo, km->n, km->d_pad, km->d_pad, tc::BM, false));
+    TSVM_TRY(make_map(&mwh, km->Whi, m, km->d_pad, km->d_pad, tc::BN, false));
+    TSVM_TRY(make_map(&mwl, km->Wlo, m, km->d_pad, km->d_pad, tc::BN, false));
     static int sms = 0;
     if (!sms) {
         int dev = 0;

@@ -20,15 +20,19 @@
 namespace tsvm {
 
 namespace tc2 {
-constexpr int BM = 128, BN = 256, BN_HALF = 128, BK = 32, STAGES = 3, UMMA_K = 8;
-constexpr uint32_t A_BYTES = BM * BK * 4;            // 16 KB per plane (this CTA's instances)
-constexpr uint32_t B_BYTES = BN_HALF * BK * 4;       // 16 KB per plane (this CTA's half of the requested rows)
+// A k slab is one 128-byte swizzle row per matrix row: 32 TF32 words or 64 FP16 halves, four MMA k-steps
+// of 32 bytes either way.
+constexpr int BM = 128, BN = 256, BN_HALF = 128, STAGES = 3, K_STEPS = 4;
+constexpr uint32_t A_BYTES = BM * 128;               // 16 KB per plane (this CTA's instances)
+constexpr uint32_t B_BYTES = BN_HALF * 128;          // 16 KB per plane (this CTA's half of the requested rows)
 constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // 64 KB per CTA
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int THREADS = 320, EPI_WARPS = 8, COLS_PER_THREAD = 128;
 constexpr uint32_t TMEM_COLS = 512;
-// D=F32, A=B=TF32, K-major, N=256, M=256 (two CTAs x 128)
-constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
+// D=F32, K-major, N=256, M=256 (two CTAs x 128); A=B=TF32 (format 2) or F16 (format 0)
+constexpr uint32_t IDESC_SHAPE = (1u << 4) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
+constexpr uint32_t IDESC_TF32 = IDESC_SHAPE | (2u << 7) | (2u << 10);
+constexpr uint32_t IDESC_F16 = IDESC_SHAPE;
 }  // namespace tc2
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -54,25 +58,35 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
 }
-__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(tc2::IDESC), "r"(accumulate) : "memory");
+template <bool F16>
+__device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    if constexpr (F16)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(tc2::IDESC_F16), "r"(accumulate) : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(tc2::IDESC_TF32), "r"(accumulate) : "memory");
 }
 // arrives on the barrier at a shared::cluster address once all MMAs issued so far have retired
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
 }
 
-template <int EPI>
+template <int EPI, bool F16>
 __global__ void __launch_bounds__(tc2::THREADS, 1)
 dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
                       const __grid_constant__ CUtensorMap map_whi, const __grid_constant__ CUtensorMap map_wlo,
-                      int n, int m, int d_pad, const float *__restrict__ sd, const float *__restrict__ sd_rows,
+                      int n, int m, int row_len, const float *__restrict__ sd, const float *__restrict__ sd_rows,
+                      const float *__restrict__ x_unscale, const float *__restrict__ w_unscale,
                       KernelFn fn, float *__restrict__ out, long long ld_out, int *__restrict__ status) {
     using namespace tc2;
+    constexpr int BK = F16 ? 64 : 32;          // elements per k slab
     extern __shared__ uint8_t smem_raw[];
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
@@ -85,7 +99,10 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-    const int pair_tiles = (n + 2 * BM - 1) / (2 * BM), n_blocks = (m + BN - 1) / BN, k_blocks = (d_pad + BK - 1) / BK;
+    const int pair_tiles = (n + 2 * BM - 1) / (2 * BM), n_blocks = (m + BN - 1) / BN, k_blocks = (row_len + BK - 1) / BK;
+    // Work items are (pair tile, row block) with the row block fastest, so neighbouring clusters stream the
+    // same instance slabs at the same time and the second reader finds them in L2.
+    const int n_items = pair_tiles * n_blocks;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
@@ -110,8 +127,8 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int pt = cluster_id; pt < pair_tiles && ok; pt += n_clusters)
-                for (int nb = 0; nb < n_blocks && ok; ++nb)
+            for (int item = cluster_id; item < n_items && ok; item += n_clusters) {
+                    const int pt = item / n_blocks, nb = item - pt * n_blocks;
                     for (int kb = 0; kb < k_blocks; ++kb) {
                         if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
                         const uint32_t base = ring + stage * STAGE_BYTES;
@@ -124,14 +141,14 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                         tma_load_2d_pair(base + 2 * A_BYTES + B_BYTES, &map_wlo, leader_full, kb * BK, wrow);
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
+            }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only) ----------------
         if (lane == 0 && rank == 0) {
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (int pt = cluster_id; pt < pair_tiles && ok; pt += n_clusters)
-                for (int nb = 0; nb < n_blocks && ok; ++nb)
+            for (int item = cluster_id; item < n_items && ok; item += n_clusters)
                     for (int kb = 0; kb < k_blocks; ++kb) {
                         if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, 2)) { ok = false; break; }
                         if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
@@ -139,17 +156,17 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                         const uint32_t d_tmem = tmem_base + acc * BN;
                         const uint32_t base = ring + stage * STAGE_BYTES;
 #pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; ++k) {
-                            const uint32_t koff = k * UMMA_K * 4;
-                            umma_tf32_pair(d_tmem, smem_desc_sw128(base + A_BYTES + koff),
+                        for (int k = 0; k < K_STEPS; ++k) {
+                            const uint32_t koff = k * 32;
+                            umma_pair<F16>(d_tmem, smem_desc_sw128(base + A_BYTES + koff),
                                            smem_desc_sw128(base + 2 * A_BYTES + koff), k != 0);
-                            umma_tf32_pair(d_tmem, smem_desc_sw128(base + koff),
+                            umma_pair<F16>(d_tmem, smem_desc_sw128(base + koff),
                                            smem_desc_sw128(base + 2 * A_BYTES + B_BYTES + koff), 1);
                         }
 #pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; ++k) {
-                            const uint32_t koff = k * UMMA_K * 4;
-                            umma_tf32_pair(d_tmem, smem_desc_sw128(base + koff), smem_desc_sw128(base + 2 * A_BYTES + koff), 1);
+                        for (int k = 0; k < K_STEPS; ++k) {
+                            const uint32_t koff = k * 32;
+                            umma_pair<F16>(d_tmem, smem_desc_sw128(base + koff), smem_desc_sw128(base + 2 * A_BYTES + koff), 1);
                         }
                         // stage free / slab complete, signalled in both CTAs
                         umma_commit_pair(mapa_u32(empty_bar + 8 * stage, 0));
@@ -165,10 +182,12 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
-        for (int pt = cluster_id; pt < pair_tiles && ok; pt += n_clusters) {
+        for (int item = cluster_id; item < n_items && ok; item += n_clusters) {
+            const int pt = item / n_blocks, nb = item - pt * n_blocks;
             const int j = pt * 2 * BM + (int) rank * BM + quarter * 32 + lane;
             const float sdj = j < n ? sd[j] : 0.0f;
-            for (int nb = 0; nb < n_blocks && ok; ++nb) {
+            const float uxj = (F16 && j < n) ? x_unscale[j] : 1.0f;
+            {
                 float sum[COLS_PER_THREAD];
 #pragma unroll
                 for (int c = 0; c < COLS_PER_THREAD; ++c) sum[c] = 0.0f;
@@ -194,7 +213,11 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
 #pragma unroll
                     for (int c = 0; c < COLS_PER_THREAD; ++c) {
                         const int i = i0 + c;
-                        if (i < m) out[(size_t) i * ld_out + j] = epilogue_value<EPI>(fn, sum[c], __ldg(sd_rows + i), sdj);
+                        if (i < m) {
+                            float dot = sum[c];
+                            if constexpr (F16) dot = dot * uxj * __ldg(w_unscale + i);
+                            out[(size_t) i * ld_out + j] = epilogue_value<EPI>(fn, dot, __ldg(sd_rows + i), sdj);
+                        }
                     }
                 }
             }
@@ -214,25 +237,18 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
     if (threadIdx.x == 0 && *abort_flag) atomicMax(status, *abort_flag);
 }
 
-tsvm_status make_map(CUtensorMap *map, const float *ptr, int rows, int d_pad, long long ld, int box_rows);   // dense_tc.cu
+tsvm_status make_map(CUtensorMap *map, const void *ptr, int rows, int row_len, long long ld, int box_rows,
+                     bool f16);   // dense_tc.cu
 
-tsvm_status launch_dense_tc2(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
-    CUtensorMap mxh, mxl, mwh, mwl;
-    TSVM_TRY(make_map(&mxh, km->Xhi, km->n, km->d_pad, km->d_pad, tc2::BM));
-    TSVM_TRY(make_map(&mxl, km->Xlo, km->n, km->d_pad, km->d_pad, tc2::BM));
-    TSVM_TRY(make_map(&mwh, km->Whi, m, km->d_pad, km->d_pad, tc2::BN_HALF));
-    TSVM_TRY(make_map(&mwl, km->Wlo, m, km->d_pad, km->d_pad, tc2::BN_HALF));
-    static int max_clusters = 0;
+template <int EPI, bool F16>
+static tsvm_status launch_pair_kernel(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
+    auto kernel = dense_rows_tc2_kernel<EPI, F16>;
+    static int max_clusters = 0;      // per instantiation
     if (!max_clusters) {
         int dev = 0, sms = 0;
         TSVM_CUDA(cudaGetDevice(&dev));
         TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc2_kernel<EPI_RBF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int) tc2::SMEM_BYTES));
-        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc2_kernel<EPI_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int) tc2::SMEM_BYTES));
-        TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc2_kernel<EPI_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int) tc2::SMEM_BYTES));
+        TSVM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) tc2::SMEM_BYTES));
         cudaLaunchConfig_t probe = {};
         cudaLaunchAttribute pattr[1];
         pattr[0].id = cudaLaunchAttributeClusterDimension;
@@ -240,32 +256,45 @@ tsvm_status launch_dense_tc2(tsvm_km *km, int m, float *out, long long ld_out, c
         probe.gridDim = dim3(sms & ~1); probe.blockDim = dim3(tc2::THREADS); probe.dynamicSmemBytes = tc2::SMEM_BYTES;
         probe.attrs = pattr; probe.numAttrs = 1;
         int nc = 0;
-        if (cudaOccupancyMaxActiveClusters(&nc, dense_rows_tc2_kernel<EPI_RBF>, &probe) != cudaSuccess || nc < 1) {
+        if (cudaOccupancyMaxActiveClusters(&nc, kernel, &probe) != cudaSuccess || nc < 1) {
             cudaGetLastError();
             nc = sms / 2;
         }
         max_clusters = nc;
     }
-    const int pair_tiles = ceil_div(km->n, 2 * tc2::BM);
-    const int clusters = pair_tiles < max_clusters ? pair_tiles : max_clusters;
+    CUtensorMap mxh, mxl, mwh, mwl;
+    const int len = km->plane_ld;
+    TSVM_TRY(make_map(&mxh, km->Xhi, km->n, len, len, tc2::BM, F16));
+    TSVM_TRY(make_map(&mxl, km->Xlo, km->n, len, len, tc2::BM, F16));
+    TSVM_TRY(make_map(&mwh, km->Whi, m, len, len, tc2::BN_HALF, F16));
+    TSVM_TRY(make_map(&mwl, km->Wlo, m, len, len, tc2::BN_HALF, F16));
+    const int n_items = ceil_div(km->n, 2 * tc2::BM) * ceil_div(m, tc2::BN);
+    const int clusters = n_items < max_clusters ? n_items : max_clusters;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(tc2::THREADS); cfg.dynamicSmemBytes = tc2::SMEM_BYTES;
     cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
-#define TC2_LAUNCH(E)                                                                                            \
-    TSVM_CUDA(cudaLaunchKernelEx(&cfg, dense_rows_tc2_kernel<E>, mxh, mxl, mwh, mwl, km->n, m, km->d_pad,           \
-                                 (const float *) km->self_dot, (const float *) km->sd_rows, km->fn, out, ld_out,   \
-                                 km->status_dev))
-    switch (epilogue_kind(km->fn)) {
-        case EPI_RBF: TC2_LAUNCH(EPI_RBF); break;
-        case EPI_LINEAR: TC2_LAUNCH(EPI_LINEAR); break;
-        default: TC2_LAUNCH(EPI_GENERIC); break;
-    }
-#undef TC2_LAUNCH
+    TSVM_CUDA(cudaLaunchKernelEx(&cfg, kernel, mxh, mxl, mwh, mwl, km->n, m, len, (const float *) km->self_dot,
+                                 (const float *) km->sd_rows, (const float *) km->x_unscale,
+                                 (const float *) km->w_unscale, km->fn, out, ld_out, km->status_dev));
     count_launch();
     return TSVM_OK;
+}
+
+// The planes of X (kind 1 = TF32 words, 2 = row-scaled FP16) and of the m requested rows are staged.
+tsvm_status launch_dense_tc2(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
+    TSVM_REQUIRE(km->plane_kind == 1 || km->plane_kind == 2, "tensor engine: operand planes are not built");
+    const int epi = epilogue_kind(km->fn);
+    if (km->plane_kind == 2) {
+        if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, true>(km, m, out, ld_out, st);
+        if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, true>(km, m, out, ld_out, st);
+        return launch_pair_kernel<EPI_GENERIC, true>(km, m, out, ld_out, st);
+    }
+    if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, false>(km, m, out, ld_out, st);
+    if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, false>(km, m, out, ld_out, st);
+    return launch_pair_kernel<EPI_GENERIC, false>(km, m, out, ld_out, st);
 }
 
 }  // namespace tsvm

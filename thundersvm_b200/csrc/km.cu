@@ -2,6 +2,7 @@
 // CSR engine and the CUDA-core dense engine. The tensor-core dense engine lives in
 // dense_tc.cu. Reference behaviour: src/thundersvm/kernelmatrix.cpp:183-316,385-406.
 #include "common.cuh"
+#include <cuda_fp16.h>
 #include <string.h>
 #include <atomic>
 
@@ -91,80 +92,141 @@ __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
     lo = __uint_as_float(l);
 }
 
-// Xhi/Xlo[row * d_pad + k] from X[row * ld + k]; columns d..d_pad-1 are zero.
-__global__ void split_rows_kernel(const float *__restrict__ X, int n, int d, int ld, int d_pad,
-                                  float *__restrict__ hi, float *__restrict__ lo) {
-    size_t total = (size_t) n * d_pad;
-    for (size_t e = (size_t) blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t) gridDim.x * blockDim.x) {
-        int row = (int) (e / d_pad), k = (int) (e % d_pad);
-        float h = 0, l = 0;
-        if (k < d) split_tf32(X[(size_t) row * ld + k], h, l);
-        hi[e] = h;
-        lo[e] = l;
+// Row-scaled FP16 split: the row is multiplied by a power of two that puts its largest magnitude in
+// [2^14, 2^15), then x*scale = hi + lo (+ <= 2^-24 |x*scale|) with hi, lo FP16 (lo may be subnormal:
+// absolute precision 2^-24, i.e. 2^-39 of the row maximum). Products of FP16 values are exact in the
+// tensor core's FP32 accumulator, and the epilogue multiplies the sum by the two rows' 1/scale.
+__device__ __forceinline__ void row_scale_from_max(float amax, float &scale, float &unscale) {
+    const int ex = (int) ((__float_as_uint(amax) >> 23) & 0xffu) - 127;
+    int se = (ex == -127) ? 0 : 14 - ex;          // all-zero (or denormal) rows stay unscaled
+    se = se < -126 ? -126 : (se > 126 ? 126 : se);
+    scale = __uint_as_float((unsigned) (se + 127) << 23);
+    unscale = __uint_as_float((unsigned) (127 - se) << 23);
+}
+
+__device__ __forceinline__ void split_f16(float xs, __half &hi, __half &lo) {
+    hi = __float2half_rn(xs);
+    lo = __float2half_rn(xs - __half2float(hi));
+}
+
+// plane_kind 1: TF32 words; 2: FP16 halves of the scaled value (off counts elements of the plane).
+__device__ __forceinline__ void store_planes(int kind, float *hi, float *lo, size_t off, float v, float scale) {
+    if (kind == 2) {
+        __half h, l;
+        split_f16(v * scale, h, l);
+        reinterpret_cast<__half *>(hi)[off] = h;
+        reinterpret_cast<__half *>(lo)[off] = l;
+    } else {
+        float h, l;
+        split_tf32(v, h, l);
+        hi[off] = h;
+        lo[off] = l;
+    }
+}
+
+// max |v| over the block (every thread calls it once per kernel; blockDim a multiple of 32, <= 1024)
+__device__ __forceinline__ float block_max_abs(float v) {
+    __shared__ unsigned red[32];
+    const unsigned full = 0xffffffffu;
+    unsigned b = __reduce_max_sync(full, __float_as_uint(fabsf(v)));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = b;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    b = (int) (threadIdx.x & 31) < nw ? red[threadIdx.x & 31] : 0u;
+    return __uint_as_float(__reduce_max_sync(full, b));
+}
+
+// Where the staging kernels put a requested row: FP32 W (CUDA-core engine) or the two planes.
+struct RowDst {
+    float *W, *hi, *lo, *unscale;
+    int kind, ld;                  // plane kind (0 = FP32 W) and row length in elements
+};
+
+// Planes of all instances: one warp per row; columns d..pld-1 are zero.
+__global__ void split_rows_kernel(const float *__restrict__ X, int n, int d, int ld, int kind, int pld,
+                                  float *__restrict__ hi, float *__restrict__ lo, float *__restrict__ x_unscale) {
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < n; row += gridDim.x * wpb) {
+        const float *x = X + (size_t) row * ld;
+        float scale = 1.0f, unscale = 1.0f;
+        if (kind == 2) {
+            float amax = 0.0f;
+            for (int k = lane; k < d; k += 32) amax = fmaxf(amax, fabsf(x[k]));
+            amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));
+            row_scale_from_max(amax, scale, unscale);
+            if (lane == 0) x_unscale[row] = unscale;
+        }
+        for (int k = lane; k < pld; k += 32)
+            store_planes(kind, hi, lo, (size_t) row * pld + k, k < d ? x[k] : 0.0f, scale);
     }
 }
 
 // ---- gathering the requested rows ----------------------------------------------------------
 
-// W[i][0..d_pad) = X[idx[i]][0..d) (zero padded); optional TF32 split; sd_rows[i].
-__global__ void gather_rows_dense_kernel(const float *__restrict__ X, int ld, int d, int d_pad,
-                                         const int *__restrict__ idx, int m, const float *__restrict__ sd,
-                                         float *__restrict__ W, float *__restrict__ Whi, float *__restrict__ Wlo,
+// Requested row i = X[idx[i]][0..d) (zero padded to the destination's row length); sd_rows[i].
+__global__ void gather_rows_dense_kernel(const float *__restrict__ X, int ld, int d, const int *__restrict__ idx,
+                                         int m, const float *__restrict__ sd, RowDst dst,
                                          float *__restrict__ sd_rows) {
     int i = blockIdx.x;
     if (i >= m) return;
     int r = idx[i];
     const float *x = X + (size_t) r * ld;
-    for (int k = threadIdx.x; k < d_pad; k += blockDim.x) {
+    float scale = 1.0f, unscale = 1.0f;
+    if (dst.kind == 2) {
+        float amax = 0.0f;
+        for (int k = threadIdx.x; k < d; k += blockDim.x) amax = fmaxf(amax, fabsf(x[k]));
+        row_scale_from_max(block_max_abs(amax), scale, unscale);
+        if (threadIdx.x == 0) dst.unscale[i] = unscale;
+    }
+    for (int k = threadIdx.x; k < dst.ld; k += blockDim.x) {
         float v = k < d ? x[k] : 0.0f;
-        if (W) W[(size_t) i * d_pad + k] = v;
-        if (Whi) {
-            float h, l;
-            split_tf32(v, h, l);
-            Whi[(size_t) i * d_pad + k] = h;
-            Wlo[(size_t) i * d_pad + k] = l;
-        }
+        if (dst.W) dst.W[(size_t) i * dst.ld + k] = v;
+        else store_planes(dst.kind, dst.hi, dst.lo, (size_t) i * dst.ld + k, v, scale);
     }
     if (threadIdx.x == 0) sd_rows[i] = sd[r];
 }
 
 // Same for a batch of new dense instances T (m x dt, stride ldt); features >= d are dropped.
-__global__ void stage_rows_dense_kernel(const float *__restrict__ T, int ldt, int dt, int d, int d_pad, int m,
-                                        float *__restrict__ W, float *__restrict__ Whi, float *__restrict__ Wlo) {
+__global__ void stage_rows_dense_kernel(const float *__restrict__ T, int ldt, int dt, int d, int m, RowDst dst) {
     int i = blockIdx.x;
     if (i >= m) return;
     const float *x = T + (size_t) i * ldt;
-    for (int k = threadIdx.x; k < d_pad; k += blockDim.x) {
-        float v = (k < d && k < dt) ? x[k] : 0.0f;
-        if (W) W[(size_t) i * d_pad + k] = v;
-        if (Whi) {
-            float h, l;
-            split_tf32(v, h, l);
-            Whi[(size_t) i * d_pad + k] = h;
-            Wlo[(size_t) i * d_pad + k] = l;
-        }
+    const int lim = d < dt ? d : dt;
+    float scale = 1.0f, unscale = 1.0f;
+    if (dst.kind == 2) {
+        float amax = 0.0f;
+        for (int k = threadIdx.x; k < lim; k += blockDim.x) amax = fmaxf(amax, fabsf(x[k]));
+        row_scale_from_max(block_max_abs(amax), scale, unscale);
+        if (threadIdx.x == 0) dst.unscale[i] = unscale;
+    }
+    for (int k = threadIdx.x; k < dst.ld; k += blockDim.x) {
+        float v = k < lim ? x[k] : 0.0f;
+        if (dst.W) dst.W[(size_t) i * dst.ld + k] = v;
+        else store_planes(dst.kind, dst.hi, dst.lo, (size_t) i * dst.ld + k, v, scale);
     }
 }
 
-// CSR rows -> zero-initialised dense W (row-major) for the dense engines.
+// CSR rows -> zero-initialised dense rows for the dense engines.
 __global__ void scatter_csr_to_w_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr,
                                         const int *__restrict__ col, const int *__restrict__ idx, int m, int d,
-                                        int d_pad, float *__restrict__ W, float *__restrict__ Whi,
-                                        float *__restrict__ Wlo) {
+                                        RowDst dst) {
     int i = blockIdx.x;
     if (i >= m) return;
     int r = idx ? idx[i] : i;
+    float scale = 1.0f, unscale = 1.0f;
+    if (dst.kind == 2) {
+        float amax = 0.0f;
+        for (int p = row_ptr[r] + threadIdx.x; p < row_ptr[r + 1]; p += blockDim.x)
+            if (col[p] < d) amax = fmaxf(amax, fabsf(val[p]));
+        row_scale_from_max(block_max_abs(amax), scale, unscale);
+        if (threadIdx.x == 0) dst.unscale[i] = unscale;
+    }
     for (int p = row_ptr[r] + threadIdx.x; p < row_ptr[r + 1]; p += blockDim.x) {
         int c = col[p];
         if (c >= d) continue;
         float v = val[p];
-        if (W) W[(size_t) i * d_pad + c] = v;
-        if (Whi) {
-            float h, l;
-            split_tf32(v, h, l);
-            Whi[(size_t) i * d_pad + c] = h;
-            Wlo[(size_t) i * d_pad + c] = l;
-        }
+        if (dst.W) dst.W[(size_t) i * dst.ld + c] = v;
+        else store_planes(dst.kind, dst.hi, dst.lo, (size_t) i * dst.ld + c, v, scale);
     }
 }
 
@@ -315,10 +377,13 @@ static tsvm_status ensure_scratch(tsvm_km *km, int m) {
     int cap = 128;
     while (cap < m) cap *= 2;
     cudaFree(km->W); cudaFree(km->Whi); cudaFree(km->Wlo); cudaFree(km->WT); cudaFree(km->sd_rows);
-    km->W = km->Whi = km->Wlo = km->WT = km->sd_rows = nullptr;
+    cudaFree(km->w_unscale);
+    km->W = km->Whi = km->Wlo = km->WT = km->sd_rows = km->w_unscale = nullptr;
     km->w_cap = 0;
     TSVM_TRY(dev_alloc(&km->sd_rows, (size_t) cap));
     if (km->dense) {
+        // either plane kind fits cap x d_pad words: round_up(d, 8) halves <= d_pad floats
+        TSVM_TRY(dev_alloc(&km->w_unscale, (size_t) cap));
         TSVM_TRY(dev_alloc(&km->W, (size_t) cap * km->d_pad));
         TSVM_TRY(dev_alloc(&km->Whi, (size_t) cap * km->d_pad));
         TSVM_TRY(dev_alloc(&km->Wlo, (size_t) cap * km->d_pad));
@@ -329,6 +394,42 @@ static tsvm_status ensure_scratch(tsvm_km *km, int m) {
     }
     km->w_cap = cap;
     return TSVM_OK;
+}
+
+// engine: 0 = automatic, 1 = CUDA cores, 2 / 3 = tensor cores on TF32 planes (one CTA per tile / CTA
+// pairs), 4 = tensor cores on row-scaled FP16 planes (CTA pairs; what "automatic" picks for d_pad > 32)
+static inline bool use_tensor_engine(const tsvm_km *km) {
+    return km->engine >= 2 || (km->engine == 0 && km->d_pad > 32);
+}
+static inline int wanted_plane_kind(const tsvm_km *km) {
+    if (!km->dense || !use_tensor_engine(km)) return 0;
+    return (km->engine == 2 || km->engine == 3) ? 1 : 2;
+}
+
+// Builds the planes the selected engine reads, once; a change of engine rebuilds them.
+static tsvm_status ensure_planes(tsvm_km *km, cudaStream_t st) {
+    const int kind = wanted_plane_kind(km);
+    if (kind == 0 || kind == km->plane_kind) return TSVM_OK;
+    cudaFree(km->Xhi); cudaFree(km->Xlo);
+    km->Xhi = km->Xlo = nullptr;
+    km->plane_kind = 0;
+    km->plane_ld = kind == 1 ? km->d_pad : (km->d + 7) & ~7;
+    const size_t words = kind == 1 ? (size_t) km->n * km->plane_ld : ((size_t) km->n * km->plane_ld + 1) / 2;
+    TSVM_TRY(dev_alloc(&km->Xhi, words));
+    TSVM_TRY(dev_alloc(&km->Xlo, words));
+    if (!km->x_unscale) TSVM_TRY(dev_alloc(&km->x_unscale, (size_t) km->n));
+    TSVM_LAUNCH(split_rows_kernel, 148 * 8, 256, 0, st, km->X, km->n, km->d, km->ldx, kind, km->plane_ld, km->Xhi,
+                km->Xlo, km->x_unscale);
+    km->plane_kind = kind;
+    return TSVM_OK;
+}
+
+static inline RowDst row_dst(const tsvm_km *km) {
+    if (use_tensor_engine(km)) return RowDst{nullptr, km->Whi, km->Wlo, km->w_unscale, km->plane_kind, km->plane_ld};
+    return RowDst{km->W, nullptr, nullptr, nullptr, 0, km->d_pad};
+}
+static inline size_t row_dst_bytes(const RowDst &r, int m) {
+    return (size_t) m * r.ld * (r.kind == 2 ? sizeof(__half) : sizeof(float));
 }
 
 static tsvm_status finish_create(tsvm_km *km, cudaStream_t st) {
@@ -343,18 +444,7 @@ static tsvm_status finish_create(tsvm_km *km, cudaStream_t st) {
     else
         TSVM_LAUNCH(self_dot_csr_kernel, blocks, 256, 0, st, km->val, km->row_ptr, km->n, km->self_dot);
     TSVM_LAUNCH(diag_kernel, ceil_div(km->n, 256), 256, 0, st, km->self_dot, km->n, km->fn, km->diag);
-    if (km->dense) {
-        TSVM_TRY(dev_alloc(&km->Xhi, (size_t) km->n * km->d_pad));
-        TSVM_TRY(dev_alloc(&km->Xlo, (size_t) km->n * km->d_pad));
-        TSVM_LAUNCH(split_rows_kernel, 148 * 8, 256, 0, st, km->X, km->n, km->d, km->ldx, km->d_pad, km->Xhi,
-                    km->Xlo);
-    }
-    return TSVM_OK;
-}
-
-// engine: 0 = automatic, 1 = CUDA cores, 2 = tensor cores (one CTA per tile), 3 = tensor cores (CTA pairs)
-static inline bool use_tensor_engine(const tsvm_km *km) {
-    return km->engine >= 2 || (km->engine == 0 && km->d_pad > 32);
+    return ensure_planes(km, st);
 }
 
 static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
@@ -465,7 +555,7 @@ tsvm_status tsvm_km_create_csr(const float *val, const int *row_ptr, const int *
 
 void tsvm_km_destroy(tsvm_km *km) {
     if (!km) return;
-    cudaFree(km->X_owned); cudaFree(km->Xhi); cudaFree(km->Xlo);
+    cudaFree(km->X_owned); cudaFree(km->Xhi); cudaFree(km->Xlo); cudaFree(km->x_unscale); cudaFree(km->w_unscale);
     cudaFree(km->val_owned); cudaFree(km->row_ptr_owned); cudaFree(km->col_owned);
     cudaFree(km->self_dot); cudaFree(km->diag);
     cudaFree(km->W); cudaFree(km->Whi); cudaFree(km->Wlo); cudaFree(km->WT); cudaFree(km->sd_rows);
@@ -482,7 +572,7 @@ const float *tsvm_km_diag_dev(const tsvm_km *km) { return km ? km->diag : nullpt
 const float *tsvm_km_self_dot_dev(const tsvm_km *km) { return km ? km->self_dot : nullptr; }
 
 tsvm_status tsvm_km_set_dense_engine(tsvm_km *km, int engine) {
-    TSVM_REQUIRE(km && engine >= 0 && engine <= 3, "set_dense_engine: bad arguments");
+    TSVM_REQUIRE(km && engine >= 0 && engine <= 4, "set_dense_engine: bad arguments");
     km->engine = engine;
     return TSVM_OK;
 }
@@ -493,9 +583,9 @@ tsvm_status tsvm_km_rows_by_index(tsvm_km *km, const int *idx_dev, int q, float 
     cudaStream_t st = (cudaStream_t) stream;
     TSVM_TRY(ensure_scratch(km, q));
     if (km->dense) {
-        const bool tc = use_tensor_engine(km);
-        TSVM_LAUNCH(gather_rows_dense_kernel, q, 256, 0, st, km->X, km->ldx, km->d, km->d_pad, idx_dev, q,
-                    km->self_dot, tc ? nullptr : km->W, tc ? km->Whi : nullptr, tc ? km->Wlo : nullptr, km->sd_rows);
+        TSVM_TRY(ensure_planes(km, st));
+        TSVM_LAUNCH(gather_rows_dense_kernel, q, 256, 0, st, km->X, km->ldx, km->d, idx_dev, q, km->self_dot,
+                    row_dst(km), km->sd_rows);
         return rows_common(km, q, out_dev, ld_out, st);
     }
     TSVM_REQUIRE(q <= 1024, "CSR engine handles at most 1024 rows per call, got %d", q);
@@ -520,9 +610,8 @@ tsvm_status tsvm_km_rows_by_instances_dense(tsvm_km *km, const float *T_dev, int
         TSVM_TRY(ensure_scratch(km, mm));
         TSVM_LAUNCH(self_dot_seq_dense_kernel, ceil_div(mm, 128), 128, 0, st, T, mm, dt, ldt, km->sd_rows);
         if (km->dense) {
-            const bool tc = use_tensor_engine(km);
-            TSVM_LAUNCH(stage_rows_dense_kernel, mm, 256, 0, st, T, ldt, dt, km->d, km->d_pad, mm,
-                        tc ? nullptr : km->W, tc ? km->Whi : nullptr, tc ? km->Wlo : nullptr);
+            TSVM_TRY(ensure_planes(km, st));
+            TSVM_LAUNCH(stage_rows_dense_kernel, mm, 256, 0, st, T, ldt, dt, km->d, mm, row_dst(km));
             TSVM_TRY(rows_common(km, mm, o, ld_out, st));
         } else {
             dim3 grid(ceil_div(km->d, 32), ceil_div(mm, 32)), block(32, 8);
@@ -545,9 +634,9 @@ tsvm_status tsvm_km_rows_for_features_dense(tsvm_km *km, const float *T_dev, int
         const int mm = min(4096, m - r0);
         TSVM_TRY(ensure_scratch(km, mm));
         TSVM_CUDA(cudaMemcpyAsync(km->sd_rows, sd_T_dev + r0, sizeof(float) * mm, cudaMemcpyDeviceToDevice, st));
-        const bool tc = use_tensor_engine(km);
-        TSVM_LAUNCH(stage_rows_dense_kernel, mm, 256, 0, st, T_dev + (size_t) r0 * ldt, ldt, km->d, km->d, km->d_pad, mm,
-                    tc ? nullptr : km->W, tc ? km->Whi : nullptr, tc ? km->Wlo : nullptr);
+        TSVM_TRY(ensure_planes(km, st));
+        TSVM_LAUNCH(stage_rows_dense_kernel, mm, 256, 0, st, T_dev + (size_t) r0 * ldt, ldt, km->d, km->d, mm,
+                    row_dst(km));
         TSVM_TRY(rows_common(km, mm, out_dev + (size_t) r0 * ld_out, ld_out, st));
     }
     return TSVM_OK;
@@ -567,13 +656,15 @@ tsvm_status tsvm_km_rows_by_instances_csr(tsvm_km *km, const float *tval_dev, co
         TSVM_TRY(ensure_scratch(km, mm));
         TSVM_LAUNCH(self_dot_seq_csr_kernel, ceil_div(mm, 128), 128, 0, st, tval_dev, rp, mm, km->sd_rows);
         if (km->dense) {
-            const bool tc = use_tensor_engine(km);
-            if (tc) {
-                TSVM_CUDA(cudaMemsetAsync(km->Whi, 0, sizeof(float) * (size_t) mm * km->d_pad, st));
-                TSVM_CUDA(cudaMemsetAsync(km->Wlo, 0, sizeof(float) * (size_t) mm * km->d_pad, st));
-            } else TSVM_CUDA(cudaMemsetAsync(km->W, 0, sizeof(float) * (size_t) mm * km->d_pad, st));
+            TSVM_TRY(ensure_planes(km, st));
+            const RowDst dst = row_dst(km);
+            if (dst.W) TSVM_CUDA(cudaMemsetAsync(dst.W, 0, row_dst_bytes(dst, mm), st));
+            else {
+                TSVM_CUDA(cudaMemsetAsync(dst.hi, 0, row_dst_bytes(dst, mm), st));
+                TSVM_CUDA(cudaMemsetAsync(dst.lo, 0, row_dst_bytes(dst, mm), st));
+            }
             TSVM_LAUNCH(scatter_csr_to_w_kernel, mm, 128, 0, st, tval_dev, rp, tcol_dev, (const int *) nullptr, mm,
-                        km->d, km->d_pad, tc ? nullptr : km->W, tc ? km->Whi : nullptr, tc ? km->Wlo : nullptr);
+                        km->d, dst);
             TSVM_TRY(rows_common(km, mm, o, ld_out, st));
         } else {
             TSVM_LAUNCH(scatter_csr_to_wt_kernel, mm, 128, 0, st, tval_dev, rp, tcol_dev, (const int *) nullptr, mm,
