@@ -17,6 +17,10 @@
 // destination CTA; every load is addressed to one CTA's shared memory only. Every mbarrier wait is bounded.
 #include "tc_common.cuh"
 
+#ifndef TSVM_PROMO
+#define TSVM_PROMO 2
+#endif
+
 namespace tsvm {
 
 namespace tc2 {
@@ -26,8 +30,13 @@ constexpr int BM = 128, BN = 256, BN_HALF = 128, STAGES = 3, K_STEPS = 4;
 constexpr uint32_t A_BYTES = BM * 128;               // 16 KB per plane (this CTA's instances)
 constexpr uint32_t B_BYTES = BN_HALF * 128;          // 16 KB per plane (this CTA's half of the requested rows)
 constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // 64 KB per CTA
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int THREADS = 320, EPI_WARPS = 8, COLS_PER_THREAD = 128;
+// epilogue staging (see the epilogue): EPI_CHUNK sums of each of the 256 epilogue threads, and per warp the
+// self dots and 1/scale of its 128 requested rows
+constexpr int EPI_CHUNK = 16;
+constexpr uint32_t EPI_STAGE_BYTES = EPI_CHUNK * EPI_WARPS * 32 * 4;
+constexpr uint32_t EPI_CONST_BYTES = EPI_WARPS * 2 * COLS_PER_THREAD * 4;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_STAGE_BYTES + EPI_CONST_BYTES;
 constexpr uint32_t TMEM_COLS = 512;
 // D=F32, K-major, N=256, M=256 (two CTAs x 128); A=B=TF32 (format 2) or F16 (format 0)
 constexpr uint32_t IDESC_SHAPE = (1u << 4) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
@@ -78,6 +87,14 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
 }
 
+// sums [CH * EPI_CHUNK, (CH + 1) * EPI_CHUNK) of the thread -> its private column of the staging block
+template <int CH>
+__device__ __forceinline__ void stage_chunk(const float (&sum)[tc2::COLS_PER_THREAD], float *priv) {
+    static_assert(tc2::COLS_PER_THREAD / tc2::EPI_CHUNK == 8, "the epilogue's switch lists eight chunks");
+#pragma unroll
+    for (int c = 0; c < tc2::EPI_CHUNK; ++c) priv[c * (tc2::EPI_WARPS * 32)] = sum[CH * tc2::EPI_CHUNK + c];
+}
+
 template <int EPI, bool F16>
 __global__ void __launch_bounds__(tc2::THREADS, 1)
 dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
@@ -87,6 +104,7 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                       KernelFn fn, float *__restrict__ out, long long ld_out, int *__restrict__ status) {
     using namespace tc2;
     constexpr int BK = F16 ? 64 : 32;          // elements per k slab
+    constexpr int PROMO = F16 ? TSVM_PROMO : 1;   // k slabs summed in tensor memory before the FP32 promotion
     extern __shared__ uint8_t smem_raw[];
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
@@ -150,7 +168,8 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
             bool ok = true;
             for (int item = cluster_id; item < n_items && ok; item += n_clusters)
                     for (int kb = 0; kb < k_blocks; ++kb) {
-                        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, 2)) { ok = false; break; }
+                        const bool unit_start = kb % PROMO == 0, unit_end = kb % PROMO == PROMO - 1 || kb == k_blocks - 1;
+                        if (unit_start && !mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, 2)) { ok = false; break; }
                         if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
                         tc_fence_after();
                         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -159,7 +178,7 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                         for (int k = 0; k < K_STEPS; ++k) {
                             const uint32_t koff = k * 32;
                             umma_pair<F16>(d_tmem, smem_desc_sw128(base + A_BYTES + koff),
-                                           smem_desc_sw128(base + 2 * A_BYTES + koff), k != 0);
+                                           smem_desc_sw128(base + 2 * A_BYTES + koff), k != 0 || !unit_start);
                             umma_pair<F16>(d_tmem, smem_desc_sw128(base + koff),
                                            smem_desc_sw128(base + 2 * A_BYTES + B_BYTES + koff), 1);
                         }
@@ -171,15 +190,20 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                         // stage free / slab complete, signalled in both CTAs
                         umma_commit_pair(mapa_u32(empty_bar + 8 * stage, 0));
                         umma_commit_pair(mapa_u32(empty_bar + 8 * stage, 1));
-                        umma_commit_pair(mapa_u32(tfull_bar + 8 * acc, 0));
-                        umma_commit_pair(mapa_u32(tfull_bar + 8 * acc, 1));
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
-                        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                        if (unit_end) {
+                            umma_commit_pair(mapa_u32(tfull_bar + 8 * acc, 0));
+                            umma_commit_pair(mapa_u32(tfull_bar + 8 * acc, 1));
+                            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                        }
                     }
         }
     } else {
         // ---------------- slab promotion + epilogue (both CTAs, own 128 instances) ----------------
         const int quarter = warp & 3, half = (warp - 2) >> 2;
+        float *priv = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256) + (warp - 2) * 32 + lane;
+        float *rowc = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES) +
+                      (warp - 2) * 2 * COLS_PER_THREAD;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         for (int item = cluster_id; item < n_items && ok; item += n_clusters) {
@@ -188,10 +212,22 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
             const float sdj = j < n ? sd[j] : 0.0f;
             const float uxj = (F16 && j < n) ? x_unscale[j] : 1.0f;
             {
+                // Self dot and 1/scale of this warp's 128 requested rows go to shared memory by asynchronous
+                // copies while the k loop runs: with nearly all of the SM's memory configured as shared, the
+                // L1 left over does not keep them across the epilogue's stores.
+                const int i0 = nb * BN + half * COLS_PER_THREAD;
+#pragma unroll
+                for (int c = lane; c < COLS_PER_THREAD; c += 32) {
+                    if (i0 + c < m) {
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(rowc + c)), "l"(sd_rows + i0 + c) : "memory");
+                        if constexpr (F16)
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(rowc + COLS_PER_THREAD + c)), "l"(w_unscale + i0 + c) : "memory");
+                    }
+                }
                 float sum[COLS_PER_THREAD];
 #pragma unroll
                 for (int c = 0; c < COLS_PER_THREAD; ++c) sum[c] = 0.0f;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int unit = 0; unit < (k_blocks + PROMO - 1) / PROMO; ++unit) {
                     if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + ((uint32_t) (quarter * 32) << 16) + acc * BN + half * COLS_PER_THREAD;
@@ -208,18 +244,38 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                     if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 }
                 if (!ok) break;
-                if (j < n) {
-                    const int i0 = nb * BN + half * COLS_PER_THREAD;
-#pragma unroll
-                    for (int c = 0; c < COLS_PER_THREAD; ++c) {
-                        const int i = i0 + c;
-                        if (i < m) {
-                            float dot = sum[c];
-                            if constexpr (F16) dot = dot * uxj * __ldg(w_unscale + i);
-                            out[(size_t) i * ld_out + j] = epilogue_value<EPI>(fn, dot, __ldg(sd_rows + i), sdj);
+                // The sums live in registers, so a loop over them has to be fully unrolled; with the kernel
+                // function in its body that is 128 copies of it, and the instruction fetch of such an
+                // epilogue cost several times its arithmetic. Instead the sums pass 32 at a time through a
+                // thread-private column of shared memory (no synchronisation: every thread reads back only
+                // what it wrote), 16 at a time, and a short rolled loop applies the kernel function and stores.
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                __syncwarp();
+#pragma unroll 1
+                for (int ch = 0; ch < COLS_PER_THREAD / EPI_CHUNK; ++ch) {
+                    switch (ch) {           // register indices must be constants: one short case per chunk
+                        case 0: stage_chunk<0>(sum, priv); break;
+                        case 1: stage_chunk<1>(sum, priv); break;
+                        case 2: stage_chunk<2>(sum, priv); break;
+                        case 3: stage_chunk<3>(sum, priv); break;
+                        case 4: stage_chunk<4>(sum, priv); break;
+                        case 5: stage_chunk<5>(sum, priv); break;
+                        case 6: stage_chunk<6>(sum, priv); break;
+                        default: stage_chunk<7>(sum, priv); break;
+                    }
+                    if (j < n) {
+                        const int cbase = ch * EPI_CHUNK;
+                        const int lim = m - (i0 + cbase) < EPI_CHUNK ? m - (i0 + cbase) : EPI_CHUNK;
+                        float *o = out + (size_t) (i0 + cbase) * ld_out + j;
+#pragma unroll 8
+                        for (int c = 0; c < lim; ++c) {
+                            float dot = priv[c * (EPI_WARPS * 32)];
+                            if constexpr (F16) dot = dot * uxj * rowc[COLS_PER_THREAD + cbase + c];
+                            o[(size_t) c * ld_out] = epilogue_value<EPI>(fn, dot, rowc[cbase + c], sdj);
                         }
                     }
                 }
+                __syncwarp();          // the next item's copies overwrite rowc
             }
         }
     }

@@ -31,11 +31,14 @@ def main():
     ap.add_argument("--q", type=int, default=512)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--d", type=int, default=2000, help="features of the dense cases")
+    ap.add_argument("--engine", default="auto", help="dense engine: auto, simt, tensor1, tensor2, tensor")
     args = ap.parse_args()
     capi.lib()
     if args.case in ("dense_rows", "solver"):
-        prob = synth.config5(args.rows)
+        prob = synth.config5(args.rows, d=args.d)
         km = capi.KernelMatrix(dense=torch.from_numpy(prob["X"]).cuda(), gamma=prob["gamma"])
+        km.set_dense_engine(args.engine)
     else:
         prob = synth.config4(args.rows)
         val, rp, col = prob["csr"]
