@@ -153,6 +153,13 @@ tsvm_status tsvm_solver_iterate(tsvm_solver *solver, int n_iters, int *done_host
 tsvm_status tsvm_solver_finish(tsvm_solver *solver, double *rho_host, tsvm_solve_stats *stats_host);
 /* Counters and phase times so far (objective is not evaluated: NaN). */
 tsvm_status tsvm_solver_get_stats(const tsvm_solver *solver, tsvm_solve_stats *stats_host);
+/* Switches the overlapped outer iteration on (default) or off. Overlapped, the q full kernel rows are
+ * computed on the caller's stream while the local solver runs on an internal second stream, fed by a
+ * small extra launch that computes the q new rows of the ws x ws block first; it applies to dense data on
+ * the CTA-pair tensor engine and gives bit-identical results (the block's values are computed by the same
+ * arithmetic either way). No counterpart in the reference, whose steps run one after the other
+ * (csmosolver.cpp:59-120). */
+tsvm_status tsvm_solver_set_overlap(tsvm_solver *solver, int enable);
 void tsvm_solver_destroy(tsvm_solver *solver);
 
 /* The 13 partial reductions rho and the objective are made of (csmosolver.cpp:167-187,227-239;

@@ -170,6 +170,44 @@ def test_solve_matches_oracle_and_reference_fixture(capi, golden_dir, tag):
     assert stats["outer_iters"] >= 1 and stats["gpu_launches"] > 0
 
 
+@pytest.mark.parametrize("solver", ["c", "nu_svc"])
+def test_overlapped_iteration_is_bit_identical(capi, solver):
+    """The overlapped outer iteration (local solver on a second stream, fed by a small launch that computes
+    the new rows of the working-set block) must reproduce the sequential one bit for bit: same alpha, f and
+    stopping point on a dense problem that runs on the tensor engine, several outer iterations long."""
+    import torch
+    prob = synth.config5(6000, d=200)
+    y = np.where(prob["y"] > 0, 1, -1).astype(np.int32)
+    n = len(y)
+    out = []
+    for overlap in (False, True):
+        km = capi.KernelMatrix(dense=torch.from_numpy(prob["X"]).cuda(), gamma=prob["gamma"])
+        alpha = torch.zeros(n, dtype=torch.float64, device="cuda")
+        if solver == "nu_svc":
+            a0 = np.zeros(n)
+            for cls in (1, -1):
+                idx = np.nonzero(y == cls)[0]
+                budget = 0.3 * n / 2
+                full = int(budget)
+                a0[idx[:full]] = 1.0
+                a0[idx[full]] = budget - full
+            alpha = torch.from_numpy(a0).cuda()
+            f = torch.zeros(n, dtype=torch.float64, device="cuda")
+        else:
+            f = torch.from_numpy(-y.astype(np.float64)).cuda()
+        sv = capi.Solver(km, torch.from_numpy(y).cuda(), alpha, f, 1e-3, 1.0, 1.0, 1024, solver=solver)
+        sv.set_overlap(overlap)
+        sv.iterate(12)
+        st = sv.stats()
+        out.append((alpha.cpu().numpy().copy(), f.cpu().numpy().copy(), st["outer_iters"], st["local_iters"]))
+        sv.close()
+        km.close()
+    assert out[0][2] == out[1][2] and out[0][3] == out[1][3]
+    assert np.array_equal(out[0][0], out[1][0])
+    assert np.array_equal(out[0][1], out[1][1])
+    assert out[0][2] >= 3
+
+
 def test_solve_first_working_sets_follow_the_oracle(capi):
     """With max_iter = 0 the solver runs exactly one outer iteration (csmosolver.cpp:110); alpha and f
     after it must agree with the oracle closely (same working set, same local iterations)."""

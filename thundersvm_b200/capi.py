@@ -23,7 +23,7 @@ EXPORTS = [
     "tsvm_km_n_instances", "tsvm_km_n_features", "tsvm_km_nnz", "tsvm_km_is_dense", "tsvm_km_diag_dev",
     "tsvm_km_self_dot_dev", "tsvm_km_rows_by_index", "tsvm_km_rows_by_instances_dense",
     "tsvm_km_rows_by_instances_csr", "tsvm_km_rows_for_features_dense", "tsvm_km_set_dense_engine", "tsvm_rho_partials", "tsvm_smo_solve", "tsvm_solver_create",
-    "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_destroy", "tsvm_working_set_size",
+    "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_set_overlap", "tsvm_solver_destroy", "tsvm_working_set_size",
     "tsvm_ws_create", "tsvm_ws_destroy", "tsvm_ws_candidates", "tsvm_ws_merge", "tsvm_select_working_set",
     "tsvm_select_working_set_static",
     "tsvm_local_smo", "tsvm_update_f", "tsvm_predict_dec", "tsvm_vote",
@@ -83,6 +83,7 @@ def lib():
     L.tsvm_solver_iterate.argtypes = [vp, i, C.POINTER(i)]
     L.tsvm_solver_finish.argtypes = [vp, C.POINTER(d), C.POINTER(SolveStats)]
     L.tsvm_solver_get_stats.argtypes = [vp, C.POINTER(SolveStats)]
+    L.tsvm_solver_set_overlap.argtypes = [vp, i]
     L.tsvm_solver_destroy.argtypes = [vp]
     L.tsvm_solver_destroy.restype = None
     L.tsvm_working_set_size.argtypes = [i, i, sz, sz]
@@ -263,6 +264,9 @@ class Solver:
         done = C.c_int(0)
         check(lib().tsvm_solver_iterate(self._h, n_iters, C.byref(done)))
         return bool(done.value)
+
+    def set_overlap(self, enable):
+        check(lib().tsvm_solver_set_overlap(self._h, 1 if enable else 0))
 
     def stats(self):
         st = SolveStats()

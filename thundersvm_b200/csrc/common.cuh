@@ -141,6 +141,13 @@ __device__ __forceinline__ float apply_kernel(const KernelFn &k, float dot, floa
 
 }  // namespace tsvm
 
+// A set of instances as the tensor engines read it: two operand planes (row stride = the handle's plane_ld),
+// self dots and, for FP16 planes, 1/scale of every row.
+struct InstancePlanes {
+    const float *hi, *lo, *sd, *unscale;
+    int n;
+};
+
 // Opaque handle behind tsvm_km.
 struct tsvm_km {
     int n = 0, d = 0;
@@ -174,6 +181,19 @@ struct tsvm_km {
     float *WT = nullptr;            // CSR engine: d x wt_ld, column = requested row
     int wt_ld = 0;
     float *sd_rows = nullptr;       // self dots of the requested rows [w_cap]
+    int reserve_clusters = 0;       // SM pairs the pair engine leaves free (a concurrent stream's kernels run there)
     int *status_dev = nullptr;      // device status word written by kernels with bounded waits
     int *status_host = nullptr;     // pinned mirror
 };
+
+namespace tsvm {
+// Pieces of tsvm_km_rows_by_index (km.cu) for callers that overlap them with other work.
+bool km_pair_engine(tsvm_km *km, cudaStream_t st);
+size_t km_plane_row_bytes(const tsvm_km *km);
+tsvm_status km_stage_rows_by_index(tsvm_km *km, const int *idx_dev, int q, cudaStream_t st);
+tsvm_status km_rows_staged(tsvm_km *km, int q, float *out, long long ld_out, cudaStream_t st);
+tsvm_status km_gather_planes(tsvm_km *km, const int *ids_dev, int m, float *hi, float *lo, float *sd, float *unscale,
+                             cudaStream_t st);
+tsvm_status km_rows_staged_on(tsvm_km *km, const InstancePlanes &X, int q, float *out, long long ld_out,
+                              cudaStream_t st);
+}  // namespace tsvm

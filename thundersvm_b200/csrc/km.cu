@@ -264,6 +264,25 @@ __global__ void transpose_dense_to_wt_kernel(const float *__restrict__ T, int ld
     }
 }
 
+// Operand planes, self dots and 1/scale of the instances ids[0..m) copied out of the kernel matrix's planes
+// (row_bytes a multiple of 16).
+__global__ void gather_planes_kernel(const float *__restrict__ Xhi, const float *__restrict__ Xlo, size_t row_bytes,
+                                     const int *__restrict__ ids, int m, const float *__restrict__ sd,
+                                     const float *__restrict__ x_unscale, float *__restrict__ hi,
+                                     float *__restrict__ lo, float *__restrict__ sd_out,
+                                     float *__restrict__ unscale_out) {
+    const int i = blockIdx.x;
+    if (i >= m) return;
+    const int r = ids[i];
+    const size_t vecs = row_bytes / 16;
+    const uint4 *sh = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(Xhi) + (size_t) r * row_bytes);
+    const uint4 *sl = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(Xlo) + (size_t) r * row_bytes);
+    uint4 *dh = reinterpret_cast<uint4 *>(reinterpret_cast<char *>(hi) + (size_t) i * row_bytes);
+    uint4 *dl = reinterpret_cast<uint4 *>(reinterpret_cast<char *>(lo) + (size_t) i * row_bytes);
+    for (size_t v = threadIdx.x; v < vecs; v += blockDim.x) { dh[v] = sh[v]; dl[v] = sl[v]; }
+    if (threadIdx.x == 0) { sd_out[i] = sd[r]; unscale_out[i] = x_unscale ? x_unscale[r] : 1.0f; }
+}
+
 // ---- CUDA-core dense engine: out[i][j] = kfn(sum_k W[i][k] X[j][k]) -------------------------
 // 64 instances x 64 requested rows per block, 16-wide k slabs, 4x4 outputs per thread.
 __global__ void __launch_bounds__(256)
@@ -473,6 +492,46 @@ static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out,
     else { set_error("CSR engine handles at most 1024 rows per call, got %d", m); return TSVM_ERR_INVALID; }
 #undef CSR_CASE
     return TSVM_OK;
+}
+
+// ---- pieces of tsvm_km_rows_by_index for callers that overlap them (the solver) -------------------
+
+tsvm_status launch_dense_tc2_on(tsvm_km *km, const InstancePlanes &X, int m, float *out, long long ld_out,
+                                cudaStream_t st);   // dense_tc2.cu
+
+// True when kernel rows of this matrix run on the CTA-pair tensor engine, whose requested-row staging and
+// launch can be issued separately and against a caller-chosen subset of instances.
+bool km_pair_engine(tsvm_km *km, cudaStream_t st) {
+    if (!km->dense || !use_tensor_engine(km) || km->engine == 2) return false;
+    return ensure_planes(km, st) == TSVM_OK && km->plane_kind != 0;
+}
+
+size_t km_plane_row_bytes(const tsvm_km *km) {
+    return (size_t) km->plane_ld * (km->plane_kind == 2 ? sizeof(__half) : sizeof(float));
+}
+
+tsvm_status km_stage_rows_by_index(tsvm_km *km, const int *idx_dev, int q, cudaStream_t st) {
+    TSVM_TRY(ensure_scratch(km, q));
+    TSVM_TRY(ensure_planes(km, st));
+    TSVM_LAUNCH(gather_rows_dense_kernel, q, 256, 0, st, km->X, km->ldx, km->d, idx_dev, q, km->self_dot, row_dst(km),
+                km->sd_rows);
+    return TSVM_OK;
+}
+
+tsvm_status km_rows_staged(tsvm_km *km, int q, float *out, long long ld_out, cudaStream_t st) {
+    return rows_common(km, q, out, ld_out, st);
+}
+
+tsvm_status km_gather_planes(tsvm_km *km, const int *ids_dev, int m, float *hi, float *lo, float *sd, float *unscale,
+                             cudaStream_t st) {
+    TSVM_LAUNCH(gather_planes_kernel, m, 128, 0, st, km->Xhi, km->Xlo, km_plane_row_bytes(km), ids_dev, m,
+                km->self_dot, km->plane_kind == 2 ? km->x_unscale : nullptr, hi, lo, sd, unscale);
+    return TSVM_OK;
+}
+
+tsvm_status km_rows_staged_on(tsvm_km *km, const InstancePlanes &X, int q, float *out, long long ld_out,
+                              cudaStream_t st) {
+    return launch_dense_tc2_on(km, X, q, out, ld_out, st);
 }
 
 }  // namespace tsvm

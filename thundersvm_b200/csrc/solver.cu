@@ -511,10 +511,14 @@ __global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *
                                  const int *__restrict__ y, const double *__restrict__ f,
                                  const double *__restrict__ alpha, float *__restrict__ kww,
                                  float *__restrict__ diag_ws, int *__restrict__ y_ws, double *__restrict__ f_ws,
-                                 double *__restrict__ alpha_ws) {
+                                 double *__restrict__ alpha_ws, int block_rows) {
     const int a = blockIdx.x;                      // logical slot of the row
-    const float *row = rows + (size_t) phys_row(a, q, first_half_phys) * ld;
-    for (int b = threadIdx.x; b < ws; b += blockDim.x) kww[(size_t) a * ws + b] = row[ids[b]];
+    // rows >= block_rows of the block are written by someone else (the overlapped iteration computes them
+    // directly); the slot vectors are gathered for every slot
+    if (a < block_rows) {
+        const float *row = rows + (size_t) phys_row(a, q, first_half_phys) * ld;
+        for (int b = threadIdx.x; b < ws; b += blockDim.x) kww[(size_t) a * ws + b] = row[ids[b]];
+    }
     if (threadIdx.x == 0) {
         const int id = ids[a];
         diag_ws[a] = diag[id]; y_ws[a] = y[id]; f_ws[a] = f[id]; alpha_ws[a] = alpha[id];
@@ -858,6 +862,11 @@ struct tsvm_solver {
     tsvm_ws *sel = nullptr;
     double *diff_host = nullptr;
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    // overlapped iteration: second stream, fork / local-solver events, operand planes of the working set
+    bool overlap = true;
+    cudaStream_t st2 = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_l0 = nullptr, ev_l1 = nullptr;
+    float *ws_hi = nullptr, *ws_lo = nullptr, *ws_sd = nullptr, *ws_unscale = nullptr;
     // iteration state (csmosolver.cpp:51-57)
     long long iter = 0, local_iter = 0, rows_made = 0, launches0 = 0;
     int same_cnt = 0, swap_cnt = 0, local_max_iter = 0;
@@ -872,6 +881,19 @@ struct tsvm_solver {
         tsvm_ws_destroy(sel);
         if (diff_host) cudaFreeHost(diff_host);
         for (auto e : ev) if (e) cudaEventDestroy(e);
+        for (auto e : {ev_fork, ev_l0, ev_l1}) if (e) cudaEventDestroy(e);
+        cudaFree(ws_hi); cudaFree(ws_lo); cudaFree(ws_sd); cudaFree(ws_unscale);
+        if (st2) cudaStreamDestroy(st2);
+    }
+
+    tsvm_status ensure_ws_planes() {
+        if (ws_hi) return TSVM_OK;
+        const size_t words = (km_plane_row_bytes(km) * (size_t) ws + 3) / 4;
+        TSVM_TRY(dev_alloc(&ws_hi, words));
+        TSVM_TRY(dev_alloc(&ws_lo, words));
+        TSVM_TRY(dev_alloc(&ws_sd, (size_t) ws));
+        TSVM_TRY(dev_alloc(&ws_unscale, (size_t) ws));
+        return TSVM_OK;
     }
 
     tsvm_status init() {
@@ -890,6 +912,14 @@ struct tsvm_solver {
         TSVM_TRY(tsvm_ws_create(n, ws, &sel));
         TSVM_CUDA(cudaMallocHost((void **) &diff_host, 16 * sizeof(double)));
         for (auto &e : ev) TSVM_CUDA(cudaEventCreate(&e));
+        TSVM_CUDA(cudaEventCreate(&ev_l0));
+        TSVM_CUDA(cudaEventCreate(&ev_l1));
+        TSVM_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+        {
+            int lo_prio = 0, hi_prio = 0;
+            TSVM_CUDA(cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio));
+            TSVM_CUDA(cudaStreamCreateWithPriority(&st2, cudaStreamNonBlocking, hi_prio));
+        }
         // local iteration cap: max(100000, 100 * ws) (csmosolver.cpp:49)
         local_max_iter = ws > INT_MAX / 100 ? INT_MAX : (100 * ws > 100000 ? 100 * ws : 100000);
         return init_f();
@@ -926,8 +956,17 @@ struct tsvm_solver {
 
     // One outer iteration of csmosolver.cpp:59-120. Sets `done` by the reference's rules
     // (csmosolver.cpp:86-111) except the iteration cap, which the caller applies.
+    //
+    // Overlapped form (dense data on the CTA-pair tensor engine, every iteration but the first): the local
+    // solver only needs the ws x ws block of kernel values, not the q full rows. The block's q new rows are
+    // computed first by a small launch of the same engine against the working set's own operand planes
+    // (bit-identical to the values the full rows will hold: same planes, same slab order), its old rows are
+    // gathered from the rows already in the buffer, and the one-CTA local solver then runs on a second stream
+    // while the q x n launch - which leaves one SM pair free for it - fills the row buffer. Both meet before
+    // the f update.
     tsvm_status outer_iteration() {
         const int first_half_phys = (int) (iter & 1);   // iteration 0 fills both halves in logical order
+        const bool overlapped = overlap && iter > 0 && st2 && km_pair_engine(km, st);
         TSVM_CUDA(cudaEventRecord(ev[0], st));
         if (iter == 0) {
             TSVM_TRY(tsvm_select_working_set(sel, kind, n, f, alpha, y, nullptr, Cp, Cn, ws, ids, st));
@@ -938,14 +977,43 @@ struct tsvm_solver {
             TSVM_LAUNCH(shift_ws_kernel, 1, 1024, 0, st, ids, q, in_ws);
             TSVM_TRY(tsvm_select_working_set(sel, kind, n, f, alpha, y, in_ws, Cp, Cn, q, ids + q, st));
             TSVM_CUDA(cudaEventRecord(ev[1], st));
-            TSVM_TRY(tsvm_km_rows_by_index(km, ids + q, q, rows + (size_t) (1 - first_half_phys) * q * ld, ld, st));
+            float *new_rows = rows + (size_t) (1 - first_half_phys) * q * ld;
+            if (!overlapped) {
+                TSVM_TRY(tsvm_km_rows_by_index(km, ids + q, q, new_rows, ld, st));
+            } else {
+                TSVM_TRY(ensure_ws_planes());
+                TSVM_TRY(km_stage_rows_by_index(km, ids + q, q, st));
+                TSVM_TRY(km_gather_planes(km, ids, ws, ws_hi, ws_lo, ws_sd, ws_unscale, st));
+                TSVM_CUDA(cudaEventRecord(ev_fork, st));
+                // second stream: block rows q..ws-1 by the engine, rows 0..q-1 and the slot vectors by gather
+                TSVM_CUDA(cudaStreamWaitEvent(st2, ev_fork, 0));
+                const InstancePlanes members{ws_hi, ws_lo, ws_sd, ws_unscale, ws};
+                TSVM_TRY(km_rows_staged_on(km, members, q, kww + (size_t) q * ws, ws, st2));
+                TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st2, ws, q, first_half_phys, ids, rows, ld, km->diag, y, f,
+                            alpha, kww, diag_ws, y_ws, f_ws, a_ws, q);
+                TSVM_CUDA(cudaEventRecord(ev_l0, st2));
+                TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps,
+                                          local_max_iter, diff, ids, alpha, st2));
+                TSVM_CUDA(cudaEventRecord(ev_l1, st2));
+                // first stream: the q full rows on all SM pairs but one
+                km->reserve_clusters = 1;
+                const tsvm_status rs = km_rows_staged(km, q, new_rows, ld, st);
+                km->reserve_clusters = 0;
+                TSVM_TRY(rs);
+            }
             rows_made += q;
         }
         TSVM_CUDA(cudaEventRecord(ev[2], st));
-        TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st, ws, q, first_half_phys, ids, rows, ld, km->diag, y, f, alpha, kww,
-                    diag_ws, y_ws, f_ws, a_ws);
-        TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter,
-                                  diff, ids, alpha, st));
+        if (!overlapped) {
+            TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st, ws, q, first_half_phys, ids, rows, ld, km->diag, y, f, alpha,
+                        kww, diag_ws, y_ws, f_ws, a_ws, ws);
+            TSVM_CUDA(cudaEventRecord(ev_l0, st));
+            TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter,
+                                      diff, ids, alpha, st));
+            TSVM_CUDA(cudaEventRecord(ev_l1, st));
+        } else {
+            TSVM_CUDA(cudaStreamWaitEvent(st, ev_l1, 0));
+        }
         TSVM_CUDA(cudaEventRecord(ev[3], st));
         TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows, ld,
                     rows_vec_ok(rows, ld));
@@ -960,7 +1028,7 @@ struct tsvm_solver {
         float ms;
         cudaEventElapsedTime(&ms, ev[0], ev[1]); t_sel += ms;
         cudaEventElapsedTime(&ms, ev[1], ev[2]); t_rows += ms;
-        cudaEventElapsedTime(&ms, ev[2], ev[3]); t_loc += ms;
+        cudaEventElapsedTime(&ms, ev_l0, ev_l1); t_loc += ms;     // overlapped with the rows phase when both streams run
         cudaEventElapsedTime(&ms, ev[3], ev[4]); t_upd += ms;
         diff0 = diff_host[0];
         local_iter += (long long) diff_host[1];
@@ -1059,6 +1127,12 @@ tsvm_status tsvm_solver_finish(tsvm_solver *S, double *rho_host, tsvm_solve_stat
 tsvm_status tsvm_solver_get_stats(const tsvm_solver *S, tsvm_solve_stats *stats_host) {
     TSVM_REQUIRE(S && stats_host, "solver_get_stats: null argument");
     S->fill_stats(stats_host, NAN);
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_solver_set_overlap(tsvm_solver *S, int enable) {
+    TSVM_REQUIRE(S, "solver_set_overlap: null argument");
+    S->overlap = enable != 0;
     return TSVM_OK;
 }
 
