@@ -29,7 +29,7 @@ struct SelectState {            // one per list, lives in device memory
     int k_rem;                      // rank still to resolve inside the current prefix
     int take_all;                   // fewer candidates than wanted: take every one
     int count;                      // compaction cursor
-    int pad;
+    int resolved;                   // the threshold is final: later radix passes skip this list
 };
 
 __device__ __forceinline__ int list_count(int solver_kind) { return solver_kind == TSVM_SOLVER_C ? 2 : 4; }
@@ -54,48 +54,73 @@ __global__ void select_init_kernel(SelectState *st, int *hist, int *ticket, int 
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < lists * RADIX_BINS; i += gridDim.x * blockDim.x) hist[i] = 0;
     if (blockIdx.x == 0 && threadIdx.x < lists) {
         SelectState s;
-        s.prefix_hi = 0; s.prefix_lo = 0; s.k_rem = want; s.take_all = 0; s.count = 0; s.pad = 0;
+        s.prefix_hi = 0; s.prefix_lo = 0; s.k_rem = want; s.take_all = 0; s.count = 0; s.resolved = 0;
         st[threadIdx.x] = s;
     }
     if (blockIdx.x == 0 && threadIdx.x == 0) *ticket = 0;
 }
 
 // One radix pass: histogram of the current digit over the eligible instances that match the
-// prefix; the last block to finish picks the digit that holds the wanted rank.
+// prefix, all lists in one sweep over the data; the last block to finish picks, per list, the digit
+// that holds the wanted rank. A list whose threshold digit holds few enough instances for the whole
+// digit to fit the candidate capacity `cap` is resolved on the spot (the threshold becomes "everything
+// up to and including this digit" and the exact order is left to the sort of the candidates), so that
+// in practice two passes do the work and the remaining launches return at once.
+// Dynamic shared memory: lists x RADIX_BINS ints.
 __global__ void __launch_bounds__(256)
 select_hist_kernel(int solver_kind, int pass, int n, const double *__restrict__ f, const double *__restrict__ alpha,
                    const int *__restrict__ y, const unsigned char *__restrict__ in_ws, double Cp, double Cn,
-                   SelectState *st, int *hist, int *ticket) {
-    __shared__ int sh[RADIX_BINS];
+                   SelectState *st, int *hist, int *ticket, int want, int cap) {
+    extern __shared__ int sh[];
     __shared__ int scan[256];
     __shared__ bool is_last;
     const int lists = list_count(solver_kind);
     const int shift = 96 - RADIX_BITS * (pass + 1);
-    for (int l = 0; l < lists; ++l) {
-        if (st[l].take_all) continue;
-        const key96_t prefix = ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo;
-        const bool asc = list_ascending(solver_kind, l);
-        for (int b = threadIdx.x; b < RADIX_BINS; b += 256) sh[b] = 0;
-        __syncthreads();
-        for (int j = blockIdx.x * 256 + threadIdx.x; j < n; j += gridDim.x * 256) {
-            if (in_ws && in_ws[j]) continue;
-            if (!in_list(solver_kind, l, alpha[j], y[j], Cp, Cn)) continue;
-            const key96_t k = make_key(asc, f[j], (unsigned) j);
-            if (pass > 0 && (k >> (shift + RADIX_BITS)) != (prefix >> (shift + RADIX_BITS))) continue;
-            atomicAdd(&sh[(int) (k >> shift) & (RADIX_BINS - 1)], 1);
+    unsigned active = 0;
+    key96_t prefix[MAX_LISTS];
+#pragma unroll
+    for (int l = 0; l < MAX_LISTS; ++l) {
+        prefix[l] = 0;
+        if (l < lists && !st[l].take_all && !st[l].resolved) {
+            active |= 1u << l;
+            prefix[l] = ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo;
         }
-        __syncthreads();
-        for (int b = threadIdx.x; b < RADIX_BINS; b += 256)
-            if (sh[b]) atomicAdd(&hist[l * RADIX_BINS + b], sh[b]);
-        __syncthreads();
     }
+    if (!active) return;
+    for (int b = threadIdx.x; b < lists * RADIX_BINS; b += 256) sh[b] = 0;
+    __syncthreads();
+    for (int j = blockIdx.x * 256 + threadIdx.x; j < n; j += gridDim.x * 256) {
+        if (in_ws && in_ws[j]) continue;
+        const double a = alpha[j], fj = f[j];
+        const int yj = y[j];
+#pragma unroll
+        for (int l = 0; l < MAX_LISTS; ++l) {
+            if (!((active >> l) & 1u)) continue;
+            if (!in_list(solver_kind, l, a, yj, Cp, Cn)) continue;
+            const key96_t k = make_key(list_ascending(solver_kind, l), fj, (unsigned) j);
+            if (pass > 0 && (k >> (shift + RADIX_BITS)) != (prefix[l] >> (shift + RADIX_BITS))) continue;
+            const int bin = l * RADIX_BINS + ((int) (k >> shift) & (RADIX_BINS - 1));
+            if (pass == 0) {
+                // sign and exponent: nearly every instance lands in a handful of bins - one atomic per
+                // distinct bin and warp instead of one per instance
+                const unsigned peers = __match_any_sync(__activemask(), bin);
+                if ((int) (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&sh[bin], __popc(peers));
+            } else {
+                atomicAdd(&sh[bin], 1);
+            }
+        }
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < lists * RADIX_BINS; b += 256)
+        if (sh[b]) atomicAdd(&hist[b], sh[b]);
     __threadfence();
+    __syncthreads();
     if (threadIdx.x == 0) is_last = (atomicAdd(ticket, 1) == (int) gridDim.x - 1);
     __syncthreads();
     if (!is_last) return;
     __threadfence();
     for (int l = 0; l < lists; ++l) {
-        if (st[l].take_all) continue;
+        if (!((active >> l) & 1u)) continue;
         volatile int *h = hist + l * RADIX_BINS;
         // 16 consecutive bins per thread, block-wide exclusive scan of the per-thread sums
         int local[16], sum = 0;
@@ -120,11 +145,16 @@ select_hist_kernel(int solver_kind, int pass, int n, const double *__restrict__ 
 #pragma unroll
             for (int b = 0; b < 16; ++b) {
                 if (run < k_rem && k_rem <= run + local[b]) {
-                    key96_t p = ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo;
-                    p |= (key96_t) (threadIdx.x * 16 + b) << shift;
+                    key96_t p = prefix[l] | ((key96_t) (threadIdx.x * 16 + b) << shift);
+                    const int k_new = k_rem - run;
+                    // instances below this digit: want - k_new; with the whole digit: + local[b]
+                    if (shift > 0 && (want - k_new) + local[b] <= cap) {
+                        p |= ((key96_t) 1 << shift) - 1;
+                        st[l].resolved = 1;
+                    }
                     st[l].prefix_hi = (unsigned long long) (p >> 32);
                     st[l].prefix_lo = (unsigned int) p;
-                    st[l].k_rem = k_rem - run;
+                    st[l].k_rem = k_new;
                 }
                 run += local[b];
             }
@@ -137,11 +167,11 @@ select_hist_kernel(int solver_kind, int pass, int n, const double *__restrict__ 
 }
 
 // Compaction: every eligible instance whose key is <= the threshold goes to the list's
-// candidate array (unordered). Unused tail entries keep id -1.
+// candidate array (unordered, `cap` entries per list). Unused tail entries keep id -1.
 __global__ void select_collect_kernel(int solver_kind, int n, const double *__restrict__ f,
                                       const double *__restrict__ alpha, const int *__restrict__ y,
                                       const unsigned char *__restrict__ in_ws, double Cp, double Cn, SelectState *st,
-                                      int want, int id_offset, double *__restrict__ cand_f, int *__restrict__ cand_id) {
+                                      int cap, int id_offset, double *__restrict__ cand_f, int *__restrict__ cand_id) {
     const int lists = list_count(solver_kind);
     for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x) {
         if (in_ws && in_ws[j]) continue;
@@ -154,7 +184,7 @@ __global__ void select_collect_kernel(int solver_kind, int n, const double *__re
                 if (make_key(list_ascending(solver_kind, l), fj, (unsigned) j) > thr) continue;
             }
             const int pos = atomicAdd(&st[l].count, 1);
-            if (pos < want) { cand_f[(size_t) l * want + pos] = fj; cand_id[(size_t) l * want + pos] = j + id_offset; }
+            if (pos < cap) { cand_f[(size_t) l * cap + pos] = fj; cand_id[(size_t) l * cap + pos] = j + id_offset; }
         }
     }
 }
@@ -188,6 +218,7 @@ select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const in
     int *hash_id = reinterpret_cast<int *>(taken + MAX_LISTS * MERGE_MAX_WANT);        // [HASH_SLOTS]
     short *hash_pos = reinterpret_cast<short *>(hash_id + HASH_SLOTS);
     __shared__ int top_len[MAX_LISTS];
+    __shared__ unsigned long long last_fkey[MAX_LISTS];
     const int tid = threadIdx.x;
 
     for (int l = 0; l < lists; ++l) {
@@ -236,13 +267,38 @@ select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const in
             int lo = 0, hi = c;
             while (lo < hi) { int mid = (lo + hi) >> 1; if (top_id[l * MERGE_MAX_WANT + mid] >= 0) lo = mid + 1; else hi = mid; }
             top_len[l] = lo;
+            // f-order key of the last kept entry: the list's largest f (ascending) / smallest f (descending)
+            last_fkey[l] = lo > 0 ? (asc ? kh[lo - 1] : ~kh[lo - 1]) : 0ull;
         }
         __syncthreads();
     }
 
+    // An instance sits in an "up" list and in the paired "low" list only if the up list's largest f is not
+    // below the low list's smallest f. For large problems that never happens: no instance is then met twice,
+    // the reference's alternating walk takes entry p of every list in round p, and the output position of
+    // every entry follows from the list lengths alone.
+    const int half = lists / 2;
+    bool disjoint = true;
+    for (int u = 0; u < half; ++u)
+        if (top_len[u] > 0 && top_len[u + half] > 0 && !(last_fkey[u] < last_fkey[u + half])) disjoint = false;
+    if (disjoint) {
+        int total = 0;
+        for (int l = 0; l < lists; ++l) total += top_len[l];
+        const int got = total < want ? total : want;
+        for (int e = tid; e < lists * want; e += MERGE_THREADS) {
+            const int l = e / want, p = e - l * want;
+            if (p >= top_len[l]) continue;
+            int pos = 0;
+            for (int o = 0; o < lists; ++o) pos += (top_len[o] < p ? top_len[o] : p) + ((o < l && top_len[o] > p) ? 1 : 0);
+            if (pos < want) out_ids[pos] = top_id[l * MERGE_MAX_WANT + p];
+        }
+        for (int r = got + tid; r < want; r += MERGE_THREADS) out_ids[r] = -1;
+        if (tid == 0 && out_count) *out_count = got;
+        return;
+    }
+
     // partner positions: an instance can sit in an "up" list and in the "low" list of the same
     // class. up list u pairs with low list u + lists/2.
-    const int half = lists / 2;
     for (int u = 0; u < half; ++u) {
         const int lw = u + half;
         for (int s = tid; s < HASH_SLOTS; s += MERGE_THREADS) hash_id[s] = -1;
@@ -679,6 +735,7 @@ using namespace tsvm;
 
 struct tsvm_ws {
     int n_max = 0, ws_max = 0;
+    int cand_cap = 0;               // entries per list of cand_f / cand_id
     SelectState *state = nullptr;
     int *hist = nullptr, *ticket = nullptr, *count = nullptr;
     double *cand_f = nullptr;
@@ -691,12 +748,13 @@ tsvm_status tsvm_ws_create(int n_max, int ws_max, tsvm_ws **out) {
     TSVM_REQUIRE(out && n_max > 0 && ws_max > 0 && ws_max <= MERGE_MAX_WANT, "ws_create: bad arguments");
     tsvm_ws *w = new tsvm_ws;
     w->n_max = n_max; w->ws_max = ws_max;
+    w->cand_cap = 2 * ws_max;       // room for the whole threshold digit of an early-resolved list
     tsvm_status s = dev_alloc(&w->state, MAX_LISTS);
     if (s == TSVM_OK) s = dev_alloc(&w->hist, MAX_LISTS * RADIX_BINS);
     if (s == TSVM_OK) s = dev_alloc(&w->ticket, 1);
     if (s == TSVM_OK) s = dev_alloc(&w->count, 1);
-    if (s == TSVM_OK) s = dev_alloc(&w->cand_f, (size_t) MAX_LISTS * ws_max);
-    if (s == TSVM_OK) s = dev_alloc(&w->cand_id, (size_t) MAX_LISTS * ws_max);
+    if (s == TSVM_OK) s = dev_alloc(&w->cand_f, (size_t) MAX_LISTS * w->cand_cap);
+    if (s == TSVM_OK) s = dev_alloc(&w->cand_id, (size_t) MAX_LISTS * w->cand_cap);
     if (s != TSVM_OK) { tsvm_ws_destroy(w); return s; }
     *out = w;
     return TSVM_OK;
@@ -709,24 +767,38 @@ void tsvm_ws_destroy(tsvm_ws *w) {
     delete w;
 }
 
+// Candidate lists of `cap` >= want entries each (stride cap): the `want` best of every list are among them.
+static tsvm_status ws_candidates_cap(tsvm_ws *w, int solver_kind, int n, const double *f_dev, const double *alpha_dev,
+                                     const int *y_dev, const unsigned char *in_ws_dev, double Cp, double Cn, int want,
+                                     int cap, int id_offset, double *cand_f_dev, int *cand_id_dev, cudaStream_t st) {
+    const int lists = solver_kind == TSVM_SOLVER_C ? 2 : 4;
+    int grid = ceil_div(n, 256 * 4);
+    if (grid > 296) grid = 296;
+    if (grid < 1) grid = 1;
+    const size_t hist_smem = (size_t) lists * RADIX_BINS * sizeof(int);
+    static bool configured = false;
+    if (!configured) {
+        TSVM_CUDA(cudaFuncSetAttribute(select_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int) (MAX_LISTS * RADIX_BINS * sizeof(int))));
+        configured = true;
+    }
+    TSVM_LAUNCH(select_init_kernel, 16, 256, 0, st, w->state, w->hist, w->ticket, lists, want);
+    TSVM_LAUNCH(fill_int_kernel, ceil_div(lists * cap, 256), 256, 0, st, cand_id_dev, lists * cap, -1);
+    for (int p = 0; p < RADIX_PASSES; ++p)
+        TSVM_LAUNCH(select_hist_kernel, grid, 256, hist_smem, st, solver_kind, p, n, f_dev, alpha_dev, y_dev, in_ws_dev,
+                    Cp, Cn, w->state, w->hist, w->ticket, want, cap);
+    TSVM_LAUNCH(select_collect_kernel, grid, 256, 0, st, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn,
+                w->state, cap, id_offset, cand_f_dev, cand_id_dev);
+    return TSVM_OK;
+}
+
 tsvm_status tsvm_ws_candidates(tsvm_ws *w, int solver_kind, int n, const double *f_dev, const double *alpha_dev,
                                const int *y_dev, const unsigned char *in_ws_dev, double Cp, double Cn, int want,
                                int id_offset, double *cand_f_dev, int *cand_id_dev, void *stream) {
     TSVM_REQUIRE(w && f_dev && alpha_dev && y_dev && cand_f_dev && cand_id_dev && n > 0 && want > 0 &&
                  want <= w->ws_max && solver_kind >= 0 && solver_kind <= 2, "ws_candidates: bad arguments");
-    cudaStream_t st = (cudaStream_t) stream;
-    const int lists = solver_kind == TSVM_SOLVER_C ? 2 : 4;
-    int grid = ceil_div(n, 256 * 4);
-    if (grid > 296) grid = 296;
-    if (grid < 1) grid = 1;
-    TSVM_LAUNCH(select_init_kernel, 16, 256, 0, st, w->state, w->hist, w->ticket, lists, want);
-    TSVM_LAUNCH(fill_int_kernel, ceil_div(lists * want, 256), 256, 0, st, cand_id_dev, lists * want, -1);
-    for (int p = 0; p < RADIX_PASSES; ++p)
-        TSVM_LAUNCH(select_hist_kernel, grid, 256, 0, st, solver_kind, p, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp,
-                    Cn, w->state, w->hist, w->ticket);
-    TSVM_LAUNCH(select_collect_kernel, grid, 256, 0, st, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn,
-                w->state, want, id_offset, cand_f_dev, cand_id_dev);
-    return TSVM_OK;
+    return ws_candidates_cap(w, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn, want, want, id_offset,
+                             cand_f_dev, cand_id_dev, (cudaStream_t) stream);
 }
 
 tsvm_status tsvm_ws_merge(tsvm_ws *w, int solver_kind, const double *cand_f_dev, const int *cand_id_dev, int len,
@@ -749,9 +821,13 @@ tsvm_status tsvm_ws_merge(tsvm_ws *w, int solver_kind, const double *cand_f_dev,
 tsvm_status tsvm_select_working_set(tsvm_ws *w, int solver_kind, int n, const double *f_dev, const double *alpha_dev,
                                     const int *y_dev, const unsigned char *in_ws_dev, double Cp, double Cn, int want,
                                     int *out_ids_dev, void *stream) {
-    TSVM_TRY(tsvm_ws_candidates(w, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn, want, 0, w->cand_f,
-                                w->cand_id, stream));
-    return tsvm_ws_merge(w, solver_kind, w->cand_f, w->cand_id, want, want, out_ids_dev, stream);
+    TSVM_REQUIRE(w && f_dev && alpha_dev && y_dev && out_ids_dev && n > 0 && want > 0 && want <= w->ws_max &&
+                 solver_kind >= 0 && solver_kind <= 2, "select_working_set: bad arguments");
+    const int cap = 2 * want <= w->cand_cap ? 2 * want : (want <= w->cand_cap ? w->cand_cap : want);
+    TSVM_REQUIRE(cap >= want, "select_working_set: candidate buffers hold %d entries, %d wanted", w->cand_cap, want);
+    TSVM_TRY(ws_candidates_cap(w, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn, want, cap, 0, w->cand_f,
+                               w->cand_id, (cudaStream_t) stream));
+    return tsvm_ws_merge(w, solver_kind, w->cand_f, w->cand_id, cap, want, out_ids_dev, stream);
 }
 
 // ---- working-set selection without any allocation --------------------------------------------------
@@ -795,6 +871,7 @@ tsvm_status tsvm_select_working_set_static(int solver_kind, int n, const double 
     tsvm_ws view;                      // a view over the static array; owns nothing, frees nothing
     view.n_max = n;
     view.ws_max = STATIC_WS_MAX;
+    view.cand_cap = STATIC_WS_MAX;
     view.state = reinterpret_cast<SelectState *>(base + STATIC_OFF_STATE);
     view.hist = reinterpret_cast<int *>(base + STATIC_OFF_HIST);
     view.ticket = reinterpret_cast<int *>(base + STATIC_OFF_TICKET);
