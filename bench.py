@@ -45,6 +45,7 @@ def parse():
     ap.add_argument("--cpu-sample-rows", type=int, default=20000)
     ap.add_argument("--cpu-sample-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--predict-rows", type=int, default=100000, help="test rows of the prediction measurement (0: skip)")
     return ap.parse_args()
 
 
@@ -307,6 +308,50 @@ def run_b200_arm(args):
                  "rho": rho, "n_sv": int((a_host != 0).sum()), "kernel_rows_per_s": st["kernel_rows"] / sec,
                  "phase_seconds": {k: st["seconds_" + k] for k in ("select", "rows", "local", "update")}}
 
+    # ---- (4) prediction with the trained model: decision values + vote for the test rows -----------
+    predict = None
+    if train is not None and train["converged"] and args.predict_rows > 0:
+        m = args.predict_rows
+        Th = torch.empty((m, d), dtype=torch.float32, pin_memory=True)
+        y_test = synth.config5(m, d=d, seed=8, out=Th.numpy())["y"]
+        sv_idx = torch.nonzero(a_host != 0).squeeze(1)
+        y_t = torch.from_numpy(y_np)
+        order = torch.cat([sv_idx[y_t[sv_idx] > 0], sv_idx[y_t[sv_idx] < 0]])      # class +1 first (svc.cpp:56-108)
+        n_pos = int((y_t[sv_idx] > 0).sum())
+        coef_h = (a_host[order] * y_t[order].to(torch.float64)).contiguous()
+        Xsv = Xh[order].cuda()
+        km_sv = capi.KernelMatrix(dense=Xsv, gamma=GAMMA)
+        coef_d, rho_d = coef_h.cuda(), torch.tensor([rho], dtype=torch.float64, device="cuda")
+        counts = [n_pos, len(order) - n_pos]
+
+        def run_predict(T):
+            dec = capi.predict_dec(km_sv, coef_d, counts, rho_d, 2, dense=T)
+            return capi.vote(dec, 2)
+
+        warm = run_predict(Th[:2048].cuda())
+        Td = Th.cuda()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        labels = run_predict(Td)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_res = e0.elapsed_time(e1)
+        del Td
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        lab_h = run_predict(Th.cuda(non_blocking=True)).cpu()
+        sec_host = time.perf_counter() - t0
+        n_sv = len(order)
+        predict = {"rows": m, "n_sv": n_sv, "rows_per_s": m / (ms_res * 1e-3), "e2e_rows_per_s": m / sec_host,
+                   "algorithmic_tflops": 2.0 * m * n_sv * d / (ms_res * 1e-3) / 1e12,
+                   "positive_fraction": float((lab_h == 0).float().mean()),
+                   "accuracy": float(((lab_h == 0).numpy() == (y_test > 0)).mean()),
+                   "note": "decision values + vote of the seed-8 test rows against the trained model; resident: test "
+                           "rows in HBM, CUDA events; e2e: from pinned host rows, labels back on the host"}
+        km_sv.close()
+        del Xsv, warm, labels
+
     cpu = None
     if not args.no_cpu_baseline:
         try:
@@ -324,7 +369,7 @@ def run_b200_arm(args):
                    "l2": "inputs larger than L2 (X planes %.1f GB, row buffer %.1f GB)" % (2 * n * d * 2 / 1e9,
                                                                                           WS * n * 4 / 1e9)},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
-        "phase_ms_per_step": phases, "train_to_eps": train,
+        "phase_ms_per_step": phases, "train_to_eps": train, "predict": predict,
     }
     print(json.dumps(line))
 
