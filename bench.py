@@ -30,7 +30,7 @@ sys.path.insert(0, ROOT)
 
 N_FULL, D_FULL, WS, Q = 400000, 2000, 1024, 512
 GAMMA, C_SVC, EPS = 0.5, 1.0, 1e-3
-TRAFFIC_37888 = None   # bytes (dram read + write) of one 37,888-instance launch, from profiles/
+TRAFFIC_37888 = 391.5e6   # dram read + write bytes of one 37,888-instance launch of the kernel (ncu capture summarised in profiles/)
 
 
 def parse():
@@ -254,7 +254,7 @@ def run_b200_arm(args):
     traffic = TRAFFIC_37888 * n / 37888.0 if TRAFFIC_37888 else None
     roofline = {"bound": "tensor",
                 "kernel": "dense_rows_tc2_kernel<EPI_RBF, F16> (tcgen05 CTA pairs, two row-scaled FP16 planes, "
-                          "3 MMAs per product, per-slab FP32 promotion, fused RBF epilogue)",
+                          "3 MMAs per product, FP32 promotion every two k slabs, fused RBF epilogue)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "issued_frac": 3 * achieved / peak, "traffic": traffic,
                 "peak_source": peak_src + "; sustained figure %.0f; torch.matmul fp16 8192^3 best-of-10 in this run "
