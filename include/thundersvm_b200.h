@@ -162,6 +162,35 @@ tsvm_status tsvm_solver_get_stats(const tsvm_solver *solver, tsvm_solve_stats *s
 tsvm_status tsvm_solver_set_overlap(tsvm_solver *solver, int enable);
 void tsvm_solver_destroy(tsvm_solver *solver);
 
+/* ---- Column-sharded solver: the per-rank device work of CSMOSolver / NuSMOSolver::solve -----------
+ * One large binary problem whose instances (columns of the kernel matrix) are split over `world`
+ * processes, one GPU each: this rank owns instances [lo, lo + n_local) - km_local, y, alpha, f are
+ * its slices. The reference has no multi-GPU form of this loop (csmosolver.cpp:59-120 runs on one
+ * device); the steps and their results are the same, bit for bit, as tsvm_solver_* on one GPU.
+ * One outer iteration is three calls with the caller's collectives in between (any library; the
+ * buffers are plain device memory the caller allocated and passed to tsvm_shard_create):
+ *   tsvm_shard_candidates  -> cand_f / cand_id hold lists x want entries (global ids);
+ *                             all-gather them, rank-major, into all_f / all_id
+ *   tsvm_shard_select      -> the same merge on every rank; rows_contrib ([n_new][dp + 4] floats,
+ *                             dp = round_up(n_features, 4): feature row, self dot, diagonal) and
+ *                             state_contrib ([ws][3] doubles: y, f, alpha) hold this rank's share,
+ *                             zeros for members it does not own; all-reduce (sum) both
+ *   tsvm_shard_iterate     -> kernel rows of the new members against the own columns, the ws x ws
+ *                             block and the local solver (replicated, deterministic), f / alpha
+ *                             update of the own slice, the reference's stopping rules
+ * Buffer sizes: cand_* lists_max(4) * ws entries, all_* world * 4 * ws, rows_contrib ws * (dp + 4),
+ * state_contrib ws * 3. Needs dense data with more than 32 features (CTA-pair tensor engine). */
+typedef struct tsvm_shard tsvm_shard;
+tsvm_status tsvm_shard_create(tsvm_km *km_local, int solver_kind, const int *y_dev, double *alpha_dev, double *f_dev,
+                              int n_total, int lo, double eps, double Cp, double Cn, int ws_size, int world,
+                              double *cand_f_dev, int *cand_id_dev, double *all_f_dev, int *all_id_dev,
+                              float *rows_contrib_dev, double *state_contrib_dev, void *stream, tsvm_shard **out);
+tsvm_status tsvm_shard_candidates(tsvm_shard *shard, int *lists_host, int *want_host);
+tsvm_status tsvm_shard_select(tsvm_shard *shard, int *n_new_host);
+tsvm_status tsvm_shard_iterate(tsvm_shard *shard, int *done_host);
+tsvm_status tsvm_shard_get_stats(const tsvm_shard *shard, tsvm_solve_stats *stats_host);
+void tsvm_shard_destroy(tsvm_shard *shard);
+
 /* The 13 partial reductions rho and the objective are made of (csmosolver.cpp:167-187,227-239;
  * nusmosolver.cpp:9-46), over the n instances given: out13_dev[0..12] = n_free(y>0), sum f over them,
  * n_free(y<0), sum f over them, sum_i alpha_i - (f_i + y_i) alpha_i y_i / 2, then min f over I_up and

@@ -41,3 +41,77 @@ def test_rows_for_features_equals_rows_by_index(capi):
     a = km.get_rows(idx)
     b = km.rows_for_features(X[idx.long()].contiguous(), km.self_dot()[idx.long()].contiguous())
     assert torch.equal(a, b)
+
+
+def test_native_single_shard_is_bit_identical_to_plain_solver(capi):
+    """tsvm_shard_* with one shard: same working sets, same kernel values, same local solver - alpha, f and
+    the iteration counts equal those of tsvm_smo_solve exactly."""
+    import torch
+    from thundersvm_b200 import sharded
+    prob = synth.config5(5000, d=256)
+    y = binary_labels(prob)
+    n = len(y)
+    X = torch.from_numpy(prob["X"]).cuda()
+    yt = torch.from_numpy(y).cuda()
+    a1 = torch.zeros(n, dtype=torch.float64, device="cuda")
+    f1 = -yt.to(torch.float64)
+    km = capi.KernelMatrix(dense=X, gamma=prob["gamma"])
+    rho1, st1 = capi.smo_solve(km, yt, a1, f1, 1e-3, 1.0, 1.0, 1024)
+    a2 = torch.zeros(n, dtype=torch.float64, device="cuda")
+    f2 = -yt.to(torch.float64)
+    sv = sharded.NativeShardedSolver(X, yt, a2, f2, n, 0, 1e-3, 1.0, 1.0, 1024, gamma=prob["gamma"])
+    rho2, st2 = sv.solve()
+    assert st2["outer_iters"] == st1["outer_iters"] and st2["local_iters"] == st1["local_iters"]
+    assert torch.equal(a1, a2) and torch.equal(f1, f2)
+    assert abs(rho2 - rho1) < 1e-12 and abs(st2["objective"] - st1["objective"]) <= 1e-12 * abs(st1["objective"])
+    sv.close()
+
+
+def _native_rank(rank, world, port, n, d, out_path):
+    import os
+    import torch
+    import torch.distributed as dist
+    from thundersvm_b200 import sharded
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    prob = synth.config5(n, d=d)
+    y = binary_labels(prob)
+    lo, hi = sharded.shard_range(n, rank, world)
+    X = torch.from_numpy(prob["X"][lo:hi]).cuda()
+    yt = torch.from_numpy(y[lo:hi]).cuda()
+    a = torch.zeros(hi - lo, dtype=torch.float64, device="cuda")
+    f = -yt.to(torch.float64)
+    sv = sharded.NativeShardedSolver(X, yt, a, f, n, lo, 1e-3, 1.0, 1.0, 1024, gamma=prob["gamma"])
+    rho, st = sv.solve()
+    parts = [torch.empty(sharded.shard_range(n, r, world)[1] - sharded.shard_range(n, r, world)[0],
+                         dtype=torch.float64, device="cuda") for r in range(world)]
+    dist.all_gather(parts, a)
+    if rank == 0:
+        np.savez(out_path, alpha=torch.cat(parts).cpu().numpy(), rho=rho, obj=st["objective"],
+                 outer=st["outer_iters"], local=st["local_iters"])
+    sv.close()
+    dist.destroy_process_group()
+
+
+def test_native_two_shards_are_bit_identical_to_one_gpu(capi, tmp_path):
+    """Two ranks on two GPUs (NCCL): every rank computes the same working sets and the same block, the
+    columns are disjoint - the gathered alpha equals the one-GPU result exactly."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    n, d = 6000, 256
+    out = str(tmp_path / "two.npz")
+    mp.spawn(_native_rank, args=(2, 29533, n, d, out), nprocs=2, join=True)
+    got = np.load(out)
+    prob = synth.config5(n, d=d)
+    y = binary_labels(prob)
+    yt = torch.from_numpy(y).cuda()
+    a1 = torch.zeros(n, dtype=torch.float64, device="cuda")
+    f1 = -yt.to(torch.float64)
+    km = capi.KernelMatrix(dense=torch.from_numpy(prob["X"]).cuda(), gamma=prob["gamma"])
+    rho1, st1 = capi.smo_solve(km, yt, a1, f1, 1e-3, 1.0, 1.0, 1024)
+    assert int(got["outer"]) == st1["outer_iters"] and int(got["local"]) == st1["local_iters"]
+    assert np.array_equal(got["alpha"], a1.cpu().numpy())
+    assert abs(float(got["rho"]) - rho1) < 1e-9

@@ -23,7 +23,7 @@ EXPORTS = [
     "tsvm_km_n_instances", "tsvm_km_n_features", "tsvm_km_nnz", "tsvm_km_is_dense", "tsvm_km_diag_dev",
     "tsvm_km_self_dot_dev", "tsvm_km_rows_by_index", "tsvm_km_rows_by_instances_dense",
     "tsvm_km_rows_by_instances_csr", "tsvm_km_rows_for_features_dense", "tsvm_km_set_dense_engine", "tsvm_rho_partials", "tsvm_smo_solve", "tsvm_solver_create",
-    "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_set_overlap", "tsvm_solver_destroy", "tsvm_working_set_size",
+    "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_set_overlap", "tsvm_solver_destroy", "tsvm_shard_create", "tsvm_shard_candidates", "tsvm_shard_select", "tsvm_shard_iterate", "tsvm_shard_get_stats", "tsvm_shard_destroy", "tsvm_working_set_size",
     "tsvm_ws_create", "tsvm_ws_destroy", "tsvm_ws_candidates", "tsvm_ws_merge", "tsvm_select_working_set",
     "tsvm_select_working_set_static",
     "tsvm_local_smo", "tsvm_update_f", "tsvm_predict_dec", "tsvm_vote",
@@ -84,6 +84,13 @@ def lib():
     L.tsvm_solver_finish.argtypes = [vp, C.POINTER(d), C.POINTER(SolveStats)]
     L.tsvm_solver_get_stats.argtypes = [vp, C.POINTER(SolveStats)]
     L.tsvm_solver_set_overlap.argtypes = [vp, i]
+    L.tsvm_shard_create.argtypes = [vp, i, vp, vp, vp, i, i, d, d, d, i, i, vp, vp, vp, vp, vp, vp, vp, C.POINTER(vp)]
+    L.tsvm_shard_candidates.argtypes = [vp, C.POINTER(i), C.POINTER(i)]
+    L.tsvm_shard_select.argtypes = [vp, C.POINTER(i)]
+    L.tsvm_shard_iterate.argtypes = [vp, C.POINTER(i)]
+    L.tsvm_shard_get_stats.argtypes = [vp, C.POINTER(SolveStats)]
+    L.tsvm_shard_destroy.argtypes = [vp]
+    L.tsvm_shard_destroy.restype = None
     L.tsvm_solver_destroy.argtypes = [vp]
     L.tsvm_solver_destroy.restype = None
     L.tsvm_working_set_size.argtypes = [i, i, sz, sz]
@@ -249,6 +256,61 @@ def smo_solve(km, y, alpha, f, eps, Cp, Cn, ws_size, max_iter=-1, solver="c"):
     check(lib().tsvm_smo_solve(km.handle, SOLVERS[solver], _ptr(y), _ptr(alpha), _ptr(f), eps, Cp, Cn, ws_size,
                                max_iter, C.byref(rho), C.byref(st), _stream()))
     return rho.value, st.as_dict()
+
+
+class Shard:
+    """Per-rank device work of the column-sharded solver (tsvm_shard_*). The exchange buffers are torch
+    tensors owned by this object; the caller runs its collectives on them between the three phases."""
+
+    def __init__(self, km, y, alpha, f, n_total, lo, eps, Cp, Cn, ws_size, world, solver="c"):
+        dev = y.device
+        dp = (km.d + 3) // 4 * 4
+        self.ws, self.world, self.dp = ws_size, world, dp
+        self.cand_f = torch.zeros(4 * ws_size, dtype=torch.float64, device=dev)
+        self.cand_id = torch.zeros(4 * ws_size, dtype=torch.int32, device=dev)
+        self.all_f = torch.zeros(world * 4 * ws_size, dtype=torch.float64, device=dev)
+        self.all_id = torch.zeros(world * 4 * ws_size, dtype=torch.int32, device=dev)
+        self.rows_contrib = torch.zeros(ws_size * (dp + 4), dtype=torch.float32, device=dev)
+        self.state_contrib = torch.zeros(ws_size * 3, dtype=torch.float64, device=dev)
+        self._h = C.c_void_p(0)
+        self._keep = (km, y, alpha, f)
+        check(lib().tsvm_shard_create(km.handle, SOLVERS[solver], _ptr(y), _ptr(alpha), _ptr(f), n_total, lo, eps, Cp,
+                                      Cn, ws_size, world, _ptr(self.cand_f), _ptr(self.cand_id), _ptr(self.all_f),
+                                      _ptr(self.all_id), _ptr(self.rows_contrib), _ptr(self.state_contrib), _stream(),
+                                      C.byref(self._h)))
+
+    def candidates(self):
+        """-> (lists, want): cand_f / cand_id[:lists * want] are this rank's lists."""
+        lists, want = C.c_int(0), C.c_int(0)
+        check(lib().tsvm_shard_candidates(self._h, C.byref(lists), C.byref(want)))
+        return lists.value, want.value
+
+    def select(self):
+        """-> n_new: rows_contrib[:n_new * (dp + 4)] and state_contrib are this rank's contributions."""
+        n_new = C.c_int(0)
+        check(lib().tsvm_shard_select(self._h, C.byref(n_new)))
+        return n_new.value
+
+    def iterate(self):
+        done = C.c_int(0)
+        check(lib().tsvm_shard_iterate(self._h, C.byref(done)))
+        return bool(done.value)
+
+    def stats(self):
+        st = SolveStats()
+        check(lib().tsvm_shard_get_stats(self._h, C.byref(st)))
+        return st.as_dict()
+
+    def close(self):
+        if self._h:
+            lib().tsvm_shard_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class Solver:

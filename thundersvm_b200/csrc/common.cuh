@@ -147,6 +147,10 @@ struct InstancePlanes {
     const float *hi, *lo, *sd, *unscale;
     int n;
 };
+// The requested rows in the same form (nullptr hi: the handle's own staging buffers).
+struct RowPlanes {
+    const float *hi, *lo, *sd, *unscale;
+};
 
 // Opaque handle behind tsvm_km.
 struct tsvm_km {
@@ -196,4 +200,8 @@ tsvm_status km_gather_planes(tsvm_km *km, const int *ids_dev, int m, float *hi, 
                              cudaStream_t st);
 tsvm_status km_rows_staged_on(tsvm_km *km, const InstancePlanes &X, int q, float *out, long long ld_out,
                               cudaStream_t st);
+tsvm_status km_rows_planes_on(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int q, float *out,
+                              long long ld_out, cudaStream_t st);
+tsvm_status km_stage_rows_features(tsvm_km *km, const float *T_dev, int ldt, const float *sd_T_dev, int m,
+                                   cudaStream_t st);
 }  // namespace tsvm

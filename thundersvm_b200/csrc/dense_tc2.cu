@@ -297,8 +297,8 @@ tsvm_status make_map(CUtensorMap *map, const void *ptr, int rows, int row_len, l
                      bool f16);   // dense_tc.cu
 
 template <int EPI, bool F16>
-static tsvm_status launch_pair_kernel(tsvm_km *km, const InstancePlanes &X, int m, float *out, long long ld_out,
-                                      cudaStream_t st) {
+static tsvm_status launch_pair_kernel(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int m, float *out,
+                                      long long ld_out, cudaStream_t st) {
     auto kernel = dense_rows_tc2_kernel<EPI, F16>;
     static int max_clusters = 0;      // per instantiation
     if (!max_clusters) {
@@ -323,8 +323,8 @@ static tsvm_status launch_pair_kernel(tsvm_km *km, const InstancePlanes &X, int 
     const int len = km->plane_ld;
     TSVM_TRY(make_map(&mxh, X.hi, X.n, len, len, tc2::BM, F16));
     TSVM_TRY(make_map(&mxl, X.lo, X.n, len, len, tc2::BM, F16));
-    TSVM_TRY(make_map(&mwh, km->Whi, m, len, len, tc2::BN_HALF, F16));
-    TSVM_TRY(make_map(&mwl, km->Wlo, m, len, len, tc2::BN_HALF, F16));
+    TSVM_TRY(make_map(&mwh, W.hi, m, len, len, tc2::BN_HALF, F16));
+    TSVM_TRY(make_map(&mwl, W.lo, m, len, len, tc2::BN_HALF, F16));
     const int n_items = ceil_div(X.n, 2 * tc2::BM) * ceil_div(m, tc2::BN);
     int avail = max_clusters - km->reserve_clusters;     // SM pairs left free for a concurrent stream
     if (avail < 1) avail = 1;
@@ -335,26 +335,33 @@ static tsvm_status launch_pair_kernel(tsvm_km *km, const InstancePlanes &X, int 
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(tc2::THREADS); cfg.dynamicSmemBytes = tc2::SMEM_BYTES;
     cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
-    TSVM_CUDA(cudaLaunchKernelEx(&cfg, kernel, mxh, mxl, mwh, mwl, X.n, m, len, X.sd, (const float *) km->sd_rows,
-                                 X.unscale, (const float *) km->w_unscale, km->fn, out, ld_out, km->status_dev));
+    TSVM_CUDA(cudaLaunchKernelEx(&cfg, kernel, mxh, mxl, mwh, mwl, X.n, m, len, X.sd, W.sd, X.unscale, W.unscale,
+                                 km->fn, out, ld_out, km->status_dev));
     count_launch();
     return TSVM_OK;
 }
 
 // Kernel values of the m staged requested rows against a set of instances given by its operand planes
 // (kind 1 = TF32 words, 2 = row-scaled FP16, the handle's plane kind), self dots and 1/scale.
-tsvm_status launch_dense_tc2_on(tsvm_km *km, const InstancePlanes &X, int m, float *out, long long ld_out,
-                                cudaStream_t st) {
+tsvm_status launch_dense_tc2_planes(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int m, float *out,
+                                    long long ld_out, cudaStream_t st) {
     TSVM_REQUIRE(km->plane_kind == 1 || km->plane_kind == 2, "tensor engine: operand planes are not built");
     const int epi = epilogue_kind(km->fn);
     if (km->plane_kind == 2) {
-        if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, true>(km, X, m, out, ld_out, st);
-        if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, true>(km, X, m, out, ld_out, st);
-        return launch_pair_kernel<EPI_GENERIC, true>(km, X, m, out, ld_out, st);
+        if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, true>(km, X, W, m, out, ld_out, st);
+        if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, true>(km, X, W, m, out, ld_out, st);
+        return launch_pair_kernel<EPI_GENERIC, true>(km, X, W, m, out, ld_out, st);
     }
-    if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, false>(km, X, m, out, ld_out, st);
-    if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, false>(km, X, m, out, ld_out, st);
-    return launch_pair_kernel<EPI_GENERIC, false>(km, X, m, out, ld_out, st);
+    if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, false>(km, X, W, m, out, ld_out, st);
+    if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, false>(km, X, W, m, out, ld_out, st);
+    return launch_pair_kernel<EPI_GENERIC, false>(km, X, W, m, out, ld_out, st);
+}
+
+// Requested rows = the m rows staged in the handle's scratch.
+tsvm_status launch_dense_tc2_on(tsvm_km *km, const InstancePlanes &X, int m, float *out, long long ld_out,
+                                cudaStream_t st) {
+    const RowPlanes staged{km->Whi, km->Wlo, km->sd_rows, km->w_unscale};
+    return launch_dense_tc2_planes(km, X, staged, m, out, ld_out, st);
 }
 
 // The same against all instances of the kernel matrix.

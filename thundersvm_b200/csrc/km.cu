@@ -534,6 +534,24 @@ tsvm_status km_rows_staged_on(tsvm_km *km, const InstancePlanes &X, int q, float
     return launch_dense_tc2_on(km, X, q, out, ld_out, st);
 }
 
+tsvm_status launch_dense_tc2_planes(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int m, float *out,
+                                    long long ld_out, cudaStream_t st);   // dense_tc2.cu
+
+tsvm_status km_rows_planes_on(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int q, float *out,
+                              long long ld_out, cudaStream_t st) {
+    return launch_dense_tc2_planes(km, X, W, q, out, ld_out, st);
+}
+
+// Stages m explicit feature rows (m x n_features, stride ldt) with their self dots as the requested rows.
+tsvm_status km_stage_rows_features(tsvm_km *km, const float *T_dev, int ldt, const float *sd_T_dev, int m,
+                                   cudaStream_t st) {
+    TSVM_TRY(ensure_scratch(km, m));
+    TSVM_TRY(ensure_planes(km, st));
+    TSVM_CUDA(cudaMemcpyAsync(km->sd_rows, sd_T_dev, sizeof(float) * m, cudaMemcpyDeviceToDevice, st));
+    TSVM_LAUNCH(stage_rows_dense_kernel, m, 256, 0, st, T_dev, ldt, km->d, km->d, m, row_dst(km));
+    return TSVM_OK;
+}
+
 }  // namespace tsvm
 
 using namespace tsvm;

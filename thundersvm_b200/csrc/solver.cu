@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include <chrono>
 #include <limits.h>
+#include <string.h>
 #include <vector>
 
 namespace tsvm {
@@ -705,6 +706,99 @@ __global__ void scale_kernel(double *a, int n, double r) {
 }
 
 // =================================================================================================
+// Column-sharded solver: per-rank device work of one outer iteration (the exchange steps between the
+// phases belong to the caller)
+// =================================================================================================
+
+// all-gathered candidate lists [world][lists][want] -> [lists][world * want]
+__global__ void shard_regroup_kernel(const double *__restrict__ gf, const int *__restrict__ gi, int world, int lists,
+                                     int want, double *__restrict__ of, int *__restrict__ oi) {
+    const int total = world * lists * want;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        const int r = e / (lists * want), rem = e - r * lists * want, l = rem / want, p = rem - l * want;
+        const size_t o = (size_t) l * world * want + (size_t) r * want + p;
+        of[o] = gf[e];
+        oi[o] = gi[e];
+    }
+}
+
+// Slots 0..q-1 <- slots q..ws-1 (global ids and per-member vectors); in-working-set flags of the owned
+// instances: the old first half leaves, the old second half stays. One block, q <= 512.
+__global__ void shard_shift_kernel(int *ids, int q, int lo, int hi, unsigned char *in_ws, float *m_sd,
+                                   float *m_unscale, float *m_diag) {
+    const int t = threadIdx.x;
+    if (t < q) {
+        const int leaving = ids[t], staying = ids[q + t];
+        if (leaving >= lo && leaving < hi) in_ws[leaving - lo] = 0;
+        if (staying >= lo && staying < hi) in_ws[staying - lo] = 1;
+        ids[t] = staying;
+        m_sd[t] = m_sd[q + t]; m_unscale[t] = m_unscale[q + t]; m_diag[t] = m_diag[q + t];
+    }
+}
+
+// What this rank contributes to the exchange after the selection: for the n_new new members (slots slot0..)
+// their feature row, self dot and diagonal (zeros if another rank owns them) -> crow[s][0..d), [dp], [dp+1]
+// (row stride ldw = dp + 4, dp = round_up(d, 4)); for all ws members (y, f, alpha) -> cstate[slot][3].
+// Summing the contributions of all ranks gives the values (adding zeros is exact).
+__global__ void shard_contrib_kernel(const int *__restrict__ ids, int slot0, int n_new, int ws, int lo, int hi,
+                                     const float *__restrict__ X, int ldx, int d, int dp, const float *__restrict__ sd,
+                                     const float *__restrict__ diag, const int *__restrict__ y,
+                                     const double *__restrict__ f, const double *__restrict__ alpha,
+                                     float *__restrict__ crow, double *__restrict__ cstate) {
+    const int b = blockIdx.x;
+    if (b < n_new) {
+        const int gid = ids[slot0 + b];
+        const bool own = gid >= lo && gid < hi;
+        float *dst = crow + (size_t) b * (dp + 4);
+        const float *src = own ? X + (size_t) (gid - lo) * ldx : nullptr;
+        for (int k = threadIdx.x; k < dp + 4; k += blockDim.x) {
+            float v = 0.0f;
+            if (own) {
+                if (k < d) v = src[k];
+                else if (k == dp) v = sd[gid - lo];
+                else if (k == dp + 1) v = diag[gid - lo];
+            }
+            dst[k] = v;
+        }
+    } else {
+        for (int t = (b - n_new) * blockDim.x + threadIdx.x; t < ws; t += (gridDim.x - n_new) * blockDim.x) {
+            const int gid = ids[t];
+            const bool own = gid >= lo && gid < hi;
+            cstate[3 * t] = own ? (double) y[gid - lo] : 0.0;
+            cstate[3 * t + 1] = own ? f[gid - lo] : 0.0;
+            cstate[3 * t + 2] = own ? alpha[gid - lo] : 0.0;
+        }
+    }
+}
+
+// After the exchange: member vectors of the new slots out of the row buffer, solver inputs out of the state.
+__global__ void shard_unpack_kernel(const float *__restrict__ crow, int slot0, int n_new, int dp, int ws,
+                                    const double *__restrict__ cstate, float *__restrict__ m_sd,
+                                    float *__restrict__ m_diag, int *__restrict__ y_ws, double *__restrict__ f_ws,
+                                    double *__restrict__ a_ws) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n_new) {
+        m_sd[slot0 + t] = crow[(size_t) t * (dp + 4) + dp];
+        m_diag[slot0 + t] = crow[(size_t) t * (dp + 4) + dp + 1];
+    }
+    if (t < ws) {
+        y_ws[t] = (int) cstate[3 * t];
+        f_ws[t] = cstate[3 * t + 1];
+        a_ws[t] = cstate[3 * t + 2];
+    }
+}
+
+// alpha of the owned members back into the rank's slice
+__global__ void shard_scatter_kernel(const int *__restrict__ ids, int ws, int lo, int hi,
+                                     const double *__restrict__ a_ws, double *__restrict__ alpha) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < ws) {
+        const int gid = ids[t];
+        if (gid >= lo && gid < hi) alpha[gid - lo] = a_ws[t];
+    }
+}
+
+// =================================================================================================
 // host side
 // =================================================================================================
 static inline int rows_vec_ok(const float *rows, long long ld) {
@@ -1231,5 +1325,244 @@ tsvm_status tsvm_smo_solve(tsvm_km *km, int solver_kind, const int *y_dev, doubl
     delete S;
     return s;
 }
+
+}  // extern "C"
+
+// Per-rank state of the column-sharded solver. The caller owns the exchange buffers (they are the operands of
+// its collectives): cand_f/cand_id [lists * ws], all_f/all_id [world * lists * ws], crow [ws * (dp + 4)] floats,
+// cstate [ws * 3] doubles.
+struct tsvm_shard {
+    tsvm_km *km = nullptr;
+    int kind = 0, ws = 0, q = 0, n_local = 0, n_total = 0, lo = 0, hi = 0, world = 1, d = 0, dp = 0;
+    const int *y = nullptr;
+    double *alpha = nullptr, *f = nullptr;
+    double eps = 0, Cp = 0, Cn = 0;
+    long long ld = 0;
+    cudaStream_t st = nullptr, st2 = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    // exchange buffers (caller's)
+    double *cand_f = nullptr, *all_f = nullptr, *cstate = nullptr;
+    int *cand_id = nullptr, *all_id = nullptr;
+    float *crow = nullptr;
+    // own buffers
+    int *ids = nullptr, *y_ws = nullptr;
+    float *rows = nullptr, *kww = nullptr, *m_hi = nullptr, *m_lo = nullptr, *m_sd = nullptr, *m_unscale = nullptr,
+          *m_diag = nullptr;
+    double *f_ws = nullptr, *a_ws = nullptr, *alpha_diff = nullptr, *diff = nullptr, *grp_f = nullptr;
+    int *grp_id = nullptr;
+    unsigned char *in_ws = nullptr;
+    tsvm_ws *sel = nullptr;
+    double *diff_host = nullptr;
+    size_t row_bytes = 0;
+    long long iter = 0, local_iter = 0, rows_made = 0, launches0 = 0;
+    int same_cnt = 0, swap_cnt = 0, local_max_iter = 0, n_new = 0, slot0 = 0, phase = 0;
+    double prev = INFINITY, last = INFINITY, second_last = INFINITY, diff0 = 0;
+    bool done = false;
+    std::chrono::steady_clock::time_point t_begin;
+
+    ~tsvm_shard() {
+        cudaFree(ids); cudaFree(y_ws); cudaFree(rows); cudaFree(kww); cudaFree(m_hi); cudaFree(m_lo); cudaFree(m_sd);
+        cudaFree(m_unscale); cudaFree(m_diag); cudaFree(f_ws); cudaFree(a_ws); cudaFree(alpha_diff); cudaFree(diff);
+        cudaFree(grp_f); cudaFree(grp_id); cudaFree(in_ws);
+        tsvm_ws_destroy(sel);
+        if (diff_host) cudaFreeHost(diff_host);
+        if (ev_fork) cudaEventDestroy(ev_fork);
+        if (ev_join) cudaEventDestroy(ev_join);
+        if (st2) cudaStreamDestroy(st2);
+    }
+
+    tsvm_status init() {
+        TSVM_REQUIRE(km_pair_engine(km, st), "shard solver: needs dense data on the CTA-pair tensor engine "
+                                             "(more than 32 features)");
+        row_bytes = km_plane_row_bytes(km);
+        const size_t plane_words = (row_bytes * (size_t) ws + 3) / 4;
+        TSVM_TRY(dev_alloc(&ids, (size_t) ws));
+        TSVM_TRY(dev_alloc(&y_ws, (size_t) ws));
+        TSVM_TRY(dev_alloc(&rows, (size_t) ws * ld));
+        TSVM_TRY(dev_alloc(&kww, (size_t) ws * ws));
+        TSVM_TRY(dev_alloc(&m_hi, plane_words));
+        TSVM_TRY(dev_alloc(&m_lo, plane_words));
+        TSVM_TRY(dev_alloc(&m_sd, (size_t) ws));
+        TSVM_TRY(dev_alloc(&m_unscale, (size_t) ws));
+        TSVM_TRY(dev_alloc(&m_diag, (size_t) ws));
+        TSVM_TRY(dev_alloc(&f_ws, (size_t) ws));
+        TSVM_TRY(dev_alloc(&a_ws, (size_t) ws));
+        TSVM_TRY(dev_alloc(&alpha_diff, (size_t) ws));
+        TSVM_TRY(dev_alloc(&diff, 4));
+        TSVM_TRY(dev_alloc(&grp_f, (size_t) world * MAX_LISTS * ws));
+        TSVM_TRY(dev_alloc(&grp_id, (size_t) world * MAX_LISTS * ws));
+        TSVM_TRY(dev_alloc(&in_ws, (size_t) n_local));
+        TSVM_CUDA(cudaMemsetAsync(in_ws, 0, (size_t) n_local, st));
+        TSVM_TRY(tsvm_ws_create(n_local, ws, &sel));
+        TSVM_CUDA(cudaMallocHost((void **) &diff_host, 4 * sizeof(double)));
+        TSVM_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+        TSVM_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+        int lo_prio = 0, hi_prio = 0;
+        TSVM_CUDA(cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio));
+        TSVM_CUDA(cudaStreamCreateWithPriority(&st2, cudaStreamNonBlocking, hi_prio));
+        local_max_iter = ws > INT_MAX / 100 ? INT_MAX : (100 * ws > 100000 ? 100 * ws : 100000);
+        return TSVM_OK;
+    }
+
+    // phase A: rotate the working set, then this rank's candidate lists (global ids) into cand_f / cand_id
+    tsvm_status candidates(int *lists_out, int *want_out) {
+        TSVM_REQUIRE(phase == 0, "shard solver: phases out of order (candidates)");
+        const int lists = kind == TSVM_SOLVER_C ? 2 : 4;
+        n_new = iter == 0 ? ws : q;
+        slot0 = iter == 0 ? 0 : q;
+        if (iter > 0) {
+            TSVM_LAUNCH(shard_shift_kernel, 1, 1024, 0, st, ids, q, lo, hi, in_ws, m_sd, m_unscale, m_diag);
+            TSVM_CUDA(cudaMemcpyAsync(m_hi, (char *) m_hi + (size_t) q * row_bytes, (size_t) q * row_bytes,
+                                      cudaMemcpyDeviceToDevice, st));
+            TSVM_CUDA(cudaMemcpyAsync(m_lo, (char *) m_lo + (size_t) q * row_bytes, (size_t) q * row_bytes,
+                                      cudaMemcpyDeviceToDevice, st));
+        }
+        TSVM_TRY(tsvm_ws_candidates(sel, kind, n_local, f, alpha, y, iter == 0 ? nullptr : in_ws, Cp, Cn, n_new, lo,
+                                    cand_f, cand_id, st));
+        *lists_out = lists;
+        *want_out = n_new;
+        phase = 1;
+        return TSVM_OK;
+    }
+
+    // phase B: the same merge on every rank over the gathered lists, then this rank's contributions
+    tsvm_status select() {
+        TSVM_REQUIRE(phase == 1, "shard solver: phases out of order (select)");
+        const int lists = kind == TSVM_SOLVER_C ? 2 : 4;
+        const double *mf = all_f;
+        const int *mi = all_id;
+        if (world > 1) {
+            TSVM_LAUNCH(shard_regroup_kernel, ceil_div(world * lists * n_new, 256), 256, 0, st, all_f, all_id, world,
+                        lists, n_new, grp_f, grp_id);
+            mf = grp_f; mi = grp_id;
+        }
+        TSVM_TRY(tsvm_ws_merge(sel, kind, mf, mi, world * n_new, n_new, ids + slot0, st));
+        TSVM_LAUNCH(shard_contrib_kernel, n_new + 4, 256, 0, st, ids, slot0, n_new, ws, lo, hi, km->X, km->ldx, d, dp,
+                    km->self_dot, km->diag, y, f, alpha, crow, cstate);
+        phase = 2;
+        return TSVM_OK;
+    }
+
+    // phase C: everything after the exchange
+    tsvm_status iterate() {
+        TSVM_REQUIRE(phase == 2, "shard solver: phases out of order (iterate)");
+        const int first_half_phys = (int) (iter & 1);
+        TSVM_LAUNCH(shard_unpack_kernel, ceil_div(ws, 256), 256, 0, st, crow, slot0, n_new, dp, ws, cstate, m_sd, m_diag,
+                    y_ws, f_ws, a_ws);
+        TSVM_TRY(km_stage_rows_features(km, crow, dp + 4, m_sd + slot0, n_new, st));
+        TSVM_CUDA(cudaMemcpyAsync((char *) m_hi + (size_t) slot0 * row_bytes, km->Whi, (size_t) n_new * row_bytes,
+                                  cudaMemcpyDeviceToDevice, st));
+        TSVM_CUDA(cudaMemcpyAsync((char *) m_lo + (size_t) slot0 * row_bytes, km->Wlo, (size_t) n_new * row_bytes,
+                                  cudaMemcpyDeviceToDevice, st));
+        TSVM_CUDA(cudaMemcpyAsync(m_unscale + slot0, km->w_unscale, sizeof(float) * n_new, cudaMemcpyDeviceToDevice, st));
+        TSVM_CUDA(cudaEventRecord(ev_fork, st));
+        // second stream: the whole ws x ws block from the members' planes (every rank computes the same
+        // values the owners' row buffers hold), then the local solver, replicated
+        TSVM_CUDA(cudaStreamWaitEvent(st2, ev_fork, 0));
+        const InstancePlanes members{m_hi, m_lo, m_sd, m_unscale, ws};
+        const RowPlanes member_rows{m_hi, m_lo, m_sd, m_unscale};
+        TSVM_TRY(km_rows_planes_on(km, members, member_rows, ws, kww, ws, st2));
+        TSVM_TRY(launch_local_smo(kind, ws, kww, m_diag, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter, diff,
+                                  nullptr, nullptr, st2));
+        TSVM_CUDA(cudaEventRecord(ev_join, st2));
+        // first stream: the new rows against this rank's columns
+        float *new_rows = rows + (size_t) (iter == 0 ? 0 : (1 - first_half_phys) * q) * ld;
+        km->reserve_clusters = 1;
+        const tsvm_status rs = km_rows_staged(km, n_new, new_rows, ld, st);
+        km->reserve_clusters = 0;
+        TSVM_TRY(rs);
+        rows_made += n_new;
+        TSVM_CUDA(cudaStreamWaitEvent(st, ev_join, 0));
+        TSVM_LAUNCH(update_f_kernel, ceil_div(n_local, 512), 128, 0, st, f, n_local, alpha_diff, ws, q, first_half_phys,
+                    rows, ld, rows_vec_ok(rows, ld));
+        TSVM_LAUNCH(shard_scatter_kernel, ceil_div(ws, 256), 256, 0, st, ids, ws, lo, hi, a_ws, alpha);
+        TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaMemcpyAsync(km->status_host, km->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaStreamSynchronize(st));
+        if (km->status_host[0] != 0) {
+            set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", km->status_host[0]);
+            return TSVM_ERR_DEVICE;
+        }
+        diff0 = diff_host[0];
+        local_iter += (long long) diff_host[1];
+        if (fabs(diff0 - prev) < eps * 0.001) same_cnt++;
+        else { same_cnt = 0; prev = diff0; }
+        if (fabs(diff0 - second_last) < eps * 0.001) swap_cnt++;
+        else swap_cnt = 0;
+        second_last = last;
+        last = diff0;
+        if ((same_cnt >= 10 && fabs(diff0 - 2.0) > eps) || diff0 < eps || (swap_cnt >= 10 && fabs(diff0 - 2.0) > eps))
+            done = true;
+        ++iter;
+        phase = 0;
+        return TSVM_OK;
+    }
+};
+
+extern "C" {
+
+tsvm_status tsvm_shard_create(tsvm_km *km_local, int solver_kind, const int *y_dev, double *alpha_dev, double *f_dev,
+                              int n_total, int lo, double eps, double Cp, double Cn, int ws_size, int world,
+                              double *cand_f_dev, int *cand_id_dev, double *all_f_dev, int *all_id_dev,
+                              float *rows_contrib_dev, double *state_contrib_dev, void *stream, tsvm_shard **out) {
+    TSVM_REQUIRE(out && km_local && y_dev && alpha_dev && f_dev && cand_f_dev && cand_id_dev && all_f_dev &&
+                 all_id_dev && rows_contrib_dev && state_contrib_dev, "shard_create: null argument");
+    TSVM_REQUIRE(solver_kind >= 0 && solver_kind <= 2, "shard_create: unknown solver %d", solver_kind);
+    TSVM_REQUIRE(world >= 1 && lo >= 0 && lo + km_local->n <= n_total, "shard_create: bad ownership range");
+    TSVM_REQUIRE(ws_size >= 2 && ws_size <= 1024 && ws_size <= n_total && (ws_size & (ws_size - 1)) == 0 &&
+                 (long long) world * ws_size <= MERGE_MAX_LEN,
+                 "shard_create: working-set size %d must be a power of two in [2, min(n, 1024)] and world * ws <= %d",
+                 ws_size, MERGE_MAX_LEN);
+    *out = nullptr;
+    tsvm_shard *S = new tsvm_shard;
+    S->km = km_local; S->kind = solver_kind; S->y = y_dev; S->alpha = alpha_dev; S->f = f_dev;
+    S->eps = eps; S->Cp = Cp; S->Cn = Cn; S->ws = ws_size; S->q = ws_size / 2;
+    S->n_local = km_local->n; S->n_total = n_total; S->lo = lo; S->hi = lo + km_local->n; S->world = world;
+    S->d = km_local->d; S->dp = (km_local->d + 3) & ~3;
+    S->ld = ((long long) km_local->n + 3) & ~3ll;
+    S->st = (cudaStream_t) stream;
+    S->cand_f = cand_f_dev; S->cand_id = cand_id_dev; S->all_f = all_f_dev; S->all_id = all_id_dev;
+    S->crow = rows_contrib_dev; S->cstate = state_contrib_dev;
+    S->launches0 = launch_count();
+    S->t_begin = std::chrono::steady_clock::now();
+    tsvm_status s = S->init();
+    if (s != TSVM_OK) { delete S; return s; }
+    *out = S;
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_shard_candidates(tsvm_shard *S, int *lists_host, int *want_host) {
+    TSVM_REQUIRE(S && lists_host && want_host, "shard_candidates: null argument");
+    return S->candidates(lists_host, want_host);
+}
+
+tsvm_status tsvm_shard_select(tsvm_shard *S, int *n_new_host) {
+    TSVM_REQUIRE(S && n_new_host, "shard_select: null argument");
+    TSVM_TRY(S->select());
+    *n_new_host = S->n_new;
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_shard_iterate(tsvm_shard *S, int *done_host) {
+    TSVM_REQUIRE(S && done_host, "shard_iterate: null argument");
+    TSVM_TRY(S->iterate());
+    *done_host = S->done ? 1 : 0;
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_shard_get_stats(const tsvm_shard *S, tsvm_solve_stats *out) {
+    TSVM_REQUIRE(S && out, "shard_get_stats: null argument");
+    memset(out, 0, sizeof(*out));
+    out->outer_iters = S->iter;
+    out->local_iters = S->local_iter;
+    out->final_diff = S->diff0;
+    out->objective = NAN;
+    out->seconds_total = std::chrono::duration<double>(std::chrono::steady_clock::now() - S->t_begin).count();
+    out->kernel_rows = S->rows_made;
+    out->gpu_launches = launch_count() - S->launches0;
+    return TSVM_OK;
+}
+
+void tsvm_shard_destroy(tsvm_shard *S) { delete S; }
 
 }  // extern "C"

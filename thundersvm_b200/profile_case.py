@@ -32,6 +32,7 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--d", type=int, default=2000, help="features of the dense cases")
+    ap.add_argument("--no-overlap", action="store_true", help="solver case: run the steps one after the other")
     ap.add_argument("--engine", default="auto", help="dense engine: auto, simt, tensor1, tensor2, tensor")
     args = ap.parse_args()
     capi.lib()
@@ -50,6 +51,7 @@ def main():
         alpha = torch.zeros(n, dtype=torch.float64, device="cuda")
         f = -y.to(torch.float64)
         sv = capi.Solver(km, y, alpha, f, 1e-3, prob["C"], prob["C"], 1024)
+        sv.set_overlap(not args.no_overlap)
         ms = _time(lambda: sv.iterate(1), args.steps)
         print("solver steps (ms):", ["%.3f" % t for t in ms], sv.stats())
         return
