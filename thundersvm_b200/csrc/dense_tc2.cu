@@ -8,9 +8,13 @@
 // instead of 96 KB for the same tensor-core time, and three of them fit the ring instead of two - the
 // single-CTA engine was bound by the latency of its one slab in flight, not by any bandwidth.
 //
-// Roles per CTA (320 threads): warp 0 TMA producer for this CTA's operand halves (transaction bytes
-// are reported to the leader's "full" barrier), warp 1 tensor-memory allocation (both CTAs) and MMA
-// issue (leader only), warps 2..9 slab promotion + epilogue on this CTA's 128 instances.
+// Roles per CTA (384 threads = 3 warpgroups): warp 0 TMA producer for this CTA's operand halves
+// (transaction bytes are reported to the leader's "full" barrier), warp 1 tensor-memory allocation (both
+// CTAs) and MMA issue (leader only), warps 2..3 idle, warps 4..11 slab promotion + epilogue on this CTA's 128
+// instances. Warpgroup 0 hands registers to the other two (setmaxnreg): the epilogue keeps 128 sums per
+// thread live, and with the 168 registers a 384-thread CTA is compiled for it spilled a few loop-invariant
+// values - their reloads from local memory (the L1 is tiny next to 222 KB of shared memory) cost 9 % of
+// the kernel.
 // Barriers: full[s] (leader; both CTAs' TMA bytes), empty[s] (per CTA; MMAs that read the stage have
 // retired), tfull[a] (per CTA; slab sum complete), tempty[a] (leader; 16 epilogue warps drained it).
 // Cross-CTA signalling uses mbarrier arrives on shared::cluster addresses and one tcgen05.commit per
@@ -30,7 +34,11 @@ constexpr int BM = 128, BN = 256, BN_HALF = 128, STAGES = 3, K_STEPS = 4;
 constexpr uint32_t A_BYTES = BM * 128;               // 16 KB per plane (this CTA's instances)
 constexpr uint32_t B_BYTES = BN_HALF * 128;          // 16 KB per plane (this CTA's half of the requested rows)
 constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // 64 KB per CTA
-constexpr int THREADS = 320, EPI_WARPS = 8, COLS_PER_THREAD = 128;
+// 12 warps = 3 warpgroups: warpgroup 0 holds the TMA producer (warp 0), the MMA issuer (warp 1) and two idle
+// warps and gives most of its registers back; warpgroups 1 and 2 are the eight promotion / epilogue warps and
+// take them (a 384-thread CTA is compiled for 168 registers per thread: 128 * 56 + 256 * 224 = 64,512 too).
+constexpr int THREADS = 384, EPI_WARPS = 8, EPI_WARP0 = 4, COLS_PER_THREAD = 128;
+constexpr int REGS_CONTROL = 56, REGS_EPILOGUE = 224;
 // epilogue staging (see the epilogue): EPI_CHUNK sums of each of the 256 epilogue threads, and per warp the
 // self dots and 1/scale of its 128 requested rows
 constexpr int EPI_CHUNK = 16;
@@ -140,6 +148,8 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    if (warp < EPI_WARP0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_CONTROL));
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
         if (lane == 0) {
@@ -198,12 +208,14 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                         }
                     }
         }
+    }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_EPILOGUE));
         // ---------------- slab promotion + epilogue (both CTAs, own 128 instances) ----------------
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
-        float *priv = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256) + (warp - 2) * 32 + lane;
+        const int quarter = warp & 3, half = (warp - EPI_WARP0) >> 2;
+        float *priv = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256) + (warp - EPI_WARP0) * 32 + lane;
         float *rowc = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES) +
-                      (warp - 2) * 2 * COLS_PER_THREAD;
+                      (warp - EPI_WARP0) * 2 * COLS_PER_THREAD;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         for (int item = cluster_id; item < n_items && ok; item += n_clusters) {
