@@ -600,7 +600,8 @@ __global__ void shift_ws_kernel(int *ids, int q, unsigned char *in_ws) {
 // non-zero with 16-byte loads, 8 rows in flight.
 __global__ void __launch_bounds__(128)
 update_f_kernel(double *__restrict__ f, int n, const double *__restrict__ alpha_diff, int ws, int q,
-                int first_half_phys, const float *__restrict__ rows, long long ld, int vec_ok) {
+                int first_half_phys, const float *__restrict__ rows, long long ld, int vec_ok, int t_begin,
+                int t_end) {
     __shared__ double ad[1024];
     __shared__ int prow[1024];
     __shared__ int cnt;
@@ -609,9 +610,10 @@ update_f_kernel(double *__restrict__ f, int n, const double *__restrict__ alpha_
     // order-preserving compaction of the non-zero entries (one warp, ballot scan)
     if (threadIdx.x < 32) {
         int base = 0;
-        for (int t0 = 0; t0 < ws; t0 += 32) {
+        // slots [t_begin, t_end) of the working set (t_begin a multiple of 32)
+        for (int t0 = t_begin; t0 < t_end; t0 += 32) {
             const int t = t0 + threadIdx.x;
-            const double dv = t < ws ? alpha_diff[t] : 0.0;
+            const double dv = t < t_end ? alpha_diff[t] : 0.0;
             const unsigned m = __ballot_sync(0xffffffffu, dv != 0.0);
             if (dv != 0.0) {
                 const int p = base + __popc(m & ((1u << threadIdx.x) - 1));
@@ -999,7 +1001,7 @@ tsvm_status tsvm_update_f(double *f_dev, int n, const double *alpha_diff_dev, in
     TSVM_REQUIRE(f_dev && alpha_diff_dev && rows_dev && n > 0 && ws_size > 0 && ws_size <= 1024 && ld >= n,
                  "update_f: bad arguments (at most 1024 rows per call)");
     TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, (cudaStream_t) stream, f_dev, n, alpha_diff_dev, ws_size,
-                0, 0, rows_dev, ld, rows_vec_ok(rows_dev, ld));
+                0, 0, rows_dev, ld, rows_vec_ok(rows_dev, ld), 0, ws_size);
     return TSVM_OK;
 }
 
@@ -1036,7 +1038,7 @@ struct tsvm_solver {
     // overlapped iteration: second stream, fork / local-solver events, operand planes of the working set
     bool overlap = true;
     cudaStream_t st2 = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_l0 = nullptr, ev_l1 = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_l0 = nullptr, ev_l1 = nullptr;
     float *ws_hi = nullptr, *ws_lo = nullptr, *ws_sd = nullptr, *ws_unscale = nullptr;
     // iteration state (csmosolver.cpp:51-57)
     long long iter = 0, local_iter = 0, rows_made = 0, launches0 = 0;
@@ -1052,7 +1054,7 @@ struct tsvm_solver {
         tsvm_ws_destroy(sel);
         if (diff_host) cudaFreeHost(diff_host);
         for (auto e : ev) if (e) cudaEventDestroy(e);
-        for (auto e : {ev_fork, ev_l0, ev_l1}) if (e) cudaEventDestroy(e);
+        for (auto e : {ev_fork, ev_join, ev_l0, ev_l1}) if (e) cudaEventDestroy(e);
         cudaFree(ws_hi); cudaFree(ws_lo); cudaFree(ws_sd); cudaFree(ws_unscale);
         if (st2) cudaStreamDestroy(st2);
     }
@@ -1086,6 +1088,7 @@ struct tsvm_solver {
         TSVM_CUDA(cudaEventCreate(&ev_l0));
         TSVM_CUDA(cudaEventCreate(&ev_l1));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+        TSVM_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
         {
             int lo_prio = 0, hi_prio = 0;
             TSVM_CUDA(cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio));
@@ -1112,7 +1115,7 @@ struct tsvm_solver {
             TSVM_CUDA(cudaMemcpyAsync(alpha_diff, bd.data(), sizeof(double) * m, cudaMemcpyHostToDevice, st));
             TSVM_TRY(tsvm_km_rows_by_index(km, ids, m, rows, ld, st));
             TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, m, 0, 0, rows, ld,
-                        rows_vec_ok(rows, ld));
+                        rows_vec_ok(rows, ld), 0, m);
             TSVM_CUDA(cudaStreamSynchronize(st));
             rows_made += m;
             bi.clear(); bd.clear();
@@ -1166,6 +1169,11 @@ struct tsvm_solver {
                 TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps,
                                           local_max_iter, diff, ids, alpha, st2));
                 TSVM_CUDA(cudaEventRecord(ev_l1, st2));
+                // the rows that stayed in the buffer can be applied to f at once (HBM-bound, next to the
+                // tensor-bound launch); the new rows follow on the first stream
+                TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st2, f, n, alpha_diff, ws, q, first_half_phys,
+                            rows, ld, rows_vec_ok(rows, ld), 0, q);
+                TSVM_CUDA(cudaEventRecord(ev_join, st2));
                 // first stream: the q full rows on all SM pairs but one
                 km->reserve_clusters = 1;
                 const tsvm_status rs = km_rows_staged(km, q, new_rows, ld, st);
@@ -1183,11 +1191,21 @@ struct tsvm_solver {
                                       diff, ids, alpha, st));
             TSVM_CUDA(cudaEventRecord(ev_l1, st));
         } else {
-            TSVM_CUDA(cudaStreamWaitEvent(st, ev_l1, 0));
+            TSVM_CUDA(cudaStreamWaitEvent(st, ev_join, 0));
         }
         TSVM_CUDA(cudaEventRecord(ev[3], st));
-        TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows, ld,
-                    rows_vec_ok(rows, ld));
+        // f -= sum over the old half's rows, then f -= sum over the new half's rows: two launches in every
+        // form of the iteration, so that all of them round alike (the first iteration has new rows only)
+        if (iter == 0) {
+            TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows,
+                        ld, rows_vec_ok(rows, ld), 0, ws);
+        } else {
+            if (!overlapped)
+                TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys,
+                            rows, ld, rows_vec_ok(rows, ld), 0, q);
+            TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows,
+                        ld, rows_vec_ok(rows, ld), q, ws);
+        }
         TSVM_CUDA(cudaEventRecord(ev[4], st));
         TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaMemcpyAsync(km->status_host, km->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
@@ -1464,6 +1482,9 @@ struct tsvm_shard {
         TSVM_TRY(km_rows_planes_on(km, members, member_rows, ws, kww, ws, st2));
         TSVM_TRY(launch_local_smo(kind, ws, kww, m_diag, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter, diff,
                                   nullptr, nullptr, st2));
+        if (iter > 0)      // the old half's rows are in the buffer already
+            TSVM_LAUNCH(update_f_kernel, ceil_div(n_local, 512), 128, 0, st2, f, n_local, alpha_diff, ws, q,
+                        first_half_phys, rows, ld, rows_vec_ok(rows, ld), 0, q);
         TSVM_CUDA(cudaEventRecord(ev_join, st2));
         // first stream: the new rows against this rank's columns
         float *new_rows = rows + (size_t) (iter == 0 ? 0 : (1 - first_half_phys) * q) * ld;
@@ -1474,7 +1495,7 @@ struct tsvm_shard {
         rows_made += n_new;
         TSVM_CUDA(cudaStreamWaitEvent(st, ev_join, 0));
         TSVM_LAUNCH(update_f_kernel, ceil_div(n_local, 512), 128, 0, st, f, n_local, alpha_diff, ws, q, first_half_phys,
-                    rows, ld, rows_vec_ok(rows, ld));
+                    rows, ld, rows_vec_ok(rows, ld), iter == 0 ? 0 : q, ws);
         TSVM_LAUNCH(shard_scatter_kernel, ceil_div(ws, 256), 256, 0, st, ids, ws, lo, hi, a_ws, alpha);
         TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaMemcpyAsync(km->status_host, km->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
