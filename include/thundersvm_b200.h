@@ -48,6 +48,9 @@ enum { TSVM_HOST = 0, TSVM_DEVICE = 1 };
 const char *tsvm_last_error(void);
 /* ABI version, bumped on any signature change. */
 int tsvm_abi_version(void);
+/* Device and pinned-host memory released by destroyed handles is kept for the next handle of the same
+ * size (the reference frees and reallocates per binary sub-problem); this returns it to the driver. */
+void tsvm_release_cached_memory(void);
 
 /* ------------------------------------------------------------------------------------------
  * KernelMatrix  (replaces include/thundersvm/kernelmatrix.h:46-72,

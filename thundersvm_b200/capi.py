@@ -19,6 +19,7 @@ HOST, DEVICE = 0, 1
 
 # every symbol include/thundersvm_b200.h declares
 EXPORTS = [
+    "tsvm_release_cached_memory",
     "tsvm_last_error", "tsvm_abi_version", "tsvm_km_create_dense", "tsvm_km_create_csr", "tsvm_km_destroy",
     "tsvm_km_n_instances", "tsvm_km_n_features", "tsvm_km_nnz", "tsvm_km_is_dense", "tsvm_km_diag_dev",
     "tsvm_km_self_dot_dev", "tsvm_km_rows_by_index", "tsvm_km_rows_by_instances_dense",

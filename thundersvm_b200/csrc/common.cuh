@@ -46,12 +46,21 @@ void count_launch(int k = 1);
         TSVM_CUDA(cudaPeekAtLastError());                                                        \
     } while (0)
 
+// Device and pinned-host memory of the handles comes from a per-process pool (km.cu): a freed block is
+// kept and handed out again for a request of the same size class instead of going back to the driver.
+// Training a multi-class model creates and destroys a kernel matrix and a solver per class pair; the
+// driver's allocation calls cost more than such a sub-problem's whole solve.
+tsvm_status pool_alloc(void **p, size_t bytes);
+void pool_free(void *p);                      // waits for the device, like cudaFree
+void pool_release();                          // returns every cached block to the driver
+tsvm_status pinned_alloc(void **p, size_t bytes);
+void pinned_free(void *p);
+
 template <typename T>
 inline tsvm_status dev_alloc(T **p, size_t count) {
     *p = nullptr;
     if (count == 0) count = 1;
-    TSVM_CUDA(cudaMalloc((void **) p, count * sizeof(T)));
-    return TSVM_OK;
+    return pool_alloc((void **) p, count * sizeof(T));
 }
 
 inline int ceil_div(long long a, long long b) { return (int) ((a + b - 1) / b); }

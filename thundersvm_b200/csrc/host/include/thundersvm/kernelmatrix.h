@@ -13,6 +13,11 @@ struct tsvm_km;
 class KernelMatrix {
 public:
     explicit KernelMatrix(const DataSet::node2d &instances, SvmParam param);
+    /// rows [r0, r0 + n0) followed by rows [r1, r1 + n1) of a dense row-major matrix that is already on the
+    /// device (d features, row stride ld floats): the binary sub-problem of two classes of a grouped data set
+    /// without a host round trip. No counterpart in the reference, which rebuilds every sub-problem from the
+    /// host instances (svc.cpp:291-316).
+    KernelMatrix(const float *X_dev, size_t d, size_t ld, size_t r0, size_t n0, size_t r1, size_t n1, SvmParam param);
     ~KernelMatrix();
     KernelMatrix(const KernelMatrix &) = delete;
     KernelMatrix &operator=(const KernelMatrix &) = delete;
@@ -34,6 +39,7 @@ private:
     bool dense_ = false;
     SvmParam param_;
     tsvm_km *km_ = nullptr;
+    float *pair_x_ = nullptr;          // device copy of the two row blocks (second constructor)
     mutable SyncArray<kernel_type> diag_;
 };
 #endif

@@ -20,5 +20,16 @@ private:
     void probability_train(const DataSet &dataset);
     void multiclass_probability(const vector<vector<float_type>> &r, vector<float_type> &p) const;
     vector<float_type> c_weight;
+
+protected:
+    // The grouped data set as one dense device matrix, built once per train() when the data qualify for dense
+    // storage; the class pairs then take their rows from it on the device.
+    struct DeviceRows {
+        float *X = nullptr;
+        size_t n = 0, d = 0, ld = 0;
+    };
+    DeviceRows dev_rows_;
+    void build_device_rows(const DataSet &grouped);
+    void free_device_rows();
 };
 #endif

@@ -72,12 +72,31 @@ KernelMatrix::KernelMatrix(const DataSet::node2d &instances, SvmParam param) : p
     thundersvm::copy_to_host(diag_.host_data(), tsvm_km_diag_dev(km_), sizeof(kernel_type) * n_instances_);
 }
 
+KernelMatrix::KernelMatrix(const float *X_dev, size_t d, size_t ld, size_t r0, size_t n0, size_t r1, size_t n1,
+                           SvmParam param) : param_(param) {
+    n_instances_ = n0 + n1;
+    n_features_ = d;
+    nnz_ = n_instances_ * d;
+    dense_ = true;
+    CHECK(n_instances_ > 0) << "KernelMatrix needs at least one instance";
+    pair_x_ = static_cast<float *>(thundersvm::device_alloc(n_instances_ * ld * sizeof(float)));
+    thundersvm::copy_on_device(pair_x_, X_dev + r0 * ld, n0 * ld * sizeof(float));
+    thundersvm::copy_on_device(pair_x_ + n0 * ld, X_dev + r1 * ld, n1 * ld * sizeof(float));
+    b200_check(tsvm_km_create_dense(pair_x_, (int) n_instances_, (int) d, (int) ld, TSVM_DEVICE, param.kernel_type,
+                                    param.degree, (float) param.gamma, (float) param.coef0, nullptr, &km_));
+    const double dense_bytes = 3.0 * n_instances_ * ((n_features_ + 3) & ~3ul) * 4.0 + 1024.0 * n_instances_ * 4.0;
+    thundersvm::total_memory_size() += (size_t) dense_bytes;
+    diag_.resize(n_instances_);
+    thundersvm::copy_to_host(diag_.host_data(), tsvm_km_diag_dev(km_), sizeof(kernel_type) * n_instances_);
+}
+
 KernelMatrix::~KernelMatrix() {
     if (km_) {
         const double dense_bytes = 3.0 * n_instances_ * ((n_features_ + 3) & ~3ul) * 4.0 + 1024.0 * n_instances_ * 4.0;
         thundersvm::total_memory_size() -= (dense_ ? (size_t) dense_bytes : nnz_ * 8 + n_instances_ * 12);
         tsvm_km_destroy(km_);
     }
+    thundersvm::device_free(pair_x_);
 }
 
 void KernelMatrix::get_rows(const SyncArray<int> &idx, SyncArray<kernel_type> &kernel_rows) const {

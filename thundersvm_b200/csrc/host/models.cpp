@@ -322,10 +322,45 @@ void SVC::model_setup(const DataSet &dataset, SvmParam &param) {
     }
 }
 
+// Same storage rule as KernelMatrix (dense unless very sparse or too large), applied to the whole grouped data
+// set; rows are laid out in grouped order so that every class is one contiguous block.
+void SVC::build_device_rows(const DataSet &ds) {
+    free_device_rows();
+    const size_t n = ds.n_instances();
+    if (n == 0) return;
+    size_t nnz = 0;
+    int mx = 0;
+    for (auto &r : ds.instances()) {
+        nnz += r.size();
+        for (auto &nd : r) if (nd.index > mx) mx = nd.index;
+    }
+    const size_t d = (size_t) mx + 1, ld = (d + 3) & ~(size_t) 3;
+    const double density = (double) nnz / ((double) n * d);
+    size_t free_b = 0, total_b = 0;
+    cudaMemGetInfo(&free_b, &total_b);
+    const double bytes = 4.0 * n * ld * 4.0 + 1024.0 * n * 4.0;      // this copy + a pair's matrix and planes + rows
+    if (!((density >= 0.02 || d <= 256) && bytes < 0.6 * (double) free_b)) return;
+    vector<float> X(n * ld, 0.0f);
+    const vector<int> perm = ds.original_index();
+    const DataSet::node2d &ins = ds.instances();
+#pragma omp parallel for schedule(static)
+    for (long k = 0; k < (long) n; ++k)
+        for (auto &nd : ins[perm[k]]) X[(size_t) k * ld + nd.index] = nd.value;
+    dev_rows_.X = static_cast<float *>(thundersvm::device_alloc(n * ld * sizeof(float)));
+    thundersvm::copy_to_device(dev_rows_.X, X.data(), n * ld * sizeof(float));
+    dev_rows_.n = n; dev_rows_.d = d; dev_rows_.ld = ld;
+}
+
+void SVC::free_device_rows() {
+    thundersvm::device_free(dev_rows_.X);
+    dev_rows_ = DeviceRows();
+}
+
 void SVC::train(const DataSet &dataset, SvmParam param) {
     DataSet ds = dataset;
     ds.group_classes();
     model_setup(ds, param);
+    if (n_classes > 2) build_device_rows(ds);       // two classes: one sub-problem, nothing to share
     vector<std::unique_ptr<SyncArray<float_type>>> alpha(n_binary_models);
     vector<char> is_sv(ds.n_instances(), 0);
     int k = 0;
@@ -338,6 +373,7 @@ void SVC::train(const DataSet &dataset, SvmParam param) {
             const float_type *a = alpha[k]->host_data();
             for (size_t l = 0; l < ids.size(); ++l) if (a[l] != 0) is_sv[ids[l]] = 1;
         }
+    free_device_rows();
     // support vectors in class order; n_sv per class
     int *cnt = n_sv.host_data();
     for (int c = 0; c < n_classes; ++c) {
@@ -388,18 +424,24 @@ void SVC::train(const DataSet &dataset, SvmParam param) {
 }
 
 void SVC::train_binary(const DataSet &dataset, int i, int j, SyncArray<float_type> &alpha, float_type &rho) {
-    const DataSet::node2d ins = dataset.instances(i, j);
     const int ci = dataset.count()[i], cj = dataset.count()[j];
-    SyncArray<int> y(ins.size());
-    SyncArray<float_type> f_val(ins.size());
-    alpha.resize(ins.size());
+    const size_t n_pair = (size_t) ci + cj;
+    SyncArray<int> y(n_pair);
+    SyncArray<float_type> f_val(n_pair);
+    alpha.resize(n_pair);
     alpha.mem_set(0);
     for (int l = 0; l < ci + cj; ++l) {
         y.host_data()[l] = l < ci ? +1 : -1;
         f_val.host_data()[l] = l < ci ? -1 : +1;
     }
-    KernelMatrix k_mat(ins, param);
-    const int ws_size = get_working_set_size((int) ins.size(), (int) k_mat.n_features());
+    std::unique_ptr<KernelMatrix> k_mat_ptr;
+    if (dev_rows_.X)
+        k_mat_ptr.reset(new KernelMatrix(dev_rows_.X, dev_rows_.d, dev_rows_.ld, dataset.start()[i], ci, dataset.start()[j],
+                                         cj, param));
+    else
+        k_mat_ptr.reset(new KernelMatrix(dataset.instances(i, j), param));
+    KernelMatrix &k_mat = *k_mat_ptr;
+    const int ws_size = get_working_set_size((int) n_pair, (int) k_mat.n_features());
     CSMOSolver solver;
     solver.solve(k_mat, y, alpha, rho, f_val, param.epsilon, param.C * c_weight[i], param.C * c_weight[j], ws_size,
                  max_iter);
@@ -417,20 +459,26 @@ void NuSVC::model_setup(const DataSet &dataset, SvmParam &param) {
 }
 
 void NuSVC::train_binary(const DataSet &dataset, int i, int j, SyncArray<float_type> &alpha, float_type &rho) {
-    const DataSet::node2d ins = dataset.instances(i, j);
     const int n_pos = dataset.count()[i], n_neg = dataset.count()[j];
-    SyncArray<int> y(ins.size());
-    SyncArray<float_type> f_val(ins.size());
-    alpha.resize(ins.size());
+    const size_t n_pair = (size_t) n_pos + n_neg;
+    SyncArray<int> y(n_pair);
+    SyncArray<float_type> f_val(n_pair);
+    alpha.resize(n_pair);
     f_val.mem_set(0);
     // nusvc.cpp:16-28: nu * n / 2 of alpha mass per class, filled from the front
-    float_type budget_p = param.nu * ins.size() / 2, budget_n = budget_p;
+    float_type budget_p = param.nu * n_pair / 2, budget_n = budget_p;
     float_type *a = alpha.host_data();
     int *yy = y.host_data();
     for (int l = 0; l < n_pos; ++l) { yy[l] = +1; a[l] = std::min(1., budget_p); budget_p -= a[l]; }
     for (int l = n_pos; l < n_pos + n_neg; ++l) { yy[l] = -1; a[l] = std::min(1., budget_n); budget_n -= a[l]; }
-    KernelMatrix k_mat(ins, param);
-    const int ws_size = get_working_set_size((int) ins.size(), (int) k_mat.n_features());
+    std::unique_ptr<KernelMatrix> k_mat_ptr;
+    if (dev_rows_.X)
+        k_mat_ptr.reset(new KernelMatrix(dev_rows_.X, dev_rows_.d, dev_rows_.ld, dataset.start()[i], n_pos,
+                                         dataset.start()[j], n_neg, param));
+    else
+        k_mat_ptr.reset(new KernelMatrix(dataset.instances(i, j), param));
+    KernelMatrix &k_mat = *k_mat_ptr;
+    const int ws_size = get_working_set_size((int) n_pair, (int) k_mat.n_features());
     NuSMOSolver solver(false);
     solver.solve(k_mat, y, alpha, rho, f_val, param.epsilon, 1, 1, ws_size, max_iter);
     LOG(INFO) << "rho = " << rho;

@@ -5,6 +5,7 @@
 #include <thundersvm/svmparam.h>
 #include <thundersvm/util/metric.h>
 #include <cuda_runtime.h>
+#include "../common.cuh"
 
 namespace thundersvm {
 bool g_verbose = true;
@@ -15,12 +16,16 @@ static void cuda_ok(cudaError_t e, const char *what) {
     if (e == cudaErrorMemoryAllocation) throw std::bad_alloc();       // reference: util/common.h:33-39
     LOG(FATAL) << what << ": " << cudaGetErrorString(e);
 }
+// SyncArray memory comes from the library's pool (a model trains one binary problem per class pair, each
+// with its own arrays)
 void *device_alloc(size_t bytes) {
     void *p = nullptr;
-    cuda_ok(cudaMalloc(&p, bytes ? bytes : 1), "cudaMalloc");
+    const tsvm_status s = tsvm::pool_alloc(&p, bytes ? bytes : 1);
+    if (s == TSVM_ERR_OOM) throw std::bad_alloc();                    // reference: util/common.h:33-39
+    if (s != TSVM_OK) LOG(FATAL) << "device allocation: " << tsvm_last_error();
     return p;
 }
-void device_free(void *p) { if (p) cudaFree(p); }
+void device_free(void *p) { tsvm::pool_free(p); }
 void copy_to_device(void *dst, const void *src, size_t bytes) { cuda_ok(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice), "H2D copy"); }
 void copy_to_host(void *dst, const void *src, size_t bytes) { cuda_ok(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost), "D2H copy"); }
 void copy_on_device(void *dst, const void *src, size_t bytes) { cuda_ok(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToDevice), "D2D copy"); }

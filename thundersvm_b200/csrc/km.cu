@@ -5,6 +5,10 @@
 #include <cuda_fp16.h>
 #include <string.h>
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
 
 namespace tsvm {
 
@@ -19,6 +23,99 @@ void set_error(const char *fmt, ...) {
 }
 long long launch_count() { return g_launches.load(); }
 void count_launch(int k) { g_launches.fetch_add(k); }
+
+// ---- memory pool -------------------------------------------------------------------------------------
+// Size classes: eight per power of two (at most 12.5 % slack), 512 bytes at least. Blocks are per device.
+namespace {
+struct PoolBlock { int dev; size_t cls; };
+// never destroyed: handles may be released after the static destructors of this library have run
+std::mutex &g_pool_mu = *new std::mutex;
+auto &g_pool_live = *new std::unordered_map<void *, PoolBlock>;
+auto &g_pinned_live = *new std::unordered_map<void *, PoolBlock>;
+auto &g_pool_free = *new std::map<std::pair<int, size_t>, std::vector<void *>>;
+auto &g_pinned_free = *new std::map<size_t, std::vector<void *>>;
+
+size_t size_class(size_t bytes) {
+    if (bytes < 512) return 512;
+    size_t p2 = 512;
+    while (p2 < bytes) p2 <<= 1;          // smallest power of two >= bytes
+    const size_t step = p2 >> 4;          // eighths of the previous power of two
+    return (bytes + step - 1) / step * step;
+}
+}  // namespace
+
+void pool_release() {
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    int cur = 0;
+    cudaGetDevice(&cur);
+    for (auto &kv : g_pool_free) {
+        if (kv.second.empty()) continue;
+        cudaSetDevice(kv.first.first);
+        for (void *q : kv.second) cudaFree(q);
+        kv.second.clear();
+    }
+    cudaSetDevice(cur);
+}
+
+tsvm_status pool_alloc(void **p, size_t bytes) {
+    *p = nullptr;
+    int dev = 0;
+    TSVM_CUDA(cudaGetDevice(&dev));
+    const size_t cls = size_class(bytes);
+    {
+        std::lock_guard<std::mutex> lk(g_pool_mu);
+        auto it = g_pool_free.find({dev, cls});
+        if (it != g_pool_free.end() && !it->second.empty()) {
+            *p = it->second.back();
+            it->second.pop_back();
+            g_pool_live[*p] = PoolBlock{dev, cls};
+            return TSVM_OK;
+        }
+    }
+    cudaError_t e = cudaMalloc(p, cls);
+    if (e == cudaErrorMemoryAllocation) {      // give the cached blocks back and try once more
+        cudaGetLastError();
+        pool_release();
+        e = cudaMalloc(p, cls);
+    }
+    TSVM_CUDA(e);
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    g_pool_live[*p] = PoolBlock{dev, cls};
+    return TSVM_OK;
+}
+
+void pool_free(void *p) {
+    if (!p) return;
+    cudaDeviceSynchronize();                  // nothing in flight may still use the block when it is reused
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    auto it = g_pool_live.find(p);
+    if (it == g_pool_live.end()) { cudaFree(p); return; }     // not ours (never happens for handle memory)
+    g_pool_free[{it->second.dev, it->second.cls}].push_back(p);
+    g_pool_live.erase(it);
+}
+
+tsvm_status pinned_alloc(void **p, size_t bytes) {
+    *p = nullptr;
+    const size_t cls = size_class(bytes);
+    {
+        std::lock_guard<std::mutex> lk(g_pool_mu);
+        auto &v = g_pinned_free[cls];
+        if (!v.empty()) { *p = v.back(); v.pop_back(); g_pinned_live[*p] = PoolBlock{0, cls}; return TSVM_OK; }
+    }
+    TSVM_CUDA(cudaMallocHost(p, cls));
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    g_pinned_live[*p] = PoolBlock{0, cls};
+    return TSVM_OK;
+}
+
+void pinned_free(void *p) {
+    if (!p) return;
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    auto it = g_pinned_live.find(p);
+    if (it == g_pinned_live.end()) { cudaFreeHost(p); return; }
+    g_pinned_free[it->second.cls].push_back(p);
+    g_pinned_live.erase(it);
+}
 
 tsvm_status launch_dense_tc(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st);  // dense_tc.cu
 
@@ -395,8 +492,8 @@ static tsvm_status ensure_scratch(tsvm_km *km, int m) {
     if (m <= km->w_cap) return TSVM_OK;
     int cap = 128;
     while (cap < m) cap *= 2;
-    cudaFree(km->W); cudaFree(km->Whi); cudaFree(km->Wlo); cudaFree(km->WT); cudaFree(km->sd_rows);
-    cudaFree(km->w_unscale);
+    pool_free(km->W); pool_free(km->Whi); pool_free(km->Wlo); pool_free(km->WT); pool_free(km->sd_rows);
+    pool_free(km->w_unscale);
     km->W = km->Whi = km->Wlo = km->WT = km->sd_rows = km->w_unscale = nullptr;
     km->w_cap = 0;
     TSVM_TRY(dev_alloc(&km->sd_rows, (size_t) cap));
@@ -429,7 +526,7 @@ static inline int wanted_plane_kind(const tsvm_km *km) {
 static tsvm_status ensure_planes(tsvm_km *km, cudaStream_t st) {
     const int kind = wanted_plane_kind(km);
     if (kind == 0 || kind == km->plane_kind) return TSVM_OK;
-    cudaFree(km->Xhi); cudaFree(km->Xlo);
+    pool_free(km->Xhi); pool_free(km->Xlo);
     km->Xhi = km->Xlo = nullptr;
     km->plane_kind = 0;
     km->plane_ld = kind == 1 ? km->d_pad : (km->d + 7) & ~7;
@@ -456,7 +553,7 @@ static tsvm_status finish_create(tsvm_km *km, cudaStream_t st) {
     TSVM_TRY(dev_alloc(&km->diag, (size_t) km->n));
     TSVM_TRY(dev_alloc(&km->status_dev, 4));
     TSVM_CUDA(cudaMemsetAsync(km->status_dev, 0, 4 * sizeof(int), st));
-    TSVM_CUDA(cudaMallocHost((void **) &km->status_host, 4 * sizeof(int)));
+    TSVM_TRY(pinned_alloc((void **) &km->status_host, 4 * sizeof(int)));
     const int blocks = ceil_div((long long) km->n * 32, 256);
     if (km->dense)
         TSVM_LAUNCH(self_dot_dense_kernel, blocks, 256, 0, st, km->X, km->n, km->d, km->ldx, km->self_dot);
@@ -560,6 +657,7 @@ extern "C" {
 
 const char *tsvm_last_error(void) { return tsvm::g_err; }
 int tsvm_abi_version(void) { return 1; }
+void tsvm_release_cached_memory(void) { tsvm::pool_release(); }
 
 tsvm_status tsvm_km_create_dense(const float *X, int n, int d, int ld, int loc, int kernel_type, int degree,
                                  float gamma, float coef0, void *stream, tsvm_km **out) {
@@ -632,12 +730,12 @@ tsvm_status tsvm_km_create_csr(const float *val, const int *row_ptr, const int *
 
 void tsvm_km_destroy(tsvm_km *km) {
     if (!km) return;
-    cudaFree(km->X_owned); cudaFree(km->Xhi); cudaFree(km->Xlo); cudaFree(km->x_unscale); cudaFree(km->w_unscale);
-    cudaFree(km->val_owned); cudaFree(km->row_ptr_owned); cudaFree(km->col_owned);
-    cudaFree(km->self_dot); cudaFree(km->diag);
-    cudaFree(km->W); cudaFree(km->Whi); cudaFree(km->Wlo); cudaFree(km->WT); cudaFree(km->sd_rows);
-    cudaFree(km->status_dev);
-    if (km->status_host) cudaFreeHost(km->status_host);
+    pool_free(km->X_owned); pool_free(km->Xhi); pool_free(km->Xlo); pool_free(km->x_unscale); pool_free(km->w_unscale);
+    pool_free(km->val_owned); pool_free(km->row_ptr_owned); pool_free(km->col_owned);
+    pool_free(km->self_dot); pool_free(km->diag);
+    pool_free(km->W); pool_free(km->Whi); pool_free(km->Wlo); pool_free(km->WT); pool_free(km->sd_rows);
+    pool_free(km->status_dev);
+    if (km->status_host) pinned_free(km->status_host);
     delete km;
 }
 

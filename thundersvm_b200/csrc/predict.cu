@@ -115,8 +115,8 @@ tsvm_status tsvm_predict_dec(tsvm_km *km_sv, const double *coef_dev, const int *
             s = TSVM_ERR_DEVICE;
         }
     } else cudaStreamSynchronize(st);
-    cudaFree(K);
-    cudaFree(meta);
+    pool_free(K);
+    pool_free(meta);
     return s;
 }
 

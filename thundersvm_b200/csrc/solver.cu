@@ -858,8 +858,8 @@ tsvm_status tsvm_ws_create(int n_max, int ws_max, tsvm_ws **out) {
 
 void tsvm_ws_destroy(tsvm_ws *w) {
     if (!w) return;
-    cudaFree(w->state); cudaFree(w->hist); cudaFree(w->ticket); cudaFree(w->count);
-    cudaFree(w->cand_f); cudaFree(w->cand_id);
+    pool_free(w->state); pool_free(w->hist); pool_free(w->ticket); pool_free(w->count);
+    pool_free(w->cand_f); pool_free(w->cand_id);
     delete w;
 }
 
@@ -1049,13 +1049,13 @@ struct tsvm_solver {
     std::chrono::steady_clock::time_point t_begin;
 
     ~tsvm_solver() {
-        cudaFree(ids); cudaFree(y_ws); cudaFree(rows); cudaFree(kww); cudaFree(diag_ws); cudaFree(f_ws);
-        cudaFree(a_ws); cudaFree(alpha_diff); cudaFree(diff); cudaFree(red); cudaFree(in_ws);
+        pool_free(ids); pool_free(y_ws); pool_free(rows); pool_free(kww); pool_free(diag_ws); pool_free(f_ws);
+        pool_free(a_ws); pool_free(alpha_diff); pool_free(diff); pool_free(red); pool_free(in_ws);
         tsvm_ws_destroy(sel);
-        if (diff_host) cudaFreeHost(diff_host);
+        if (diff_host) pinned_free(diff_host);
         for (auto e : ev) if (e) cudaEventDestroy(e);
         for (auto e : {ev_fork, ev_join, ev_l0, ev_l1}) if (e) cudaEventDestroy(e);
-        cudaFree(ws_hi); cudaFree(ws_lo); cudaFree(ws_sd); cudaFree(ws_unscale);
+        pool_free(ws_hi); pool_free(ws_lo); pool_free(ws_sd); pool_free(ws_unscale);
         if (st2) cudaStreamDestroy(st2);
     }
 
@@ -1083,7 +1083,7 @@ struct tsvm_solver {
         TSVM_TRY(dev_alloc(&in_ws, (size_t) n));
         TSVM_CUDA(cudaMemsetAsync(in_ws, 0, (size_t) n, st));
         TSVM_TRY(tsvm_ws_create(n, ws, &sel));
-        TSVM_CUDA(cudaMallocHost((void **) &diff_host, 16 * sizeof(double)));
+        TSVM_TRY(pinned_alloc((void **) &diff_host, 16 * sizeof(double)));
         for (auto &e : ev) TSVM_CUDA(cudaEventCreate(&e));
         TSVM_CUDA(cudaEventCreate(&ev_l0));
         TSVM_CUDA(cudaEventCreate(&ev_l1));
@@ -1379,11 +1379,11 @@ struct tsvm_shard {
     std::chrono::steady_clock::time_point t_begin;
 
     ~tsvm_shard() {
-        cudaFree(ids); cudaFree(y_ws); cudaFree(rows); cudaFree(kww); cudaFree(m_hi); cudaFree(m_lo); cudaFree(m_sd);
-        cudaFree(m_unscale); cudaFree(m_diag); cudaFree(f_ws); cudaFree(a_ws); cudaFree(alpha_diff); cudaFree(diff);
-        cudaFree(grp_f); cudaFree(grp_id); cudaFree(in_ws);
+        pool_free(ids); pool_free(y_ws); pool_free(rows); pool_free(kww); pool_free(m_hi); pool_free(m_lo); pool_free(m_sd);
+        pool_free(m_unscale); pool_free(m_diag); pool_free(f_ws); pool_free(a_ws); pool_free(alpha_diff); pool_free(diff);
+        pool_free(grp_f); pool_free(grp_id); pool_free(in_ws);
         tsvm_ws_destroy(sel);
-        if (diff_host) cudaFreeHost(diff_host);
+        if (diff_host) pinned_free(diff_host);
         if (ev_fork) cudaEventDestroy(ev_fork);
         if (ev_join) cudaEventDestroy(ev_join);
         if (st2) cudaStreamDestroy(st2);
@@ -1412,7 +1412,7 @@ struct tsvm_shard {
         TSVM_TRY(dev_alloc(&in_ws, (size_t) n_local));
         TSVM_CUDA(cudaMemsetAsync(in_ws, 0, (size_t) n_local, st));
         TSVM_TRY(tsvm_ws_create(n_local, ws, &sel));
-        TSVM_CUDA(cudaMallocHost((void **) &diff_host, 4 * sizeof(double)));
+        TSVM_TRY(pinned_alloc((void **) &diff_host, 4 * sizeof(double)));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
         int lo_prio = 0, hi_prio = 0;
