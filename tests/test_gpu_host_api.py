@@ -117,3 +117,31 @@ def test_cli_train_predict_cross_validation(fx, tmp_path):
     assert r.returncode == 0, r.stdout
     acc = float(r.stdout.strip().split("Cross Accuracy = ")[1].split()[0])
     assert abs(acc - 0.973) < 1e-3
+
+
+def test_cached_memory_is_reused_and_released(capi):
+    """Handles give their device memory back to the library's pool; tsvm_release_cached_memory returns it to
+    the driver. Creating, destroying and re-creating kernel matrices of the same size must neither grow
+    the memory in use nor break after a release."""
+    import torch
+    from thundersvm_b200 import synth
+    prob = synth.config5(4000, d=256)
+    X = torch.from_numpy(prob["X"]).cuda()
+    idx = torch.arange(0, 512, dtype=torch.int32, device="cuda")
+
+    def cycle():
+        km = capi.KernelMatrix(dense=X, gamma=0.5)
+        rows = km.get_rows(idx).clone()
+        km.close()
+        return rows
+
+    first = cycle()
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(5):
+        assert torch.equal(cycle(), first)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] >= free_before - (8 << 20)     # no growth beyond the cached blocks
+    capi.lib().tsvm_release_cached_memory()
+    assert torch.cuda.mem_get_info()[0] >= free_before
+    assert torch.equal(cycle(), first)

@@ -60,6 +60,8 @@ def lib():
     vp, i, f, d, ll, sz = C.c_void_p, C.c_int, C.c_float, C.c_double, C.c_longlong, C.c_size_t
     L.tsvm_last_error.restype = C.c_char_p
     L.tsvm_abi_version.restype = i
+    L.tsvm_release_cached_memory.restype = None
+    L.tsvm_release_cached_memory.argtypes = []
     L.tsvm_km_create_dense.argtypes = [vp, i, i, i, i, i, i, f, f, vp, C.POINTER(vp)]
     L.tsvm_km_create_csr.argtypes = [vp, vp, vp, i, i, i, i, i, f, f, vp, C.POINTER(vp)]
     L.tsvm_km_destroy.argtypes = [vp]
