@@ -597,7 +597,7 @@ __global__ void shift_ws_kernel(int *ids, int q, unsigned char *in_ws) {
 // f update:  f[j] -= sum_t alpha_diff[t] * rows[phys(t)][j]   (smo_kernel.cu:289-310)
 // =================================================================================================
 // HBM-bound: every thread owns 4 consecutive columns and streams the rows whose alpha_diff is
-// non-zero with 16-byte loads, 8 rows in flight.
+// non-zero with 16-byte loads, 16 rows in flight.
 __global__ void __launch_bounds__(128)
 update_f_kernel(double *__restrict__ f, int n, const double *__restrict__ alpha_diff, int ws, int q,
                 int first_half_phys, const float *__restrict__ rows, long long ld, int vec_ok, int t_begin,
@@ -631,12 +631,12 @@ update_f_kernel(double *__restrict__ f, int n, const double *__restrict__ alpha_
     double s0 = 0, s1 = 0, s2 = 0, s3 = 0;
     if (j + 3 < n && vec_ok) {
         int r = 0;
-        for (; r + 8 <= m; r += 8) {
-            float4 v[8];
+        for (; r + 16 <= m; r += 16) {
+            float4 v[16];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = __ldcs(reinterpret_cast<const float4 *>(rows + (size_t) prow[r + u] * ld + j));
+            for (int u = 0; u < 16; ++u) v[u] = __ldcs(reinterpret_cast<const float4 *>(rows + (size_t) prow[r + u] * ld + j));
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < 16; ++u) {
                 const double dv = ad[r + u];
                 s0 += dv * v[u].x; s1 += dv * v[u].y; s2 += dv * v[u].z; s3 += dv * v[u].w;
             }
