@@ -201,7 +201,8 @@ def run_b200_arm(args):
 
     if world > 1:
         from thundersvm_b200 import sharded
-        line = sharded.bench(args, rank, world, local_rank)
+        line = sharded.bench(args, rank, world, local_rank, clock_sampler=ClockSampler(local_rank) if rank == 0 else None,
+                             peaks=measured_peaks())
         if rank == 0:
             print(json.dumps(line))
         dist.destroy_process_group()

@@ -1357,7 +1357,8 @@ struct tsvm_shard {
     double eps = 0, Cp = 0, Cn = 0;
     long long ld = 0;
     cudaStream_t st = nullptr, st2 = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_r0 = nullptr, ev_r1 = nullptr, ev_b0 = nullptr, ev_b1 = nullptr;
+    double t_rows = 0, t_loc = 0;    // ms: kernel-row launch (first stream); block + local solver (second stream)
     // exchange buffers (caller's)
     double *cand_f = nullptr, *all_f = nullptr, *cstate = nullptr;
     int *cand_id = nullptr, *all_id = nullptr;
@@ -1384,8 +1385,7 @@ struct tsvm_shard {
         pool_free(grp_f); pool_free(grp_id); pool_free(in_ws);
         tsvm_ws_destroy(sel);
         if (diff_host) pinned_free(diff_host);
-        if (ev_fork) cudaEventDestroy(ev_fork);
-        if (ev_join) cudaEventDestroy(ev_join);
+        for (auto e : {ev_fork, ev_join, ev_r0, ev_r1, ev_b0, ev_b1}) if (e) cudaEventDestroy(e);
         if (st2) cudaStreamDestroy(st2);
     }
 
@@ -1415,6 +1415,7 @@ struct tsvm_shard {
         TSVM_TRY(pinned_alloc((void **) &diff_host, 4 * sizeof(double)));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+        for (auto e : {&ev_r0, &ev_r1, &ev_b0, &ev_b1}) TSVM_CUDA(cudaEventCreate(e));
         int lo_prio = 0, hi_prio = 0;
         TSVM_CUDA(cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio));
         TSVM_CUDA(cudaStreamCreateWithPriority(&st2, cudaStreamNonBlocking, hi_prio));
@@ -1479,9 +1480,11 @@ struct tsvm_shard {
         TSVM_CUDA(cudaStreamWaitEvent(st2, ev_fork, 0));
         const InstancePlanes members{m_hi, m_lo, m_sd, m_unscale, ws};
         const RowPlanes member_rows{m_hi, m_lo, m_sd, m_unscale};
+        TSVM_CUDA(cudaEventRecord(ev_b0, st2));
         TSVM_TRY(km_rows_planes_on(km, members, member_rows, ws, kww, ws, st2));
         TSVM_TRY(launch_local_smo(kind, ws, kww, m_diag, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter, diff,
                                   nullptr, nullptr, st2));
+        TSVM_CUDA(cudaEventRecord(ev_b1, st2));
         if (iter > 0)      // the old half's rows are in the buffer already
             TSVM_LAUNCH(update_f_kernel, ceil_div(n_local, 512), 128, 0, st2, f, n_local, alpha_diff, ws, q,
                         first_half_phys, rows, ld, rows_vec_ok(rows, ld), 0, q);
@@ -1489,9 +1492,11 @@ struct tsvm_shard {
         // first stream: the new rows against this rank's columns
         float *new_rows = rows + (size_t) (iter == 0 ? 0 : (1 - first_half_phys) * q) * ld;
         km->reserve_clusters = 1;
+        TSVM_CUDA(cudaEventRecord(ev_r0, st));
         const tsvm_status rs = km_rows_staged(km, n_new, new_rows, ld, st);
         km->reserve_clusters = 0;
         TSVM_TRY(rs);
+        TSVM_CUDA(cudaEventRecord(ev_r1, st));
         rows_made += n_new;
         TSVM_CUDA(cudaStreamWaitEvent(st, ev_join, 0));
         TSVM_LAUNCH(update_f_kernel, ceil_div(n_local, 512), 128, 0, st, f, n_local, alpha_diff, ws, q, first_half_phys,
@@ -1504,6 +1509,9 @@ struct tsvm_shard {
             set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", km->status_host[0]);
             return TSVM_ERR_DEVICE;
         }
+        float ms_ev = 0;
+        cudaEventElapsedTime(&ms_ev, ev_r0, ev_r1); t_rows += ms_ev;
+        cudaEventElapsedTime(&ms_ev, ev_b0, ev_b1); t_loc += ms_ev;
         diff0 = diff_host[0];
         local_iter += (long long) diff_host[1];
         if (fabs(diff0 - prev) < eps * 0.001) same_cnt++;
@@ -1578,6 +1586,8 @@ tsvm_status tsvm_shard_get_stats(const tsvm_shard *S, tsvm_solve_stats *out) {
     out->local_iters = S->local_iter;
     out->final_diff = S->diff0;
     out->objective = NAN;
+    out->seconds_rows = S->t_rows * 1e-3;
+    out->seconds_local = S->t_loc * 1e-3;       // ws x ws block + local solver, on the second stream
     out->seconds_total = std::chrono::duration<double>(std::chrono::steady_clock::now() - S->t_begin).count();
     out->kernel_rows = S->rows_made;
     out->gpu_launches = launch_count() - S->launches0;

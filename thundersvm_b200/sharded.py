@@ -374,9 +374,25 @@ def predict_rows(n_test, rank, world):
 
 
 # ---- benchmark entry used by bench.py for N > 1 --------------------------------------------------------
-def bench(args, rank, world, local_rank):
-    """Strong scaling of config 5: the same problem, instance columns sharded over `world` GPUs."""
-    from . import synth
+def _gather_rows(t, group=None):
+    """Concatenation over ranks of tensors that differ in their first dimension."""
+    world = dist.get_world_size(group)
+    cnt = torch.tensor([t.shape[0]], device=t.device)
+    cnts = [torch.zeros_like(cnt) for _ in range(world)]
+    dist.all_gather(cnts, cnt, group=group)
+    cnts = [int(c.item()) for c in cnts]
+    mx = max(max(cnts), 1)
+    pad = torch.zeros((mx,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+    pad[:t.shape[0]] = t
+    parts = [torch.empty_like(pad) for _ in range(world)]
+    dist.all_gather(parts, pad, group=group)
+    return torch.cat([p[:c] for p, c in zip(parts, cnts)], 0)
+
+
+def bench(args, rank, world, local_rank, clock_sampler=None, peaks=None):
+    """Strong scaling of config 5: the same problem, instance columns sharded over `world` GPUs; then the
+    whole training run to eps and the prediction of the test rows, split evenly over the ranks."""
+    from . import capi, synth
     n, d, ws, q = args.rows, 2000, 1024, 512
     gamma, C, eps = 0.5, 1.0, 1e-3
     K, W = args.steps, max(3, args.warmup)
@@ -385,50 +401,129 @@ def bench(args, rank, world, local_rank):
     y_np = np.where(prob["y"] > 0, 1, -1).astype(np.int32)
     Xh = torch.from_numpy(prob["X"][lo:hi]).pin_memory()
     del prob
-    ops = CapiOps()
 
-    def make(from_host):
+    def make():
         X = Xh.cuda(non_blocking=True)
         y = torch.from_numpy(y_np[lo:hi]).cuda()
         f = -y.to(torch.float64)
         a = torch.zeros(hi - lo, dtype=torch.float64, device="cuda")
-        return NativeShardedSolver(X, y, a, f, n, lo, eps, C, C, ws, gamma=gamma), a
+        return NativeShardedSolver(X, y, a, f, n, lo, eps, C, C, ws, gamma=gamma), a, X, y
+
+    def max_over_ranks(v):
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     # resident: W warm-up steps, K timed steps, device time, max over ranks
-    sv, _ = make(False)
+    sv, _, _, _ = make()
     sv.iterate(W)
     torch.cuda.synchronize()
+    s0 = sv.shard.stats()
     dist.barrier()
     torch.cuda.synchronize()
+    if clock_sampler is not None:
+        clock_sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    rows0 = sv.rows_made
     e0.record()
     sv.iterate(K)
     e1.record()
     torch.cuda.synchronize()
     dist.barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms.item())
-    rows_timed = sv.rows_made - rows0
-    launches = sv.shard.stats()["gpu_launches"]
+    clk = clock_sampler.stop() if clock_sampler is not None else None
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    s1 = sv.shard.stats()
+    rows_timed = s1["kernel_rows"] - s0["kernel_rows"]
+    launches = s1["gpu_launches"] - s0["gpu_launches"]
+    t_rows = max_over_ranks((s1["seconds_rows"] - s0["seconds_rows"]) / K)
+    t_loc = max_over_ranks((s1["seconds_local"] - s0["seconds_local"]) / K)
     sv.close()
     del sv
     torch.cuda.empty_cache()
+    achieved = 2.0 * q * (hi - lo) * d / t_rows / 1e12          # per GPU, this rank's launch
+    achieved = max_over_ranks(-achieved) * -1.0                   # the slowest rank's figure
+    peak, peak_sustained, peak_src = peaks if peaks else (1590.0, 1400.0, "of fallback (1.59 PFLOP/s burst)")
+    roofline = {"bound": "tensor", "kernel": "dense_rows_tc2_kernel<EPI_RBF, F16>, per GPU: 512 rows x n/N instances",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "issued_frac": 3 * achieved / peak, "traffic": None, "peak_source": peak_src,
+                "ms_per_launch": t_rows * 1e3}
 
     # end to end from host buffers: H2D of the shard, set-up, W+K steps, D2H of alpha
     torch.cuda.synchronize()
     dist.barrier()
     t0 = time.perf_counter()
-    sv, a = make(True)
+    sv, a, _, _ = make()
     sv.iterate(W + K)
     rho, st = sv.finish()
     a_host = a.cpu()
     torch.cuda.synchronize()
     dist.barrier()
-    sec = torch.tensor([time.perf_counter() - t0], device="cuda")
-    dist.all_reduce(sec, op=dist.ReduceOp.MAX)
-    sec = float(sec.item())
+    sec = max_over_ranks(time.perf_counter() - t0)
+    sv.close()
+    del sv, a
+    torch.cuda.empty_cache()
+
+    # the whole training run to eps, from the pinned host shard
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    sv, a, X, y = make()
+    while not sv.done and time.perf_counter() - t0 < args.train_budget_s:
+        sv.iterate(50)
+    rho_t, st_t = sv.finish()
+    torch.cuda.synchronize()
+    dist.barrier()
+    sec_train = max_over_ranks(time.perf_counter() - t0)
+    n_sv_local = int((a != 0).sum().item())
+    train = {"seconds": sec_train, "converged": bool(sv.done), "outer_iters": st_t["outer_iters"],
+             "local_iters": st_t["local_iters"], "objective": st_t["objective"], "rho": rho_t,
+             "phase_seconds": {"rows": st_t["seconds_rows"], "block_and_local": st_t["seconds_local"]}}
+
+    # prediction: every rank holds all support vectors and predicts its share of the test rows
+    predict = None
+    if train["converged"] and args.predict_rows > 0:
+        m = args.predict_rows
+        idx = torch.nonzero(a != 0).squeeze(1)
+        pos, neg = idx[y[idx] > 0], idx[y[idx] < 0]
+        parts = [_gather_rows(X[pos]), _gather_rows(X[neg])]
+        coefs = [_gather_rows((a[pos] * y[pos].to(torch.float64)).reshape(-1, 1)),
+                 _gather_rows((a[neg] * y[neg].to(torch.float64)).reshape(-1, 1))]
+        sv.close()
+        del sv, X
+        torch.cuda.empty_cache()
+        Xsv = torch.cat(parts, 0)
+        coef = torch.cat(coefs, 0).reshape(-1).contiguous()
+        counts = [parts[0].shape[0], parts[1].shape[0]]
+        del parts
+        km_sv = capi.KernelMatrix(dense=Xsv, gamma=gamma)
+        rho_d = torch.tensor([rho_t], dtype=torch.float64, device="cuda")
+        tl, th = predict_rows(m, rank, world)
+        test = synth.config5(m, d=d, seed=8)
+        Th = torch.from_numpy(test["X"][tl:th]).pin_memory()
+        y_test = test["y"][tl:th]
+        del test
+        capi.vote(capi.predict_dec(km_sv, coef, counts, rho_d, 2, dense=Th[:1024].cuda()), 2)      # warm-up
+        Td = Th.cuda()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        lab = capi.vote(capi.predict_dec(km_sv, coef, counts, rho_d, 2, dense=Td), 2)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_p = max_over_ranks(e0.elapsed_time(e1))
+        del Td
+        dist.barrier()
+        t0 = time.perf_counter()
+        lab_h = capi.vote(capi.predict_dec(km_sv, coef, counts, rho_d, 2, dense=Th.cuda(non_blocking=True)), 2).cpu()
+        sec_p = max_over_ranks(time.perf_counter() - t0)
+        hits = torch.tensor([float(((lab_h == 0).numpy() == (y_test > 0)).sum())], dtype=torch.float64, device="cuda")
+        dist.all_reduce(hits)
+        predict = {"rows": m, "n_sv": int(coef.numel()), "rows_per_s": m / (ms_p * 1e-3), "e2e_rows_per_s": m / sec_p,
+                   "accuracy": float(hits.item()) / m,
+                   "note": "test rows split evenly over the ranks, support vectors on every rank; max over ranks"}
+        km_sv.close()
+    else:
+        sv.close()
     return {
         "metric": "kernel_rows_per_s", "value": rows_timed / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
         "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
@@ -438,9 +533,11 @@ def bench(args, rank, world, local_rank):
         "config": {"workload": "config5: binary C-SVC, RBF gamma=0.5 C=1 eps=1e-3, %dx%d dense fp32, ws=1024, 512 new "
                                "kernel rows per outer iteration, instance columns sharded over %d GPUs" % (n, d, world),
                    "l2": "inputs larger than L2", "parallelism": "column-sharded x%d" % world},
+        "roofline": roofline, "cpu_baseline": None,
         "e2e": {"value": st["kernel_rows"] / sec, "unit": "rows/s",
                 "h2d_bytes_per_step": (hi - lo) * d * 4 / (W + K), "d2h_bytes_per_step": (hi - lo) * 8 / (W + K),
                 "seconds": sec, "steps": W + K},
-        "gpu_launches": int(launches * K / (W + K)), "train_state": {"objective": st["objective"], "rho": rho,
-                                                                      "outer_iters": st["outer_iters"]},
+        "gpu_launches": int(launches), "clocks": clk,
+        "phase_ms_per_step": {"rows": t_rows * 1e3, "block_and_local": t_loc * 1e3},
+        "train_to_eps": train, "predict": predict,
     }
