@@ -30,7 +30,7 @@ sys.path.insert(0, ROOT)
 
 N_FULL, D_FULL, WS, Q = 400000, 2000, 1024, 512
 GAMMA, C_SVC, EPS = 0.5, 1.0, 1e-3
-TRAFFIC_37888 = 391.5e6   # dram read + write bytes of one 37,888-instance launch of the kernel (ncu capture summarised in profiles/)
+TRAFFIC_37888 = 388.7e6   # dram read + write bytes of one 37,888-instance launch of the kernel (ncu capture summarised in profiles/)
 
 
 def parse():
