@@ -192,6 +192,8 @@ def run_b200_arm(args):
         raise SystemExit("bench.py: no CUDA device - the B200 arm has no CPU fallback")
     torch.cuda.set_device(local_rank)
     if world > 1:
+        # stdout carries exactly one JSON line: NCCL's own messages (it prints its version there) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     if rank == 0:
         build.build()
