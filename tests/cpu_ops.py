@@ -112,3 +112,17 @@ class OracleOps:
         out = [fp.sum(), f[fp].sum(), fn.sum(), f[fn].sum(), (a - (f + y) * a * y / 2).sum(), mn(up & p), mx(low & p),
                mn(up & ng), mx(low & ng), mx(up & p), mn(low & p), mx(up & ng), mn(low & ng)]
         return torch.tensor(out, dtype=torch.float64)
+
+    def solve_pair(self, X_pair, y, C, eps, ws, kernel, gamma, coef0, degree):
+        X = P.Csr(dense=X_pair.numpy())
+        yy = y.numpy().astype(np.int32)
+        r = P.smo_solve(X, yy, np.zeros(len(yy)), -yy.astype(np.float64), eps, C, C, ws, kernel=kernel, gamma=gamma,
+                        coef0=coef0, degree=degree)
+        return torch.from_numpy(r["alpha"]), float(r["rho"])
+
+    def predict_labels(self, sv, coef, n_sv, rho, n_classes, T, kernel, gamma, coef0, degree):
+        dec = P.predict_dec(P.Csr(dense=sv.numpy()), np.ascontiguousarray(coef), np.asarray(n_sv, np.int32),
+                            np.asarray(rho, np.float64), n_classes, P.Csr(dense=T.numpy()), kernel=kernel, gamma=gamma,
+                            coef0=coef0, degree=degree)
+        return torch.from_numpy(P.vote(dec, n_classes).astype(np.int32))
+

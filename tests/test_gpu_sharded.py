@@ -115,3 +115,30 @@ def test_native_two_shards_are_bit_identical_to_one_gpu(capi, tmp_path):
     assert int(got["outer"]) == st1["outer_iters"] and int(got["local"]) == st1["local_iters"]
     assert np.array_equal(got["alpha"], a1.cpu().numpy())
     assert abs(float(got["rho"]) - rho1) < 1e-9
+
+
+def test_one_vs_one_on_the_gpu_matches_the_oracle_back_end(capi):
+    """train_ovo / predict_ovo with the C-ABI back end against the same driver with the oracle behind it: same
+    support-vector sets up to the 0.5 % bound, same labels."""
+    import os
+    import sys
+    import torch
+    from thundersvm_b200 import sharded
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from cpu_ops import OracleOps
+    rng = np.random.default_rng(3)
+    k, per, d = 5, 120, 64
+    centres = rng.standard_normal((k, d))
+    lab = np.repeat(np.arange(k), per)
+    X = (centres[lab] + 0.9 * rng.standard_normal((k * per, d))).astype(np.float32)
+    T = (centres[np.arange(200) % k] + 0.9 * rng.standard_normal((200, d))).astype(np.float32)
+    gamma = 1.0 / d
+    ref = sharded.train_ovo(OracleOps(), torch.from_numpy(X), lab, C=10.0, gamma=gamma)
+    ref_pred = sharded.predict_ovo(OracleOps(), ref, torch.from_numpy(X), torch.from_numpy(T), gamma=gamma).numpy()
+    Xd, Td = torch.from_numpy(X).cuda(), torch.from_numpy(T).cuda()
+    got = sharded.train_ovo(sharded.CapiOps(), Xd, lab, C=10.0, gamma=gamma)
+    pred = sharded.predict_ovo(sharded.CapiOps(), got, Xd, Td, gamma=gamma).cpu().numpy()
+    assert abs(sum(got["n_sv"]) - sum(ref["n_sv"])) <= max(1, 0.005 * sum(ref["n_sv"]))
+    assert np.max(np.abs(got["rho"] - ref["rho"])) < 1e-3
+    assert (pred == ref_pred).mean() >= 0.999
+    assert (pred == np.arange(200) % k).mean() > 0.9

@@ -115,3 +115,60 @@ def test_combine_rho_matches_oracle_formulas():
     free = (a > 0) & (a < 1.0)
     assert abs(rho - f[free].mean()) < 1e-12
     assert abs(obj - P.objective(f, a, y)) < 1e-9
+
+
+def _ovo_problem():
+    """Four classes on a circle in 8 dimensions, 70 instances each, class index in order of first appearance."""
+    rng = np.random.default_rng(11)
+    k, per, d = 4, 70, 8
+    centres = rng.standard_normal((k, d)) * 1.5
+    lab = rng.permutation(np.repeat(np.arange(k), per))
+    first = {}
+    for c in lab:
+        first.setdefault(int(c), len(first))
+    lab = np.array([first[int(c)] for c in lab])
+    X = (centres[lab] + rng.standard_normal((k * per, d))).astype(np.float32)
+    T = (centres[np.arange(40) % k] + rng.standard_normal((40, d))).astype(np.float32)
+    return X, lab, T
+
+
+def _ovo_rank(rank, world, port, out_dir):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from cpu_ops import OracleOps
+    if world > 1:
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    X, lab, T = _ovo_problem()
+    ops = OracleOps()
+    model = sharded.train_ovo(ops, torch.from_numpy(X), lab, C=10.0, gamma=0.2)
+    pred = sharded.predict_ovo(ops, model, torch.from_numpy(X), torch.from_numpy(T), gamma=0.2)
+    np.savez(os.path.join(out_dir, "ovo%d.npz" % rank), coef=model["coef"], rho=model["rho"], sv=model["sv_index"],
+             n_sv=np.asarray(model["n_sv"]), pred=pred.numpy(), owner=np.asarray(model["owner"]))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_one_vs_one_pairs_sharded_over_ranks(tmp_path, world):
+    """The six binary problems of a four-class set are split over the ranks; after the gather every rank
+    holds the same model, equal to the one a single process trains, and the row-sharded prediction returns
+    the same labels as the single process."""
+    single = tmp_path / "single"
+    single.mkdir()
+    _ovo_rank(0, 1, 0, str(single))
+    ref = np.load(single / "ovo0.npz")
+    multi = tmp_path / "multi"
+    multi.mkdir()
+    mp.spawn(_ovo_rank, args=(world, _free_port(), str(multi)), nprocs=world, join=True)
+    parts = [np.load(multi / ("ovo%d.npz" % r)) for r in range(world)]
+    assert sorted(set(parts[0]["owner"].tolist())) == list(range(world))        # every rank solved something
+    for p in parts:
+        assert np.array_equal(p["sv"], ref["sv"]) and np.array_equal(p["n_sv"], ref["n_sv"])
+        assert np.array_equal(p["coef"], ref["coef"]) and np.array_equal(p["rho"], ref["rho"])
+        assert np.array_equal(p["pred"], ref["pred"])
+    # and the model is a sensible classifier of its own training distribution
+    X, lab, T = _ovo_problem()
+    truth = np.arange(40) % 4
+    assert (ref["pred"] == truth).mean() > 0.8
+    assert ref["coef"].shape == (3, int(ref["n_sv"].sum()))

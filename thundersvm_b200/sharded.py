@@ -79,6 +79,24 @@ class CapiOps:
     def rho_partials(self, f, alpha, y, Cp, Cn):
         return self.capi.rho_partials(f, alpha, y, Cp, Cn)
 
+    def solve_pair(self, X_pair, y, C, eps, ws, kernel, gamma, coef0, degree):
+        """-> (alpha [n] >= 0, rho) of one binary C-SVC problem."""
+        km = self.capi.KernelMatrix(dense=X_pair, kernel=kernel, gamma=gamma, coef0=coef0, degree=degree)
+        alpha = torch.zeros(X_pair.shape[0], dtype=torch.float64, device=X_pair.device)
+        f = -y.to(torch.float64)
+        rho, _ = self.capi.smo_solve(km, y, alpha, f, eps, C, C, ws)
+        km.close()
+        return alpha, rho
+
+    def predict_labels(self, sv, coef, n_sv, rho, n_classes, T, kernel, gamma, coef0, degree):
+        km = self.capi.KernelMatrix(dense=sv, kernel=kernel, gamma=gamma, coef0=coef0, degree=degree)
+        dec = self.capi.predict_dec(km, torch.from_numpy(np.ascontiguousarray(coef)).to(T.device), n_sv,
+                                    torch.from_numpy(np.ascontiguousarray(rho)).to(T.device), n_classes,
+                                    dense=T.contiguous())
+        lab = self.capi.vote(dec, n_classes)
+        km.close()
+        return lab
+
 
 def combine_rho(parts, solver):
     """parts: [world, 13] partial reductions -> (rho, objective, r) as csmosolver.cpp:167-187 /
@@ -366,6 +384,80 @@ def assign_pairs(counts, world):
         owner[k] = r
         load[r] += counts[pairs[k][0]] + counts[pairs[k][1]]
     return pairs, owner
+
+
+def working_set_size(n, d, free_bytes=8 << 30):
+    """SvmModel::get_working_set_size (svmmodel.cpp:437-451)."""
+    p2 = lambda x: 2 ** int(math.floor(math.log2(x))) if x >= 1 else 0
+    return int(min(p2(n), min(p2(free_bytes / 4 / (n + d)), 1024)))
+
+
+def train_ovo(ops, X, labels, C, eps=1e-3, kernel="rbf", gamma=0.5, coef0=0.0, degree=3, group=None):
+    """One-vs-one C-SVC (SVC::train, svc.cpp:50-108) with the binary sub-problems split over the ranks.
+
+    Every rank holds X [n, d] and the class index of every instance (0 .. k-1, in order of first appearance
+    as DataSet::group_classes numbers them). Pairs are assigned by `assign_pairs`; a rank solves its pairs
+    with `ops.solve_pair`; one all-gather of the signed alphas and rho makes the model identical on every
+    rank. No collective runs while a pair is being solved.
+    Returns dict(n_classes, sv_index [n_sv] original ids in class order, n_sv [k], coef [(k-1), n_sv] in the
+    reference's layout (svmmodel.h:155-164), rho [k(k-1)/2])."""
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    lab = labels.cpu().numpy() if torch.is_tensor(labels) else np.asarray(labels)
+    k = int(lab.max()) + 1
+    members = [np.nonzero(lab == c)[0] for c in range(k)]
+    counts = [len(m) for m in members]
+    pairs, owner = assign_pairs(counts, world)
+    sizes = [counts[i] + counts[j] for i, j in pairs]
+    offs = np.concatenate([[0], np.cumsum(sizes)])
+    dev = X.device
+    flat = torch.zeros(int(offs[-1]), dtype=torch.float64, device=dev)       # signed alphas of all pairs
+    rho = torch.zeros(len(pairs), dtype=torch.float64, device=dev)
+    for p, (i, j) in enumerate(pairs):
+        if owner[p] != rank:
+            continue
+        idx = torch.from_numpy(np.concatenate([members[i], members[j]])).to(dev)
+        y = torch.cat([torch.ones(counts[i], dtype=torch.int32), -torch.ones(counts[j], dtype=torch.int32)]).to(dev)
+        ws = working_set_size(len(idx), X.shape[1])
+        a, r = ops.solve_pair(X[idx].contiguous(), y, C, eps, ws, kernel, gamma, coef0, degree)
+        flat[offs[p]:offs[p + 1]] = a * y.to(torch.float64)
+        rho[p] = r
+    if world > 1:                                   # every entry is written by exactly one rank: a sum gathers
+        dist.all_reduce(flat, group=group)
+        dist.all_reduce(rho, group=group)
+    flat_h = flat.cpu().numpy()
+    is_sv = np.zeros(len(lab), dtype=bool)
+    for p, (i, j) in enumerate(pairs):
+        ids = np.concatenate([members[i], members[j]])
+        is_sv[ids[flat_h[offs[p]:offs[p + 1]] != 0]] = True
+    sv_per_class = [m[is_sv[m]] for m in members]
+    n_sv = [len(v) for v in sv_per_class]
+    start = np.concatenate([[0], np.cumsum(n_sv)])
+    total = int(start[-1])
+    coef = np.zeros((max(k - 1, 1), total))
+    for p, (i, j) in enumerate(pairs):
+        a = flat_h[offs[p]:offs[p + 1]]
+        ai, aj = a[:counts[i]], a[counts[i]:]
+        coef[j - 1, start[i]:start[i + 1]] = ai[is_sv[members[i]]]
+        coef[i, start[j]:start[j + 1]] = aj[is_sv[members[j]]]
+    return dict(n_classes=k, sv_index=np.concatenate(sv_per_class) if total else np.zeros(0, np.int64), n_sv=n_sv,
+                coef=coef, rho=rho.cpu().numpy(), pairs=pairs, owner=owner)
+
+
+def predict_ovo(ops, model, X_train, T, kernel="rbf", gamma=0.5, coef0=0.0, degree=3, group=None):
+    """Class index of every row of T (SVC::predict, svc.cpp:265-289), test rows split over the ranks
+    (`predict_rows`) and the labels gathered on every rank."""
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    lo, hi = predict_rows(T.shape[0], rank, world)
+    out = torch.zeros(T.shape[0], dtype=torch.int32, device=T.device)
+    if hi > lo:
+        sv = X_train[torch.from_numpy(model["sv_index"]).to(X_train.device)].contiguous()
+        out[lo:hi] = ops.predict_labels(sv, model["coef"], model["n_sv"], model["rho"], model["n_classes"], T[lo:hi],
+                                        kernel, gamma, coef0, degree)
+    if world > 1:
+        dist.all_reduce(out, group=group)
+    return out
 
 
 def predict_rows(n_test, rank, world):
