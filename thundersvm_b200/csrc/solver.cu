@@ -869,7 +869,7 @@ static tsvm_status ws_candidates_cap(tsvm_ws *w, int solver_kind, int n, const d
                                      int cap, int id_offset, double *cand_f_dev, int *cand_id_dev, cudaStream_t st) {
     const int lists = solver_kind == TSVM_SOLVER_C ? 2 : 4;
     int grid = ceil_div(n, 256 * 4);
-    { static const char *ge = getenv("TSVM_SEL_GRID"); const int cap = ge ? atoi(ge) : 296; if (grid > cap) grid = cap; }
+    if (grid > 296) grid = 296;
     if (grid < 1) grid = 1;
     const size_t hist_smem = (size_t) lists * RADIX_BINS * sizeof(int);
     static bool configured = false;
