@@ -263,3 +263,36 @@ def test_one_class_style_init_f(capi):
     r = P.smo_solve(X, y, a0, np.zeros(n), 1e-3, 1.0, 1.0, 512, gamma=prob["gamma"])
     assert abs(stats["objective"] - r["obj"]) <= 1e-4 * abs(r["obj"])
     assert abs(rho - r["rho"]) < 1e-3
+
+
+def test_config5_generator_at_scale_against_the_reference_fixture(capi, golden_dir):
+    """The reference's CPU solver run to convergence on the first N instances of the 400,000 x 2,000
+    configuration's generator (tests/golden/make_c5_scale.py; the full size is not tractable on host cores):
+    objective 1e-4 relative, rho 1e-3, support-vector count 0.5 %, decision values of 64 test rows 1e-3."""
+    import torch
+    path = os.path.join(golden_dir, "c5_scale.npz")
+    if not os.path.exists(path):
+        pytest.skip("fixture not generated")
+    g = np.load(path)
+    n = int(g["n"])
+    prob = synth.config5(n)
+    y = np.where(prob["y"] > 0, 1, -1).astype(np.int32)
+    X = torch.from_numpy(prob["X"]).cuda()
+    km = capi.KernelMatrix(dense=X, gamma=prob["gamma"])
+    yt = torch.from_numpy(y).cuda()
+    alpha = torch.zeros(n, dtype=torch.float64, device="cuda")
+    f = -yt.to(torch.float64)
+    rho, st = capi.smo_solve(km, yt, alpha, f, 1e-3, 1.0, 1.0, 1024)
+    assert abs(st["objective"] - float(g["objective"])) <= 1e-4 * abs(float(g["objective"]))
+    assert abs(rho - float(g["rho"])) < 1e-3
+    n_sv = int((alpha != 0).sum().item())
+    assert abs(n_sv - int(g["n_sv"])) <= 0.005 * int(g["n_sv"])
+    sv = torch.nonzero(alpha != 0).squeeze(1)
+    order = torch.cat([sv[yt[sv] > 0], sv[yt[sv] < 0]])
+    km_sv = capi.KernelMatrix(dense=X[order].contiguous(), gamma=prob["gamma"])
+    coef = (alpha[order] * yt[order].to(torch.float64)).contiguous()
+    test = synth.config5(64, seed=8)
+    dec = capi.predict_dec(km_sv, coef, [int((yt[sv] > 0).sum()), int((yt[sv] < 0).sum())],
+                           torch.tensor([rho], dtype=torch.float64, device="cuda"), 2,
+                           dense=torch.from_numpy(test["X"]).cuda())
+    assert np.max(np.abs(dec.cpu().numpy()[:, 0] - g["dec"])) < 1e-3

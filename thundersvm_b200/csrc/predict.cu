@@ -79,7 +79,12 @@ tsvm_status tsvm_predict_dec(tsvm_km *km_sv, const double *coef_dev, const int *
     TSVM_REQUIRE(total == n_sv, "predict_dec: support-vector counts sum to %d but the matrix holds %d", total, n_sv);
     // batch rows so that the kernel-value buffer stays within the budget (svmmodel.cpp:86-89 caps at 10000)
     const long long ldk = ((long long) n_sv + 3) & ~3ll;
-    size_t budget = max_mem_bytes ? max_mem_bytes : ((size_t) 2 << 30);
+    size_t budget = max_mem_bytes;
+    if (!budget) {                 // no cap given: a quarter of what is free (the reference batches by its own cap)
+        size_t free_b = 0, total_b = 0;
+        budget = cudaMemGetInfo(&free_b, &total_b) == cudaSuccess ? free_b / 4 : ((size_t) 2 << 30);
+        if (budget < ((size_t) 256 << 20)) budget = (size_t) 256 << 20;
+    }
     long long batch = (long long) (budget / sizeof(float) / (size_t) ldk);
     if (batch > 10000) batch = 10000;
     if (batch > m) batch = m;
