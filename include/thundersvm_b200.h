@@ -191,6 +191,17 @@ tsvm_status tsvm_shard_create(tsvm_km *km_local, int solver_kind, const int *y_d
 tsvm_status tsvm_shard_candidates(tsvm_shard *shard, int *lists_host, int *want_host);
 tsvm_status tsvm_shard_select(tsvm_shard *shard, int *n_new_host);
 tsvm_status tsvm_shard_iterate(tsvm_shard *shard, int *done_host);
+/* The same iteration with the exchange steps run by the library itself: NCCL is looked up at run time in
+ * the process (libnccl.so.2; the library does not link it). Rank 0 asks for a 128-byte unique id
+ * (ncclGetUniqueId), the caller distributes it by any means, every rank creates a communicator
+ * (ncclCommInitRank, a collective call; the handle may serve any number of shard solvers of the same ranks,
+ * one at a time), attaches it, and tsvm_shard_step then runs candidates -> all-gather -> select ->
+ * all-reduce -> iterate on the solver's stream without host work in between. */
+int tsvm_nccl_unique_id(void *id128_host);
+tsvm_status tsvm_nccl_comm_create(const void *id128_host, int rank, int world, void **comm_out);
+void tsvm_nccl_comm_destroy(void *comm);
+tsvm_status tsvm_shard_attach_nccl(tsvm_shard *shard, void *comm);
+tsvm_status tsvm_shard_step(tsvm_shard *shard, int *done_host);
 tsvm_status tsvm_shard_get_stats(const tsvm_shard *shard, tsvm_solve_stats *stats_host);
 void tsvm_shard_destroy(tsvm_shard *shard);
 

@@ -24,7 +24,7 @@ EXPORTS = [
     "tsvm_km_n_instances", "tsvm_km_n_features", "tsvm_km_nnz", "tsvm_km_is_dense", "tsvm_km_diag_dev",
     "tsvm_km_self_dot_dev", "tsvm_km_rows_by_index", "tsvm_km_rows_by_instances_dense",
     "tsvm_km_rows_by_instances_csr", "tsvm_km_rows_for_features_dense", "tsvm_km_set_dense_engine", "tsvm_rho_partials", "tsvm_smo_solve", "tsvm_solver_create",
-    "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_set_overlap", "tsvm_solver_destroy", "tsvm_shard_create", "tsvm_shard_candidates", "tsvm_shard_select", "tsvm_shard_iterate", "tsvm_shard_get_stats", "tsvm_shard_destroy", "tsvm_working_set_size",
+    "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_set_overlap", "tsvm_solver_destroy", "tsvm_shard_create", "tsvm_shard_candidates", "tsvm_shard_select", "tsvm_shard_iterate", "tsvm_nccl_unique_id", "tsvm_nccl_comm_create", "tsvm_nccl_comm_destroy", "tsvm_shard_attach_nccl", "tsvm_shard_step", "tsvm_shard_get_stats", "tsvm_shard_destroy", "tsvm_working_set_size",
     "tsvm_ws_create", "tsvm_ws_destroy", "tsvm_ws_candidates", "tsvm_ws_merge", "tsvm_select_working_set",
     "tsvm_select_working_set_static",
     "tsvm_local_smo", "tsvm_update_f", "tsvm_predict_dec", "tsvm_vote",
@@ -92,6 +92,12 @@ def lib():
     L.tsvm_shard_select.argtypes = [vp, C.POINTER(i)]
     L.tsvm_shard_iterate.argtypes = [vp, C.POINTER(i)]
     L.tsvm_shard_get_stats.argtypes = [vp, C.POINTER(SolveStats)]
+    L.tsvm_nccl_unique_id.argtypes = [vp]
+    L.tsvm_shard_attach_nccl.argtypes = [vp, vp]
+    L.tsvm_nccl_comm_create.argtypes = [vp, i, i, C.POINTER(vp)]
+    L.tsvm_nccl_comm_destroy.argtypes = [vp]
+    L.tsvm_nccl_comm_destroy.restype = None
+    L.tsvm_shard_step.argtypes = [vp, C.POINTER(i)]
     L.tsvm_shard_destroy.argtypes = [vp]
     L.tsvm_shard_destroy.restype = None
     L.tsvm_solver_destroy.argtypes = [vp]
@@ -297,6 +303,30 @@ class Shard:
     def iterate(self):
         done = C.c_int(0)
         check(lib().tsvm_shard_iterate(self._h, C.byref(done)))
+        return bool(done.value)
+
+    @staticmethod
+    def nccl_unique_id():
+        """128 bytes from ncclGetUniqueId (call on one rank, give the bytes to all)."""
+        buf = (C.c_char * 128)()
+        check(lib().tsvm_nccl_unique_id(buf))
+        return bytes(buf)
+
+    @staticmethod
+    def nccl_comm_create(unique_id, rank, world):
+        """Collective: every rank calls it with the same id. -> communicator handle (not destroyed here)."""
+        comm = C.c_void_p(0)
+        check(lib().tsvm_nccl_comm_create(C.c_char_p(unique_id), rank, world, C.byref(comm)))
+        return comm
+
+    def attach_nccl(self, comm):
+        check(lib().tsvm_shard_attach_nccl(self._h, comm))
+        self._comm = comm
+
+    def step(self):
+        """One whole outer iteration, exchange steps included (after attach_nccl, or with one rank)."""
+        done = C.c_int(0)
+        check(lib().tsvm_shard_step(self._h, C.byref(done)))
         return bool(done.value)
 
     def stats(self):

@@ -6,6 +6,7 @@
 #include <chrono>
 #include <limits.h>
 #include <string.h>
+#include <dlfcn.h>
 #include <vector>
 
 namespace tsvm {
@@ -1346,6 +1347,54 @@ tsvm_status tsvm_smo_solve(tsvm_km *km, int solver_kind, const int *y_dev, doubl
 
 }  // extern "C"
 
+// ---- NCCL, bound at run time -------------------------------------------------------------------------
+// The library does not link NCCL (a single GPU needs none of it). tsvm_shard_attach_nccl looks the few
+// entry points up in the libnccl.so.2 the process already has (or can load) and keeps a communicator.
+namespace {
+typedef struct ncclComm *ncclComm_t;
+struct ncclUniqueIdBytes { char internal[128]; };
+enum { NCCL_INT32 = 2, NCCL_FLOAT32 = 7, NCCL_FLOAT64 = 8, NCCL_SUM = 0 };
+struct NcclApi {
+    int (*GetUniqueId)(ncclUniqueIdBytes *) = nullptr;
+    int (*CommInitRank)(ncclComm_t *, int, ncclUniqueIdBytes, int) = nullptr;
+    int (*CommDestroy)(ncclComm_t) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+    bool ok = false;
+};
+NcclApi &nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (tried) return api;
+    tried = true;
+    void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return api;
+    api.GetUniqueId = (decltype(api.GetUniqueId)) dlsym(h, "ncclGetUniqueId");
+    api.CommInitRank = (decltype(api.CommInitRank)) dlsym(h, "ncclCommInitRank");
+    api.CommDestroy = (decltype(api.CommDestroy)) dlsym(h, "ncclCommDestroy");
+    api.AllGather = (decltype(api.AllGather)) dlsym(h, "ncclAllGather");
+    api.AllReduce = (decltype(api.AllReduce)) dlsym(h, "ncclAllReduce");
+    api.GroupStart = (decltype(api.GroupStart)) dlsym(h, "ncclGroupStart");
+    api.GroupEnd = (decltype(api.GroupEnd)) dlsym(h, "ncclGroupEnd");
+    api.GetErrorString = (decltype(api.GetErrorString)) dlsym(h, "ncclGetErrorString");
+    api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.AllReduce &&
+             api.GroupStart && api.GroupEnd && api.GetErrorString;
+    return api;
+}
+}  // namespace
+#define TSVM_NCCL(expr)                                                                                  \
+    do {                                                                                                 \
+        const int r__ = (expr);                                                                          \
+        if (r__ != 0) {                                                                                  \
+            tsvm::set_error("%s failed: %s", #expr, nccl_api().GetErrorString(r__));                     \
+            return TSVM_ERR_CUDA;                                                                        \
+        }                                                                                                \
+    } while (0)
+
 // Per-rank state of the column-sharded solver. The caller owns the exchange buffers (they are the operands of
 // its collectives): cand_f/cand_id [lists * ws], all_f/all_id [world * lists * ws], crow [ws * (dp + 4)] floats,
 // cstate [ws * 3] doubles.
@@ -1357,6 +1406,7 @@ struct tsvm_shard {
     double eps = 0, Cp = 0, Cn = 0;
     long long ld = 0;
     cudaStream_t st = nullptr, st2 = nullptr;
+    ncclComm_t comm = nullptr;       // set by tsvm_shard_attach_nccl (not owned): the library then runs the exchange steps itself
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_r0 = nullptr, ev_r1 = nullptr, ev_b0 = nullptr, ev_b1 = nullptr;
     double t_rows = 0, t_loc = 0;    // ms: kernel-row launch (first stream); block + local solver (second stream)
     // exchange buffers (caller's)
@@ -1526,9 +1576,76 @@ struct tsvm_shard {
         phase = 0;
         return TSVM_OK;
     }
+
+    // One whole outer iteration with the exchange steps enqueued on the solver's stream by the library
+    // (needs a communicator): no host work between the phases.
+    tsvm_status step() {
+        TSVM_REQUIRE(comm || world == 1, "shard solver: tsvm_shard_step needs tsvm_shard_attach_nccl first");
+        int lists = 0, want = 0;
+        TSVM_TRY(candidates(&lists, &want));
+        const size_t m = (size_t) lists * want;
+        if (world > 1) {
+            NcclApi &nc = nccl_api();
+            TSVM_NCCL(nc.GroupStart());
+            TSVM_NCCL(nc.AllGather(cand_f, all_f, m, NCCL_FLOAT64, comm, st));
+            TSVM_NCCL(nc.AllGather(cand_id, all_id, m, NCCL_INT32, comm, st));
+            TSVM_NCCL(nc.GroupEnd());
+        } else {
+            TSVM_CUDA(cudaMemcpyAsync(all_f, cand_f, m * sizeof(double), cudaMemcpyDeviceToDevice, st));
+            TSVM_CUDA(cudaMemcpyAsync(all_id, cand_id, m * sizeof(int), cudaMemcpyDeviceToDevice, st));
+        }
+        TSVM_TRY(select());
+        if (world > 1) {
+            NcclApi &nc = nccl_api();
+            TSVM_NCCL(nc.GroupStart());
+            TSVM_NCCL(nc.AllReduce(crow, crow, (size_t) n_new * (dp + 4), NCCL_FLOAT32, NCCL_SUM, comm, st));
+            TSVM_NCCL(nc.AllReduce(cstate, cstate, (size_t) ws * 3, NCCL_FLOAT64, NCCL_SUM, comm, st));
+            TSVM_NCCL(nc.GroupEnd());
+        }
+        return iterate();
+    }
 };
 
 extern "C" {
+
+int tsvm_nccl_unique_id(void *id128) {
+    NcclApi &nc = nccl_api();
+    if (!nc.ok || !id128) { tsvm::set_error("NCCL is not available in this process (libnccl.so.2 not found)"); return TSVM_ERR_INVALID; }
+    ncclUniqueIdBytes id;
+    const int r = nc.GetUniqueId(&id);
+    if (r != 0) { tsvm::set_error("ncclGetUniqueId failed: %s", nc.GetErrorString(r)); return TSVM_ERR_CUDA; }
+    memcpy(id128, &id, sizeof(id));
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_nccl_comm_create(const void *id128, int rank, int world, void **comm_out) {
+    TSVM_REQUIRE(id128 && comm_out && world >= 1 && rank >= 0 && rank < world, "nccl_comm_create: bad arguments");
+    NcclApi &nc = nccl_api();
+    TSVM_REQUIRE(nc.ok, "NCCL is not available in this process (libnccl.so.2 not found)");
+    ncclUniqueIdBytes id;
+    memcpy(&id, id128, sizeof(id));
+    ncclComm_t c = nullptr;
+    TSVM_NCCL(nc.CommInitRank(&c, world, id, rank));
+    *comm_out = c;
+    return TSVM_OK;
+}
+
+void tsvm_nccl_comm_destroy(void *comm) {
+    if (comm && nccl_api().ok) nccl_api().CommDestroy((ncclComm_t) comm);
+}
+
+tsvm_status tsvm_shard_attach_nccl(tsvm_shard *S, void *comm) {
+    TSVM_REQUIRE(S && comm, "shard_attach_nccl: null argument");
+    S->comm = (ncclComm_t) comm;
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_shard_step(tsvm_shard *S, int *done_host) {
+    TSVM_REQUIRE(S && done_host, "shard_step: null argument");
+    TSVM_TRY(S->step());
+    *done_host = S->done ? 1 : 0;
+    return TSVM_OK;
+}
 
 tsvm_status tsvm_shard_create(tsvm_km *km_local, int solver_kind, const int *y_dev, double *alpha_dev, double *f_dev,
                               int n_total, int lo, double eps, double Cp, double Cn, int ws_size, int world,

@@ -299,6 +299,20 @@ class ShardedSolver:
         return self.finish()
 
 
+_LIBRARY_COMMS = {}
+
+
+def _library_comm(capi, group, rank, world):
+    """The library's own NCCL communicator over the ranks of `group`, created on first use (a collective
+    call: the unique id travels through torch.distributed) and kept for the life of the process."""
+    key = id(group) if group is not None else None
+    if key not in _LIBRARY_COMMS:
+        box = [capi.Shard.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        _LIBRARY_COMMS[key] = capi.Shard.nccl_comm_create(box[0], rank, world)
+    return _LIBRARY_COMMS[key]
+
+
 class NativeShardedSolver:
     """The same loop with the whole per-rank device work of an iteration inside the library
     (tsvm_shard_*): three C calls per outer iteration with one all-gather (candidate lists) and two
@@ -307,7 +321,7 @@ class NativeShardedSolver:
     on a second stream underneath the kernel-row launch. Dense data with more than 32 features."""
 
     def __init__(self, X_local, y_local, alpha_local, f_local, n_total, lo, eps, Cp, Cn, ws_size, solver="c",
-                 kernel="rbf", gamma=0.5, coef0=0.0, degree=3, group=None):
+                 kernel="rbf", gamma=0.5, coef0=0.0, degree=3, group=None, native_exchange=True):
         from . import capi
         self.capi, self.group = capi, group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -318,9 +332,19 @@ class NativeShardedSolver:
         self.shard = capi.Shard(self.km, y_local, alpha_local, f_local, n_total, lo, eps, Cp, Cn, ws_size, self.world,
                                 solver=solver)
         self.done, self.iter, self.t_comm = False, 0, 0.0
+        # with NCCL as the backend the library runs the exchange steps itself (its own communicator, built from
+        # a unique id that travels through torch.distributed once); otherwise they are torch collectives
+        self.native_exchange = False
+        if self.world > 1 and native_exchange and dist.get_backend(group) == "nccl":
+            self.shard.attach_nccl(_library_comm(capi, group, self.rank, self.world))
+            self.native_exchange = True
 
     def outer_iteration(self):
         sh = self.shard
+        if self.native_exchange or self.world == 1:
+            self.done = sh.step()
+            self.iter += 1
+            return
         lists, want = sh.candidates()
         m = lists * want
         if self.world > 1:
