@@ -172,3 +172,14 @@ def test_one_vs_one_pairs_sharded_over_ranks(tmp_path, world):
     truth = np.arange(40) % 4
     assert (ref["pred"] == truth).mean() > 0.8
     assert ref["coef"].shape == (3, int(ref["n_sv"].sum()))
+
+
+def test_working_set_size_helper_matches_the_library():
+    import ctypes
+    from thundersvm_b200 import build
+    lib = ctypes.CDLL(build.build())
+    f = lib.tsvm_working_set_size
+    f.restype = ctypes.c_int
+    f.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t]
+    for n, d in ((150, 5), (1000, 785), (12025, 785), (400000, 2001), (3, 2), (2049, 64)):
+        assert sharded.working_set_size(n, d) == f(n, d, 8 << 30, 0), (n, d)
