@@ -602,7 +602,7 @@ __global__ void shift_ws_kernel(int *ids, int q, unsigned char *in_ws) {
 __global__ void __launch_bounds__(128)
 update_f_kernel(double *__restrict__ f, int n, const double *__restrict__ alpha_diff, int ws, int q,
                 int first_half_phys, const float *__restrict__ rows, long long ld, int vec_ok, int t_begin,
-                int t_end) {
+                int t_end, int cols) {
     __shared__ double ad[1024];
     __shared__ int prow[1024];
     __shared__ int cnt;
@@ -627,6 +627,24 @@ update_f_kernel(double *__restrict__ f, int n, const double *__restrict__ alpha_
     }
     __syncthreads();
     const int m = cnt;
+    if (cols == 1) {
+        // short shards: one column per thread, so that enough loads are in flight to cover the HBM latency
+        // (same order of summation per column as the four-column form)
+        const long long c = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+        if (c >= n) return;
+        double s = 0;
+        int r = 0;
+        for (; r + 16 <= m; r += 16) {
+            float v[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) v[u] = __ldcs(rows + (size_t) prow[r + u] * ld + c);
+#pragma unroll
+            for (int u = 0; u < 16; ++u) s += ad[r + u] * v[u];
+        }
+        for (; r < m; ++r) s += ad[r] * __ldcs(rows + (size_t) prow[r] * ld + c);
+        f[c] -= s;
+        return;
+    }
     const long long j = ((long long) blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (j >= n) return;
     double s0 = 0, s1 = 0, s2 = 0, s3 = 0;
@@ -804,6 +822,9 @@ __global__ void shard_scatter_kernel(const int *__restrict__ ids, int ws, int lo
 // =================================================================================================
 // host side
 // =================================================================================================
+// f update: four columns per thread (16-byte loads) for long column ranges, one for short ones
+static inline int update_f_cols(long long n) { return n >= 300000 ? 4 : 1; }
+static inline int update_f_grid(long long n) { return ceil_div(n, 128 * update_f_cols(n)); }
 static inline int rows_vec_ok(const float *rows, long long ld) {
     return (((uintptr_t) rows & 15) == 0 && (ld & 3) == 0) ? 1 : 0;
 }
@@ -1001,8 +1022,8 @@ tsvm_status tsvm_update_f(double *f_dev, int n, const double *alpha_diff_dev, in
                           long long ld, void *stream) {
     TSVM_REQUIRE(f_dev && alpha_diff_dev && rows_dev && n > 0 && ws_size > 0 && ws_size <= 1024 && ld >= n,
                  "update_f: bad arguments (at most 1024 rows per call)");
-    TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, (cudaStream_t) stream, f_dev, n, alpha_diff_dev, ws_size,
-                0, 0, rows_dev, ld, rows_vec_ok(rows_dev, ld), 0, ws_size);
+    TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, (cudaStream_t) stream, f_dev, n, alpha_diff_dev, ws_size,
+                0, 0, rows_dev, ld, rows_vec_ok(rows_dev, ld), 0, ws_size, update_f_cols(n));
     return TSVM_OK;
 }
 
@@ -1115,8 +1136,8 @@ struct tsvm_solver {
             TSVM_CUDA(cudaMemcpyAsync(ids, bi.data(), sizeof(int) * m, cudaMemcpyHostToDevice, st));
             TSVM_CUDA(cudaMemcpyAsync(alpha_diff, bd.data(), sizeof(double) * m, cudaMemcpyHostToDevice, st));
             TSVM_TRY(tsvm_km_rows_by_index(km, ids, m, rows, ld, st));
-            TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, m, 0, 0, rows, ld,
-                        rows_vec_ok(rows, ld), 0, m);
+            TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, m, 0, 0, rows, ld,
+                        rows_vec_ok(rows, ld), 0, m, update_f_cols(n));
             TSVM_CUDA(cudaStreamSynchronize(st));
             rows_made += m;
             bi.clear(); bd.clear();
@@ -1172,8 +1193,8 @@ struct tsvm_solver {
                 TSVM_CUDA(cudaEventRecord(ev_l1, st2));
                 // the rows that stayed in the buffer can be applied to f at once (HBM-bound, next to the
                 // tensor-bound launch); the new rows follow on the first stream
-                TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st2, f, n, alpha_diff, ws, q, first_half_phys,
-                            rows, ld, rows_vec_ok(rows, ld), 0, q);
+                TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st2, f, n, alpha_diff, ws, q, first_half_phys,
+                            rows, ld, rows_vec_ok(rows, ld), 0, q, update_f_cols(n));
                 TSVM_CUDA(cudaEventRecord(ev_join, st2));
                 // first stream: the q full rows on all SM pairs but one
                 km->reserve_clusters = 1;
@@ -1198,14 +1219,14 @@ struct tsvm_solver {
         // f -= sum over the old half's rows, then f -= sum over the new half's rows: two launches in every
         // form of the iteration, so that all of them round alike (the first iteration has new rows only)
         if (iter == 0) {
-            TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows,
-                        ld, rows_vec_ok(rows, ld), 0, ws);
+            TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows,
+                        ld, rows_vec_ok(rows, ld), 0, ws, update_f_cols(n));
         } else {
             if (!overlapped)
-                TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys,
-                            rows, ld, rows_vec_ok(rows, ld), 0, q);
-            TSVM_LAUNCH(update_f_kernel, ceil_div(n, 512), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows,
-                        ld, rows_vec_ok(rows, ld), q, ws);
+                TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys,
+                            rows, ld, rows_vec_ok(rows, ld), 0, q, update_f_cols(n));
+            TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows,
+                        ld, rows_vec_ok(rows, ld), q, ws, update_f_cols(n));
         }
         TSVM_CUDA(cudaEventRecord(ev[4], st));
         TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
@@ -1536,8 +1557,8 @@ struct tsvm_shard {
                                   nullptr, nullptr, st2));
         TSVM_CUDA(cudaEventRecord(ev_b1, st2));
         if (iter > 0)      // the old half's rows are in the buffer already
-            TSVM_LAUNCH(update_f_kernel, ceil_div(n_local, 512), 128, 0, st2, f, n_local, alpha_diff, ws, q,
-                        first_half_phys, rows, ld, rows_vec_ok(rows, ld), 0, q);
+            TSVM_LAUNCH(update_f_kernel, update_f_grid(n_local), 128, 0, st2, f, n_local, alpha_diff, ws, q,
+                        first_half_phys, rows, ld, rows_vec_ok(rows, ld), 0, q, update_f_cols(n_local));
         TSVM_CUDA(cudaEventRecord(ev_join, st2));
         // first stream: the new rows against this rank's columns
         float *new_rows = rows + (size_t) (iter == 0 ? 0 : (1 - first_half_phys) * q) * ld;
@@ -1549,8 +1570,8 @@ struct tsvm_shard {
         TSVM_CUDA(cudaEventRecord(ev_r1, st));
         rows_made += n_new;
         TSVM_CUDA(cudaStreamWaitEvent(st, ev_join, 0));
-        TSVM_LAUNCH(update_f_kernel, ceil_div(n_local, 512), 128, 0, st, f, n_local, alpha_diff, ws, q, first_half_phys,
-                    rows, ld, rows_vec_ok(rows, ld), iter == 0 ? 0 : q, ws);
+        TSVM_LAUNCH(update_f_kernel, update_f_grid(n_local), 128, 0, st, f, n_local, alpha_diff, ws, q, first_half_phys,
+                    rows, ld, rows_vec_ok(rows, ld), iter == 0 ? 0 : q, ws, update_f_cols(n_local));
         TSVM_LAUNCH(shard_scatter_kernel, ceil_div(ws, 256), 256, 0, st, ids, ws, lo, hi, a_ws, alpha);
         TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaMemcpyAsync(km->status_host, km->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
