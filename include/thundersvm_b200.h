@@ -239,6 +239,13 @@ tsvm_status tsvm_ws_candidates(tsvm_ws *w, int solver_kind, int n, const double 
  * NuSMOSolver::select_working_set (nusmosolver.cpp:48-118) restricted to the candidates. */
 tsvm_status tsvm_ws_merge(tsvm_ws *w, int solver_kind, const double *cand_f_dev, const int *cand_id_dev, int len,
                           int want, int *out_ids_dev, void *stream);
+/* The same in two steps that scale with the number of ranks: every rank sorts its own lists in place
+ * (padding last), and the concatenation of the ranks' runs - len entries per list, in runs of seg_len -
+ * is merged by rank computation (binary searches) instead of one sort of all candidates. */
+tsvm_status tsvm_ws_sort_candidates(tsvm_ws *ws, int solver_kind, double *cand_f_dev, int *cand_id_dev, int len,
+                                    void *stream);
+tsvm_status tsvm_ws_merge_sorted(tsvm_ws *ws, int solver_kind, const double *cand_f_dev, const int *cand_id_dev,
+                                 int len, int seg_len, int want, int *out_ids_dev, void *stream);
 
 /* Full selection = candidates + merge on one device. */
 tsvm_status tsvm_select_working_set(tsvm_ws *w, int solver_kind, int n, const double *f_dev,

@@ -84,6 +84,30 @@ def test_candidates_then_merge_equals_select(capi):
     assert np.array_equal(got, exp)
 
 
+@pytest.mark.parametrize("solver", ["c", "nu_svc"])
+@pytest.mark.parametrize("shards", [1, 3, 8])
+def test_sorted_runs_merge_equals_select(capi, solver, shards):
+    """The form the sharded solver uses: every shard sorts its own candidate lists, the concatenated runs are
+    merged by rank computation. Ties in f (broken by id), shards of unequal size, a shard with fewer
+    candidates than wanted, and the nu lists."""
+    import torch
+    n, want = 9000, 512
+    y, f, alpha = _state(n, 11, ties=True)
+    sel = capi.WorkingSetSelector(n, 1024)
+    cuts = [0] + sorted(np.random.default_rng(shards).choice(np.arange(200, n - 200), shards - 1, replace=False).tolist()) + [n]
+    if shards == 8:
+        cuts[1] = 150                                # a shard that cannot fill its lists
+    parts_f, parts_i = [], []
+    for lo, hi in zip(cuts[:-1], cuts[1:]):
+        cf, ci = sel.candidates(_t(f[lo:hi]), _t(alpha[lo:hi]), _t(y[lo:hi]), 1.0, 1.0, want, solver=solver, id_offset=lo)
+        sel.sort_candidates(cf, ci, solver=solver)
+        parts_f.append(cf)
+        parts_i.append(ci)
+    got = sel.merge_sorted(torch.cat(parts_f, 1), torch.cat(parts_i, 1), want, want, solver=solver).cpu().numpy()
+    exp = P.select_working_set("c" if solver == "c" else "nu", f, y, alpha, 1.0, 1.0, None, want)
+    assert np.array_equal(got, exp)
+
+
 @pytest.mark.parametrize("solver,ws", [("c", 1024), ("c", 128), ("c", 64), ("nu_svc", 512), ("nu_svc", 32)])
 def test_local_smo_matches_oracle(capi, solver, ws):
     import torch

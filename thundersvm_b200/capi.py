@@ -25,7 +25,7 @@ EXPORTS = [
     "tsvm_km_self_dot_dev", "tsvm_km_rows_by_index", "tsvm_km_rows_by_instances_dense",
     "tsvm_km_rows_by_instances_csr", "tsvm_km_rows_for_features_dense", "tsvm_km_set_dense_engine", "tsvm_rho_partials", "tsvm_smo_solve", "tsvm_solver_create",
     "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_set_overlap", "tsvm_solver_destroy", "tsvm_shard_create", "tsvm_shard_candidates", "tsvm_shard_select", "tsvm_shard_iterate", "tsvm_nccl_unique_id", "tsvm_nccl_comm_create", "tsvm_nccl_comm_destroy", "tsvm_shard_attach_nccl", "tsvm_shard_step", "tsvm_shard_get_stats", "tsvm_shard_destroy", "tsvm_working_set_size",
-    "tsvm_ws_create", "tsvm_ws_destroy", "tsvm_ws_candidates", "tsvm_ws_merge", "tsvm_select_working_set",
+    "tsvm_ws_create", "tsvm_ws_destroy", "tsvm_ws_candidates", "tsvm_ws_merge", "tsvm_ws_sort_candidates", "tsvm_ws_merge_sorted", "tsvm_select_working_set",
     "tsvm_select_working_set_static",
     "tsvm_local_smo", "tsvm_update_f", "tsvm_predict_dec", "tsvm_vote",
 ]
@@ -410,6 +410,19 @@ class WorkingSetSelector:
         out = torch.empty(want, dtype=torch.int32, device="cuda")
         check(lib().tsvm_ws_merge(self._h, SOLVERS[solver], _ptr(cand_f.contiguous()), _ptr(cand_id.contiguous()),
                                   length, want, _ptr(out), _stream()))
+        return out
+
+    def sort_candidates(self, cand_f, cand_id, solver="c"):
+        """In place: every list sorted by its list key, padding last."""
+        lists, length = cand_f.shape
+        check(lib().tsvm_ws_sort_candidates(self._h, SOLVERS[solver], _ptr(cand_f), _ptr(cand_id), length, _stream()))
+
+    def merge_sorted(self, cand_f, cand_id, seg_len, want, solver="c"):
+        """cand_* [lists, n_runs * seg_len]: concatenated sorted runs."""
+        lists, length = cand_f.shape
+        out = torch.empty(want, dtype=torch.int32, device="cuda")
+        check(lib().tsvm_ws_merge_sorted(self._h, SOLVERS[solver], _ptr(cand_f.contiguous()), _ptr(cand_id.contiguous()),
+                                         length, seg_len, want, _ptr(out), _stream()))
         return out
 
     def close(self):

@@ -206,7 +206,7 @@ __device__ __forceinline__ bool key_less(unsigned long long ah, unsigned al, uns
 
 __global__ void __launch_bounds__(MERGE_THREADS)
 select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const int *__restrict__ cand_id, int len,
-                    int want, int *__restrict__ out_ids, int *__restrict__ out_count) {
+                    int want, int *__restrict__ out_ids, int *__restrict__ out_count, int seg_len) {
     extern __shared__ unsigned char smem[];
     const int lists = list_count(solver_kind);
     int P = 1;
@@ -221,6 +221,7 @@ select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const in
     short *hash_pos = reinterpret_cast<short *>(hash_id + HASH_SLOTS);
     __shared__ int top_len[MAX_LISTS];
     __shared__ unsigned long long last_fkey[MAX_LISTS];
+    __shared__ int real_total;
     const int tid = threadIdx.x;
 
     for (int l = 0; l < lists; ++l) {
@@ -240,6 +241,54 @@ select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const in
             kh[e] = h; kl[e] = lo;
         }
         __syncthreads();
+        if (seg_len > 0) {
+            // The list is a sequence of sorted runs (one per rank, padding last): an entry's place in the merged
+            // order is its place in its own run plus, for every other run, the number of smaller keys there
+            // (binary search; keys are distinct because ids are). No sort, a few microseconds for 8 x 512.
+            const int nseg = len / seg_len;
+            for (int e = tid; e < want; e += MERGE_THREADS) {
+                top_id[l * MERGE_MAX_WANT + e] = -1;
+                partner[l * MERGE_MAX_WANT + e] = -1;
+                taken[l * MERGE_MAX_WANT + e] = 0;
+            }
+            if (tid == 0) real_total = 0;
+            __syncthreads();
+            if (tid < nseg) {                       // real entries of run tid: first padding key
+                int lo_i = 0, hi_i = seg_len;
+                while (lo_i < hi_i) {
+                    const int mid = (lo_i + hi_i) >> 1;
+                    const int e = tid * seg_len + mid;
+                    if (kh[e] == ~0ull && kl[e] == ~0u) hi_i = mid; else lo_i = mid + 1;
+                }
+                atomicAdd(&real_total, lo_i);
+            }
+            __syncthreads();
+            const int keep = real_total < want ? real_total : want;
+            for (int e = tid; e < len; e += MERGE_THREADS) {
+                const unsigned long long h = kh[e];
+                const unsigned lo = kl[e];
+                if (h == ~0ull && lo == ~0u) continue;
+                const int r = e / seg_len;
+                int rank = e - r * seg_len;
+                for (int r2 = 0; r2 < nseg && rank < want; ++r2) {
+                    if (r2 == r) continue;
+                    int lo_i = 0, hi_i = seg_len;            // number of keys in run r2 below (h, lo)
+                    while (lo_i < hi_i) {
+                        const int mid = (lo_i + hi_i) >> 1;
+                        const int x = r2 * seg_len + mid;
+                        if (key_less(kh[x], kl[x], h, lo)) lo_i = mid + 1; else hi_i = mid;
+                    }
+                    rank += lo_i;
+                }
+                if (rank < want) {
+                    top_id[l * MERGE_MAX_WANT + rank] = (int) (asc ? lo : ~lo);
+                    if (rank == keep - 1) last_fkey[l] = asc ? h : ~h;
+                }
+            }
+            if (tid == 0) { top_len[l] = keep; if (keep == 0) last_fkey[l] = 0ull; }
+            __syncthreads();
+            continue;
+        }
         for (int k = 2; k <= P; k <<= 1)
             for (int j = k >> 1; j > 0; j >>= 1) {
                 for (int e = tid; e < P; e += MERGE_THREADS) {
@@ -359,6 +408,56 @@ select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const in
         }
         if (out_count) *out_count = got;
         for (int r = got; r < want; ++r) out_ids[r] = -1;
+    }
+}
+
+// Sorts every candidate list in place by its list key (padding, id -1, last): one block per list, bitonic in
+// shared memory. The runs of several ranks can then be merged by rank computation instead of a sort.
+__global__ void __launch_bounds__(MERGE_THREADS)
+select_sort_candidates_kernel(int solver_kind, double *__restrict__ cand_f, int *__restrict__ cand_id, int len) {
+    extern __shared__ unsigned char smem[];
+    const int l = blockIdx.x, tid = threadIdx.x;
+    int P = 1;
+    while (P < len) P <<= 1;
+    unsigned long long *kh = reinterpret_cast<unsigned long long *>(smem);
+    unsigned int *kl = reinterpret_cast<unsigned int *>(kh + P);
+    double *fv = reinterpret_cast<double *>(kl + P + (P & 1));          // the f values travel with their keys
+    const bool asc = list_ascending(solver_kind, l);
+    for (int e = tid; e < P; e += MERGE_THREADS) {
+        unsigned long long h = ~0ull;
+        unsigned lo = ~0u;
+        double v = 0.0;
+        if (e < len) {
+            const int id = cand_id[(size_t) l * len + e];
+            if (id >= 0) {
+                v = cand_f[(size_t) l * len + e];
+                h = ordered_key(v);
+                lo = (unsigned) id;
+                if (!asc) { h = ~h; lo = ~lo; }
+            }
+        }
+        kh[e] = h; kl[e] = lo; fv[e] = v;
+    }
+    __syncthreads();
+    for (int k = 2; k <= P; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int e = tid; e < P; e += MERGE_THREADS) {
+                const int x = e ^ j;
+                if (x > e) {
+                    const bool up = (e & k) == 0;
+                    if (key_less(kh[x], kl[x], kh[e], kl[e]) == up) {
+                        unsigned long long th = kh[e]; kh[e] = kh[x]; kh[x] = th;
+                        unsigned tl = kl[e]; kl[e] = kl[x]; kl[x] = tl;
+                        double tv = fv[e]; fv[e] = fv[x]; fv[x] = tv;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    for (int e = tid; e < len; e += MERGE_THREADS) {
+        const bool pad = kh[e] == ~0ull && kl[e] == ~0u;
+        cand_f[(size_t) l * len + e] = pad ? 0.0 : fv[e];
+        cand_id[(size_t) l * len + e] = pad ? -1 : (int) (asc ? kl[e] : ~kl[e]);
     }
 }
 
@@ -919,11 +1018,8 @@ tsvm_status tsvm_ws_candidates(tsvm_ws *w, int solver_kind, int n, const double 
                              cand_f_dev, cand_id_dev, (cudaStream_t) stream);
 }
 
-tsvm_status tsvm_ws_merge(tsvm_ws *w, int solver_kind, const double *cand_f_dev, const int *cand_id_dev, int len,
-                          int want, int *out_ids_dev, void *stream) {
-    TSVM_REQUIRE(w && cand_f_dev && cand_id_dev && out_ids_dev && len > 0 && len <= MERGE_MAX_LEN && want > 0 &&
-                 want <= MERGE_MAX_WANT, "ws_merge: bad arguments (len=%d want=%d)", len, want);
-    cudaStream_t st = (cudaStream_t) stream;
+static tsvm_status ws_merge_impl(tsvm_ws *w, int solver_kind, const double *cand_f_dev, const int *cand_id_dev, int len,
+                                 int seg_len, int want, int *out_ids_dev, cudaStream_t st) {
     const size_t smem = merge_smem_bytes(len);
     static size_t configured = 0;
     if (smem > configured) {
@@ -932,8 +1028,41 @@ tsvm_status tsvm_ws_merge(tsvm_ws *w, int solver_kind, const double *cand_f_dev,
         configured = merge_smem_bytes(MERGE_MAX_LEN);
     }
     TSVM_LAUNCH(select_merge_kernel, 1, MERGE_THREADS, smem, st, solver_kind, cand_f_dev, cand_id_dev, len, want,
-                out_ids_dev, w->count);
+                out_ids_dev, w->count, seg_len);
     return TSVM_OK;
+}
+
+tsvm_status tsvm_ws_merge(tsvm_ws *w, int solver_kind, const double *cand_f_dev, const int *cand_id_dev, int len,
+                          int want, int *out_ids_dev, void *stream) {
+    TSVM_REQUIRE(w && cand_f_dev && cand_id_dev && out_ids_dev && len > 0 && len <= MERGE_MAX_LEN && want > 0 &&
+                 want <= MERGE_MAX_WANT, "ws_merge: bad arguments (len=%d want=%d)", len, want);
+    return ws_merge_impl(w, solver_kind, cand_f_dev, cand_id_dev, len, 0, want, out_ids_dev, (cudaStream_t) stream);
+}
+
+tsvm_status tsvm_ws_sort_candidates(tsvm_ws *w, int solver_kind, double *cand_f_dev, int *cand_id_dev, int len,
+                                    void *stream) {
+    TSVM_REQUIRE(w && cand_f_dev && cand_id_dev && len > 0 && len <= MERGE_MAX_LEN && solver_kind >= 0 &&
+                 solver_kind <= 2, "ws_sort_candidates: bad arguments (len=%d)", len);
+    int P = 1;
+    while (P < len) P <<= 1;
+    const size_t smem = (size_t) P * 12 + 8 + (size_t) P * 8;
+    static bool configured = false;
+    if (!configured) {
+        TSVM_CUDA(cudaFuncSetAttribute(select_sort_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int) ((size_t) MERGE_MAX_LEN * 20 + 8)));
+        configured = true;
+    }
+    TSVM_LAUNCH(select_sort_candidates_kernel, solver_kind == TSVM_SOLVER_C ? 2 : 4, MERGE_THREADS, smem,
+                (cudaStream_t) stream, solver_kind, cand_f_dev, cand_id_dev, len);
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_ws_merge_sorted(tsvm_ws *w, int solver_kind, const double *cand_f_dev, const int *cand_id_dev, int len,
+                                 int seg_len, int want, int *out_ids_dev, void *stream) {
+    TSVM_REQUIRE(w && cand_f_dev && cand_id_dev && out_ids_dev && len > 0 && len <= MERGE_MAX_LEN && want > 0 &&
+                 want <= MERGE_MAX_WANT && seg_len > 0 && len % seg_len == 0 && len / seg_len <= MERGE_THREADS,
+                 "ws_merge_sorted: bad arguments (len=%d seg_len=%d want=%d)", len, seg_len, want);
+    return ws_merge_impl(w, solver_kind, cand_f_dev, cand_id_dev, len, seg_len, want, out_ids_dev, (cudaStream_t) stream);
 }
 
 tsvm_status tsvm_select_working_set(tsvm_ws *w, int solver_kind, int n, const double *f_dev, const double *alpha_dev,
@@ -1509,6 +1638,8 @@ struct tsvm_shard {
         }
         TSVM_TRY(tsvm_ws_candidates(sel, kind, n_local, f, alpha, y, iter == 0 ? nullptr : in_ws, Cp, Cn, n_new, lo,
                                     cand_f, cand_id, st));
+        // every rank hands over sorted lists: the merge of the gathered runs then needs no sort
+        TSVM_TRY(tsvm_ws_sort_candidates(sel, kind, cand_f, cand_id, n_new, st));
         *lists_out = lists;
         *want_out = n_new;
         phase = 1;
@@ -1526,7 +1657,7 @@ struct tsvm_shard {
                         lists, n_new, grp_f, grp_id);
             mf = grp_f; mi = grp_id;
         }
-        TSVM_TRY(tsvm_ws_merge(sel, kind, mf, mi, world * n_new, n_new, ids + slot0, st));
+        TSVM_TRY(tsvm_ws_merge_sorted(sel, kind, mf, mi, world * n_new, n_new, n_new, ids + slot0, st));
         TSVM_LAUNCH(shard_contrib_kernel, n_new + 4, 256, 0, st, ids, slot0, n_new, ws, lo, hi, km->X, km->ldx, d, dp,
                     km->self_dot, km->diag, y, f, alpha, crow, cstate);
         phase = 2;
