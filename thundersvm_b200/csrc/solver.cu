@@ -414,7 +414,8 @@ select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const in
 // Sorts every candidate list in place by its list key (padding, id -1, last): one block per list, bitonic in
 // shared memory. The runs of several ranks can then be merged by rank computation instead of a sort.
 __global__ void __launch_bounds__(MERGE_THREADS)
-select_sort_candidates_kernel(int solver_kind, double *__restrict__ cand_f, int *__restrict__ cand_id, int len) {
+select_sort_candidates_kernel(int solver_kind, const double *cand_f, const int *cand_id, int len, double *out_f,
+                              int *out_id, int out_len) {
     extern __shared__ unsigned char smem[];
     const int l = blockIdx.x, tid = threadIdx.x;
     int P = 1;
@@ -454,10 +455,11 @@ select_sort_candidates_kernel(int solver_kind, double *__restrict__ cand_f, int 
             }
             __syncthreads();
         }
-    for (int e = tid; e < len; e += MERGE_THREADS) {
+    // the first out_len entries of the sorted list (out_len <= len; the output may be the input)
+    for (int e = tid; e < out_len; e += MERGE_THREADS) {
         const bool pad = kh[e] == ~0ull && kl[e] == ~0u;
-        cand_f[(size_t) l * len + e] = pad ? 0.0 : fv[e];
-        cand_id[(size_t) l * len + e] = pad ? -1 : (int) (asc ? kl[e] : ~kl[e]);
+        out_f[(size_t) l * out_len + e] = pad ? 0.0 : fv[e];
+        out_id[(size_t) l * out_len + e] = pad ? -1 : (int) (asc ? kl[e] : ~kl[e]);
     }
 }
 
@@ -1039,10 +1041,8 @@ tsvm_status tsvm_ws_merge(tsvm_ws *w, int solver_kind, const double *cand_f_dev,
     return ws_merge_impl(w, solver_kind, cand_f_dev, cand_id_dev, len, 0, want, out_ids_dev, (cudaStream_t) stream);
 }
 
-tsvm_status tsvm_ws_sort_candidates(tsvm_ws *w, int solver_kind, double *cand_f_dev, int *cand_id_dev, int len,
-                                    void *stream) {
-    TSVM_REQUIRE(w && cand_f_dev && cand_id_dev && len > 0 && len <= MERGE_MAX_LEN && solver_kind >= 0 &&
-                 solver_kind <= 2, "ws_sort_candidates: bad arguments (len=%d)", len);
+static tsvm_status ws_sort_impl(int solver_kind, const double *in_f, const int *in_id, int len, double *out_f, int *out_id,
+                                int out_len, cudaStream_t st) {
     int P = 1;
     while (P < len) P <<= 1;
     const size_t smem = (size_t) P * 12 + 8 + (size_t) P * 8;
@@ -1052,9 +1052,16 @@ tsvm_status tsvm_ws_sort_candidates(tsvm_ws *w, int solver_kind, double *cand_f_
                                        (int) ((size_t) MERGE_MAX_LEN * 20 + 8)));
         configured = true;
     }
-    TSVM_LAUNCH(select_sort_candidates_kernel, solver_kind == TSVM_SOLVER_C ? 2 : 4, MERGE_THREADS, smem,
-                (cudaStream_t) stream, solver_kind, cand_f_dev, cand_id_dev, len);
+    TSVM_LAUNCH(select_sort_candidates_kernel, solver_kind == TSVM_SOLVER_C ? 2 : 4, MERGE_THREADS, smem, st,
+                solver_kind, in_f, in_id, len, out_f, out_id, out_len);
     return TSVM_OK;
+}
+
+tsvm_status tsvm_ws_sort_candidates(tsvm_ws *w, int solver_kind, double *cand_f_dev, int *cand_id_dev, int len,
+                                    void *stream) {
+    TSVM_REQUIRE(w && cand_f_dev && cand_id_dev && len > 0 && len <= MERGE_MAX_LEN && solver_kind >= 0 &&
+                 solver_kind <= 2, "ws_sort_candidates: bad arguments (len=%d)", len);
+    return ws_sort_impl(solver_kind, cand_f_dev, cand_id_dev, len, cand_f_dev, cand_id_dev, len, (cudaStream_t) stream);
 }
 
 tsvm_status tsvm_ws_merge_sorted(tsvm_ws *w, int solver_kind, const double *cand_f_dev, const int *cand_id_dev, int len,
@@ -1636,10 +1643,13 @@ struct tsvm_shard {
             TSVM_CUDA(cudaMemcpyAsync(m_lo, (char *) m_lo + (size_t) q * row_bytes, (size_t) q * row_bytes,
                                       cudaMemcpyDeviceToDevice, st));
         }
-        TSVM_TRY(tsvm_ws_candidates(sel, kind, n_local, f, alpha, y, iter == 0 ? nullptr : in_ws, Cp, Cn, n_new, lo,
-                                    cand_f, cand_id, st));
-        // every rank hands over sorted lists: the merge of the gathered runs then needs no sort
-        TSVM_TRY(tsvm_ws_sort_candidates(sel, kind, cand_f, cand_id, n_new, st));
+        // Candidates into the selector's own lists with twice the wanted capacity where it fits (the radix
+        // select then stops after two sweeps, see select_hist_kernel), sorted, and the best n_new of every
+        // list handed over: the merge of the gathered sorted runs needs no sort.
+        const int cap = 2 * n_new <= sel->cand_cap ? 2 * n_new : n_new;
+        TSVM_TRY(ws_candidates_cap(sel, kind, n_local, f, alpha, y, iter == 0 ? nullptr : in_ws, Cp, Cn, n_new, cap, lo,
+                                   sel->cand_f, sel->cand_id, st));
+        TSVM_TRY(ws_sort_impl(kind, sel->cand_f, sel->cand_id, cap, cand_f, cand_id, n_new, st));
         *lists_out = lists;
         *want_out = n_new;
         phase = 1;
