@@ -16,7 +16,7 @@ public:
     /// rows [r0, r0 + n0) followed by rows [r1, r1 + n1) of a dense row-major matrix that is already on the
     /// device (d features, row stride ld floats): the binary sub-problem of two classes of a grouped data set
     /// without a host round trip. No counterpart in the reference, which rebuilds every sub-problem from the
-    /// host instances (svc.cpp:291-316).
+    /// host instances (svc.cpp:147-178).
     KernelMatrix(const float *X_dev, size_t d, size_t ld, size_t r0, size_t n0, size_t r1, size_t n1, SvmParam param);
     ~KernelMatrix();
     KernelMatrix(const KernelMatrix &) = delete;
