@@ -254,18 +254,20 @@ tsvm_status tsvm_select_working_set(tsvm_ws *w, int solver_kind, int n, const do
 
 /* Allocation-free working-set selection. Same result as tsvm_select_working_set, but needs no tsvm_ws
  * and calls neither cudaMalloc / cudaFree nor any other allocating routine: its scratch (selection
- * state, radix histograms, candidate lists; about 114 KB) is a fixed array inside the library image,
+ * state, radix histograms, candidate lists; 115,200 bytes) is a fixed array inside the library image,
  * resident on every GPU that loads the library. It has no counterpart in the reference. It is meant
  * for callers that must not allocate at the point where they pick a working set: a solver loop that
  * has handed all device memory to its own pool (a later cudaMalloc would fail or fragment it), or a
  * latency-sensitive loop sharing the GPU with other streams, which a cudaMalloc would stall because
  * allocation synchronises the whole device.
- * Limits and rules: want <= 1024 (TSVM_ERR_INVALID with a message otherwise; n is unlimited). The
- * first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
- * device current) - make that first call outside any stream capture. All calls on a device share
- * the one array: it still holds the previous call's contents when a call starts (the entry point
- * clears what must start at zero itself), and two calls that overlap on the GPU - from different
- * streams or threads - race on it; serialise them. */
+ * Limits and rules: want <= TSVM_STATIC_WS_MAX (TSVM_ERR_INVALID with a message otherwise; n is
+ * unlimited). The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current) and sets the shared-memory limits of the selection
+ * kernels (cudaFuncSetAttribute) - make that first call outside any stream capture. All calls on a
+ * device share the one array: it still holds the previous call's contents when a call starts (the
+ * entry point clears what must start at zero itself), and two calls that overlap on the GPU - from
+ * different streams or threads - race on it; serialise them. */
+#define TSVM_STATIC_WS_MAX 1024
 tsvm_status tsvm_select_working_set_static(int solver_kind, int n, const double *f_dev, const double *alpha_dev,
                                            const int *y_dev, const unsigned char *in_ws_dev, double Cp,
                                            double Cn, int want, int *out_ids_dev, void *stream);

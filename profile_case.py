@@ -1,8 +1,8 @@
 """Small, bounded invocations of single hot-path kernels, for profilers.
 
-    python -m thundersvm_b200.profile_case dense_rows --rows 20000 --reps 3
-    python -m thundersvm_b200.profile_case csr_rows   --rows 20242 --reps 3
-    python -m thundersvm_b200.profile_case solver     --rows 20000 --steps 5
+    python profile_case.py dense_rows --rows 20000 --reps 3
+    python profile_case.py csr_rows   --rows 20242 --reps 3
+    python profile_case.py solver     --rows 20000 --steps 5
 
 Each case builds seeded synthetic data of the benchmark's shape at a reduced row count (larger than
 L2, a few hundred MB on the device), runs the kernel `reps` times and prints CUDA-event timings.
@@ -12,7 +12,11 @@ import argparse
 import numpy as np
 import torch
 
-from . import capi, synth
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from thundersvm_b200 import capi, synth  # noqa: E402
 
 
 def _time(fn, reps):

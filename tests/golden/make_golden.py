@@ -127,7 +127,9 @@ def fixture_solver():
 
 
 if __name__ == "__main__":
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    import subprocess
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else subprocess.check_output(
+        ["make", "-s", "-C", os.path.join(ROOT, "oracle"), "print-ref"], text=True).strip()
     fixture_dataset(ref_root)
     fixture_solver()
     print("wrote", [f for f in os.listdir(OUT) if f.endswith(".npz")])

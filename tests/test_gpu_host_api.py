@@ -84,7 +84,15 @@ def test_probability_and_infeasible_nu(fx):
     m, nf, nc, ok = host_api.train(L, 0, X=X, y=g["y"], gamma=0.5, C_=100, probability=1)
     pred = host_api.predict_dense(L, m, X)
     assert (pred == g["y"]).mean() > 0.95
-    assert "probA " in host_api.model_text(L, m)
+    text = host_api.model_text(L, m)
+    assert "probA " in text
+    # Platt coefficients of SVC::probability_train (svc.cpp:427-492: five folds, sigmoidTrain per class pair)
+    # against the reference build's own values for this data set
+    ref = np.load(os.path.join(ROOT, "tests", "golden", "prob.npz"))
+    for key in ("probA", "probB"):
+        got = np.array([float(v) for v in [ln for ln in text.splitlines() if ln.startswith(key + " ")][0].split()[1:]])
+        assert got.shape == ref[key].shape
+        assert np.all(np.abs(got - ref[key]) <= 0.02 * np.abs(ref[key]) + 5e-3), (key, got, ref[key])
     L.model_free(m)
     m, nf, nc, ok = host_api.train(L, 1, X=X, y=g["y"], gamma=0.5, nu=0.99)
     assert ok == -1                                  # thundersvm-scikit.cpp:93-96

@@ -250,3 +250,30 @@ def test_working_set_selection_edge_cases():
     a[:] = np.where(y > 0, 1.0, 0.0)      # every positive at its bound -> all instances are I_low only
     ws = P.select_working_set("c", f, y, a, 1.0, 1.0, None, 6)
     assert list(ws) == [63, 62, 61, 60, 59, 58]
+
+
+FULL = {"c1": synth.config1, "c2": synth.config2, "c4": synth.config4}
+
+
+@pytest.mark.parametrize("tag", sorted(FULL))
+def test_port_kernel_rows_match_reference_at_full_size(golden_dir, tag):
+    """Full-length kernel rows of the benchmark configurations: the restatement reproduces the reference
+    build's rows (tests/golden/make_full_configs.py) bit for bit."""
+    g = np.load(os.path.join(golden_dir, "full_%s.npz" % tag))
+    prob = FULL[tag]()
+    X = oracle_matrix(P, prob)
+    assert X.n == int(g["n"])
+    assert np.array_equal(P.kernel_rows_idx(X, g["rows_idx"], gamma=prob["gamma"]), g["rows"])
+
+
+def test_port_solves_config1_at_full_size(golden_dir):
+    """The 10,000 x 20 configuration to convergence: objective, rho and support-vector count of the reference."""
+    g = np.load(os.path.join(golden_dir, "full_c1.npz"))
+    prob = synth.config1()
+    X = oracle_matrix(P, prob)
+    y = binary_labels(prob)
+    n = len(y)
+    r = P.smo_solve(X, y, np.zeros(n), -y.astype(np.float64), 1e-3, prob["C"], prob["C"], 1024, gamma=prob["gamma"])
+    assert abs(r["obj"] - float(g["objective"])) <= 1e-6 * abs(float(g["objective"]))
+    assert abs(r["rho"] - float(g["rho"])) < 1e-6
+    assert int((r["alpha"] != 0).sum()) == int(g["n_sv"])

@@ -56,5 +56,13 @@ def rel_err(a, b, floor=1e-4):
     return float(np.max(np.abs(a - b) / np.maximum(np.abs(b), floor)))
 
 
+def rel_err_pure(a, b):
+    """Un-floored relative error max |a-b| / |b| over the entries with b != 0 (reported next to rel_err)."""
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    m = b != 0
+    return float(np.max(np.abs(a[m] - b[m]) / np.abs(b[m]))) if m.any() else 0.0
+
+
 def objective(alpha, f, y):
     return -float(np.sum(alpha - (f + y) * alpha * y / 2))

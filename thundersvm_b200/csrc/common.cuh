@@ -6,6 +6,8 @@
 #include <stdio.h>
 #include <stdarg.h>
 #include <math.h>
+#include <atomic>
+#include <initializer_list>
 #include "../../include/thundersvm_b200.h"
 
 namespace tsvm {
@@ -46,12 +48,30 @@ void count_launch(int k = 1);
         TSVM_CUDA(cudaPeekAtLastError());                                                        \
     } while (0)
 
+// One-time set-up that belongs to a device, not to the process (cudaFuncSetAttribute applies to the device
+// that is current when it runs): the statement runs on the first use on every device ordinal. Two threads
+// that meet here for the same device both run it; the set-ups are idempotent, so that race is harmless.
+constexpr int MAX_DEVICES = 64;
+#define TSVM_ONCE_PER_DEVICE(...)                                                                \
+    do {                                                                                         \
+        static std::atomic<unsigned long long> done__{0};                                        \
+        int dev__ = 0;                                                                           \
+        TSVM_CUDA(cudaGetDevice(&dev__));                                                        \
+        const unsigned long long bit__ = 1ull << (dev__ & (tsvm::MAX_DEVICES - 1));              \
+        if (!(done__.load(std::memory_order_acquire) & bit__)) {                                 \
+            __VA_ARGS__;                                                                         \
+            done__.fetch_or(bit__, std::memory_order_release);                                   \
+        }                                                                                        \
+    } while (0)
+
 // Device and pinned-host memory of the handles comes from a per-process pool (km.cu): a freed block is
 // kept and handed out again for a request of the same size class instead of going back to the driver.
 // Training a multi-class model creates and destroys a kernel matrix and a solver per class pair; the
 // driver's allocation calls cost more than such a sub-problem's whole solve.
 tsvm_status pool_alloc(void **p, size_t bytes);
-void pool_free(void *p);                      // waits for the device, like cudaFree
+void pool_free(void *p);                      // waits for the block's device, like cudaFree
+// Several blocks at once: one wait per device that owns any of them, then all are filed.
+void pool_free_many(std::initializer_list<void *> blocks);
 void pool_release();                          // returns every cached block to the driver
 tsvm_status pinned_alloc(void **p, size_t bytes);
 void pinned_free(void *p);

@@ -233,18 +233,17 @@ tsvm_status launch_dense_tc(tsvm_km *km, int m, float *out, long long ld_out, cu
     TSVM_TRY(make_map(&mxl, km->Xlo, km->n, km->d_pad, km->d_pad, tc::BM, false));
     TSVM_TRY(make_map(&mwh, km->Whi, m, km->d_pad, km->d_pad, tc::BN, false));
     TSVM_TRY(make_map(&mwl, km->Wlo, m, km->d_pad, km->d_pad, tc::BN, false));
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        TSVM_CUDA(cudaGetDevice(&dev));
-        TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int dev = 0, sms = 0;
+    TSVM_CUDA(cudaGetDevice(&dev));
+    TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    TSVM_ONCE_PER_DEVICE({
         TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc_kernel<EPI_RBF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int) tc::SMEM_BYTES));
         TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc_kernel<EPI_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int) tc::SMEM_BYTES));
         TSVM_CUDA(cudaFuncSetAttribute(dense_rows_tc_kernel<EPI_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int) tc::SMEM_BYTES));
-    }
+    });
     const int m_tiles = ceil_div(km->n, tc::BM);
     const int grid = m_tiles < sms ? m_tiles : sms;
 #define TC_LAUNCH(E)                                                                                              \

@@ -312,10 +312,12 @@ template <int EPI, bool F16>
 static tsvm_status launch_pair_kernel(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int m, float *out,
                                       long long ld_out, cudaStream_t st) {
     auto kernel = dense_rows_tc2_kernel<EPI, F16>;
-    static int max_clusters = 0;      // per instantiation
+    static int clusters_of_device[MAX_DEVICES] = {0};      // per instantiation and per device ordinal
+    int dev = 0;
+    TSVM_CUDA(cudaGetDevice(&dev));
+    int &max_clusters = clusters_of_device[dev & (MAX_DEVICES - 1)];
     if (!max_clusters) {
-        int dev = 0, sms = 0;
-        TSVM_CUDA(cudaGetDevice(&dev));
+        int sms = 0;
         TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
         TSVM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) tc2::SMEM_BYTES));
         cudaLaunchConfig_t probe = {};

@@ -4,6 +4,7 @@
 #include "common.cuh"
 #include <cuda_fp16.h>
 #include <string.h>
+#include <stdlib.h>
 #include <atomic>
 #include <map>
 #include <mutex>
@@ -34,6 +35,7 @@ auto &g_pool_live = *new std::unordered_map<void *, PoolBlock>;
 auto &g_pinned_live = *new std::unordered_map<void *, PoolBlock>;
 auto &g_pool_free = *new std::map<std::pair<int, size_t>, std::vector<void *>>;
 auto &g_pinned_free = *new std::map<size_t, std::vector<void *>>;
+size_t g_pool_cached = 0;               // bytes in g_pool_free
 
 size_t size_class(size_t bytes) {
     if (bytes < 512) return 512;
@@ -54,6 +56,7 @@ void pool_release() {
         for (void *q : kv.second) cudaFree(q);
         kv.second.clear();
     }
+    g_pool_cached = 0;
     cudaSetDevice(cur);
 }
 
@@ -68,6 +71,7 @@ tsvm_status pool_alloc(void **p, size_t bytes) {
         if (it != g_pool_free.end() && !it->second.empty()) {
             *p = it->second.back();
             it->second.pop_back();
+            g_pool_cached -= cls;
             g_pool_live[*p] = PoolBlock{dev, cls};
             return TSVM_OK;
         }
@@ -84,14 +88,68 @@ tsvm_status pool_alloc(void **p, size_t bytes) {
     return TSVM_OK;
 }
 
+// A freed block may be handed out again at once, so nothing in flight may still use it: one wait per device
+// that owns one of the blocks (the owning device, which need not be the caller's current one), then all of
+// them go to the free lists. Cached bytes above the cap go back to the driver, largest blocks first.
+static size_t pool_cache_cap() {
+    static const size_t cap = [] {
+        const char *e = getenv("TSVM_POOL_CACHE_MB");
+        return (size_t) (e ? strtoull(e, nullptr, 10) : 32768ull) << 20;
+    }();
+    return cap;
+}
+
+void pool_free_many(std::initializer_list<void *> blocks) {
+    int cur = 0;
+    bool have_cur = false;
+    unsigned long long synced = 0;
+    std::vector<void *> foreign;
+    {
+        std::lock_guard<std::mutex> lk(g_pool_mu);
+        for (void *p : blocks) {
+            if (!p) continue;
+            auto it = g_pool_live.find(p);
+            if (it == g_pool_live.end()) { foreign.push_back(p); continue; }
+            synced |= 1ull << (it->second.dev & (MAX_DEVICES - 1));
+        }
+    }
+    for (int dev = 0; dev < MAX_DEVICES; ++dev) {
+        if (!((synced >> dev) & 1ull)) continue;
+        if (!have_cur) { cudaGetDevice(&cur); have_cur = true; }
+        if (dev != cur) cudaSetDevice(dev);
+        cudaDeviceSynchronize();
+        if (dev != cur) cudaSetDevice(cur);
+    }
+    for (void *p : foreign) cudaFree(p);                     // not ours (never happens for handle memory)
+    std::vector<std::pair<int, void *>> to_driver;
+    {
+        std::lock_guard<std::mutex> lk(g_pool_mu);
+        for (void *p : blocks) {
+            if (!p) continue;
+            auto it = g_pool_live.find(p);
+            if (it == g_pool_live.end()) continue;
+            g_pool_free[{it->second.dev, it->second.cls}].push_back(p);
+            g_pool_cached += it->second.cls;
+            g_pool_live.erase(it);
+        }
+        // over the cap: return the largest cached blocks first
+        for (auto kv = g_pool_free.rbegin(); kv != g_pool_free.rend() && g_pool_cached > pool_cache_cap(); ++kv)
+            while (!kv->second.empty() && g_pool_cached > pool_cache_cap()) {
+                to_driver.push_back({kv->first.first, kv->second.back()});
+                kv->second.pop_back();
+                g_pool_cached -= kv->first.second;
+            }
+    }
+    for (auto &b : to_driver) {
+        if (!have_cur) { cudaGetDevice(&cur); have_cur = true; }
+        if (b.first != cur) cudaSetDevice(b.first);
+        cudaFree(b.second);
+        if (b.first != cur) cudaSetDevice(cur);
+    }
+}
+
 void pool_free(void *p) {
-    if (!p) return;
-    cudaDeviceSynchronize();                  // nothing in flight may still use the block when it is reused
-    std::lock_guard<std::mutex> lk(g_pool_mu);
-    auto it = g_pool_live.find(p);
-    if (it == g_pool_live.end()) { cudaFree(p); return; }     // not ours (never happens for handle memory)
-    g_pool_free[{it->second.dev, it->second.cls}].push_back(p);
-    g_pool_live.erase(it);
+    if (p) pool_free_many({p});
 }
 
 tsvm_status pinned_alloc(void **p, size_t bytes) {
@@ -266,21 +324,22 @@ __global__ void gather_rows_dense_kernel(const float *__restrict__ X, int ld, in
                                          float *__restrict__ sd_rows) {
     int i = blockIdx.x;
     if (i >= m) return;
-    int r = idx[i];
-    const float *x = X + (size_t) r * ld;
+    const int r = idx[i];
+    const int dr = r >= 0 ? d : 0;           // id -1 (an empty working-set slot) is staged as an all-zero row
+    const float *x = X + (size_t) (r >= 0 ? r : 0) * ld;
     float scale = 1.0f, unscale = 1.0f;
     if (dst.kind == 2) {
         float amax = 0.0f;
-        for (int k = threadIdx.x; k < d; k += blockDim.x) amax = fmaxf(amax, fabsf(x[k]));
+        for (int k = threadIdx.x; k < dr; k += blockDim.x) amax = fmaxf(amax, fabsf(x[k]));
         row_scale_from_max(block_max_abs(amax), scale, unscale);
         if (threadIdx.x == 0) dst.unscale[i] = unscale;
     }
     for (int k = threadIdx.x; k < dst.ld; k += blockDim.x) {
-        float v = k < d ? x[k] : 0.0f;
+        float v = k < dr ? x[k] : 0.0f;
         if (dst.W) dst.W[(size_t) i * dst.ld + k] = v;
         else store_planes(dst.kind, dst.hi, dst.lo, (size_t) i * dst.ld + k, v, scale);
     }
-    if (threadIdx.x == 0) sd_rows[i] = sd[r];
+    if (threadIdx.x == 0) sd_rows[i] = r >= 0 ? sd[r] : 0.0f;
 }
 
 // Same for a batch of new dense instances T (m x dt, stride ldt); features >= d are dropped.
@@ -336,6 +395,10 @@ __global__ void scatter_csr_to_wt_kernel(const float *__restrict__ val, const in
     int i = blockIdx.x;
     if (i >= m) return;
     int r = idx ? idx[i] : i;
+    if (r < 0) {                             // an empty working-set slot: an all-zero row
+        if (!clear && sd && threadIdx.x == 0) sd_rows[i] = 0.0f;
+        return;
+    }
     for (int p = row_ptr[r] + threadIdx.x; p < row_ptr[r + 1]; p += blockDim.x) {
         int c = col[p];
         if (c < d) WT[(size_t) c * wt_ld + i] = clear ? 0.0f : val[p];
@@ -370,7 +433,7 @@ __global__ void gather_planes_kernel(const float *__restrict__ Xhi, const float 
                                      float *__restrict__ unscale_out) {
     const int i = blockIdx.x;
     if (i >= m) return;
-    const int r = ids[i];
+    const int r = ids[i] >= 0 ? ids[i] : 0;      // an empty slot copies some row; its y = 0 keeps it inert
     const size_t vecs = row_bytes / 16;
     const uint4 *sh = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(Xhi) + (size_t) r * row_bytes);
     const uint4 *sl = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(Xlo) + (size_t) r * row_bytes);
@@ -492,8 +555,7 @@ static tsvm_status ensure_scratch(tsvm_km *km, int m) {
     if (m <= km->w_cap) return TSVM_OK;
     int cap = 128;
     while (cap < m) cap *= 2;
-    pool_free(km->W); pool_free(km->Whi); pool_free(km->Wlo); pool_free(km->WT); pool_free(km->sd_rows);
-    pool_free(km->w_unscale);
+    pool_free_many({km->W, km->Whi, km->Wlo, km->WT, km->sd_rows, km->w_unscale});
     km->W = km->Whi = km->Wlo = km->WT = km->sd_rows = km->w_unscale = nullptr;
     km->w_cap = 0;
     TSVM_TRY(dev_alloc(&km->sd_rows, (size_t) cap));
@@ -526,7 +588,7 @@ static inline int wanted_plane_kind(const tsvm_km *km) {
 static tsvm_status ensure_planes(tsvm_km *km, cudaStream_t st) {
     const int kind = wanted_plane_kind(km);
     if (kind == 0 || kind == km->plane_kind) return TSVM_OK;
-    pool_free(km->Xhi); pool_free(km->Xlo);
+    pool_free_many({km->Xhi, km->Xlo});
     km->Xhi = km->Xlo = nullptr;
     km->plane_kind = 0;
     km->plane_ld = kind == 1 ? km->d_pad : (km->d + 7) & ~7;
@@ -730,11 +792,9 @@ tsvm_status tsvm_km_create_csr(const float *val, const int *row_ptr, const int *
 
 void tsvm_km_destroy(tsvm_km *km) {
     if (!km) return;
-    pool_free(km->X_owned); pool_free(km->Xhi); pool_free(km->Xlo); pool_free(km->x_unscale); pool_free(km->w_unscale);
-    pool_free(km->val_owned); pool_free(km->row_ptr_owned); pool_free(km->col_owned);
-    pool_free(km->self_dot); pool_free(km->diag);
-    pool_free(km->W); pool_free(km->Whi); pool_free(km->Wlo); pool_free(km->WT); pool_free(km->sd_rows);
-    pool_free(km->status_dev);
+    pool_free_many({km->X_owned, km->Xhi, km->Xlo, km->x_unscale, km->w_unscale, km->val_owned, km->row_ptr_owned,
+                    km->col_owned, km->self_dot, km->diag, km->W, km->Whi, km->Wlo, km->WT, km->sd_rows,
+                    km->status_dev});
     if (km->status_host) pinned_free(km->status_host);
     delete km;
 }

@@ -120,8 +120,7 @@ tsvm_status tsvm_predict_dec(tsvm_km *km_sv, const double *coef_dev, const int *
             s = TSVM_ERR_DEVICE;
         }
     } else cudaStreamSynchronize(st);
-    pool_free(K);
-    pool_free(meta);
+    pool_free_many({K, meta});
     return s;
 }
 

@@ -652,7 +652,7 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
         if (t < ws) {
             alpha_ws[t] = a[s];
             alpha_diff[t] = -(a[s] - aold[s]) * y[s];
-            if (alpha_global) alpha_global[ids[t]] = a[s];
+            if (alpha_global && ids[t] >= 0) alpha_global[ids[t]] = a[s];
         }
     }
     if (tid == 0) diff[1] = it;
@@ -674,13 +674,18 @@ __global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *
     const int a = blockIdx.x;                      // logical slot of the row
     // rows >= block_rows of the block are written by someone else (the overlapped iteration computes them
     // directly); the slot vectors are gathered for every slot
+    // a slot without an instance (id -1: fewer eligible instances than slots) is inert: y = 0 puts it in no set
     if (a < block_rows) {
         const float *row = rows + (size_t) phys_row(a, q, first_half_phys) * ld;
-        for (int b = threadIdx.x; b < ws; b += blockDim.x) kww[(size_t) a * ws + b] = row[ids[b]];
+        for (int b = threadIdx.x; b < ws; b += blockDim.x) {
+            const int id = ids[b];
+            kww[(size_t) a * ws + b] = id >= 0 ? row[id] : 0.0f;
+        }
     }
     if (threadIdx.x == 0) {
         const int id = ids[a];
-        diag_ws[a] = diag[id]; y_ws[a] = y[id]; f_ws[a] = f[id]; alpha_ws[a] = alpha[id];
+        if (id >= 0) { diag_ws[a] = diag[id]; y_ws[a] = y[id]; f_ws[a] = f[id]; alpha_ws[a] = alpha[id]; }
+        else { diag_ws[a] = 1.0f; y_ws[a] = 0; f_ws[a] = 0.0; alpha_ws[a] = 0.0; }
     }
 }
 
@@ -688,9 +693,9 @@ __global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *
 __global__ void shift_ws_kernel(int *ids, int q, unsigned char *in_ws) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;   // launched as one block, q <= 512
     if (t < q) {
-        const int leaving = ids[t], staying = ids[q + t];  // distinct instances
-        in_ws[leaving] = 0;
-        in_ws[staying] = 1;
+        const int leaving = ids[t], staying = ids[q + t];  // distinct instances (-1: empty slot)
+        if (leaving >= 0) in_ws[leaving] = 0;
+        if (staying >= 0) in_ws[staying] = 1;
         ids[t] = staying;
     }
 }
@@ -981,8 +986,7 @@ tsvm_status tsvm_ws_create(int n_max, int ws_max, tsvm_ws **out) {
 
 void tsvm_ws_destroy(tsvm_ws *w) {
     if (!w) return;
-    pool_free(w->state); pool_free(w->hist); pool_free(w->ticket); pool_free(w->count);
-    pool_free(w->cand_f); pool_free(w->cand_id);
+    pool_free_many({w->state, w->hist, w->ticket, w->count, w->cand_f, w->cand_id});
     delete w;
 }
 
@@ -995,12 +999,8 @@ static tsvm_status ws_candidates_cap(tsvm_ws *w, int solver_kind, int n, const d
     if (grid > 296) grid = 296;
     if (grid < 1) grid = 1;
     const size_t hist_smem = (size_t) lists * RADIX_BINS * sizeof(int);
-    static bool configured = false;
-    if (!configured) {
-        TSVM_CUDA(cudaFuncSetAttribute(select_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int) (MAX_LISTS * RADIX_BINS * sizeof(int))));
-        configured = true;
-    }
+    TSVM_ONCE_PER_DEVICE(TSVM_CUDA(cudaFuncSetAttribute(select_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                        (int) (MAX_LISTS * RADIX_BINS * sizeof(int)))));
     TSVM_LAUNCH(select_init_kernel, 16, 256, 0, st, w->state, w->hist, w->ticket, lists, want);
     TSVM_LAUNCH(fill_int_kernel, ceil_div(lists * cap, 256), 256, 0, st, cand_id_dev, lists * cap, -1);
     for (int p = 0; p < RADIX_PASSES; ++p)
@@ -1023,12 +1023,8 @@ tsvm_status tsvm_ws_candidates(tsvm_ws *w, int solver_kind, int n, const double 
 static tsvm_status ws_merge_impl(tsvm_ws *w, int solver_kind, const double *cand_f_dev, const int *cand_id_dev, int len,
                                  int seg_len, int want, int *out_ids_dev, cudaStream_t st) {
     const size_t smem = merge_smem_bytes(len);
-    static size_t configured = 0;
-    if (smem > configured) {
-        TSVM_CUDA(cudaFuncSetAttribute(select_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int) merge_smem_bytes(MERGE_MAX_LEN)));
-        configured = merge_smem_bytes(MERGE_MAX_LEN);
-    }
+    TSVM_ONCE_PER_DEVICE(TSVM_CUDA(cudaFuncSetAttribute(select_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                        (int) merge_smem_bytes(MERGE_MAX_LEN))));
     TSVM_LAUNCH(select_merge_kernel, 1, MERGE_THREADS, smem, st, solver_kind, cand_f_dev, cand_id_dev, len, want,
                 out_ids_dev, w->count, seg_len);
     return TSVM_OK;
@@ -1046,12 +1042,9 @@ static tsvm_status ws_sort_impl(int solver_kind, const double *in_f, const int *
     int P = 1;
     while (P < len) P <<= 1;
     const size_t smem = (size_t) P * 12 + 8 + (size_t) P * 8;
-    static bool configured = false;
-    if (!configured) {
-        TSVM_CUDA(cudaFuncSetAttribute(select_sort_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int) ((size_t) MERGE_MAX_LEN * 20 + 8)));
-        configured = true;
-    }
+    TSVM_ONCE_PER_DEVICE(TSVM_CUDA(cudaFuncSetAttribute(select_sort_candidates_kernel,
+                                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                        (int) ((size_t) MERGE_MAX_LEN * 20 + 8))));
     TSVM_LAUNCH(select_sort_candidates_kernel, solver_kind == TSVM_SOLVER_C ? 2 : 4, MERGE_THREADS, smem, st,
                 solver_kind, in_f, in_id, len, out_f, out_id, out_len);
     return TSVM_OK;
@@ -1089,7 +1082,7 @@ tsvm_status tsvm_select_working_set(tsvm_ws *w, int solver_kind, int n, const do
 // ticket / count words and the candidate lists for up to TSVM_STATIC_WS_MAX wanted ids and four
 // lists. It is a fixed part of the library image: every GPU that loads the library holds these
 // bytes until the process exits.
-constexpr int STATIC_WS_MAX = 1024;
+constexpr int STATIC_WS_MAX = TSVM_STATIC_WS_MAX;
 constexpr size_t STATIC_OFF_STATE = 0;                                                   // SelectState[4]
 constexpr size_t STATIC_OFF_HIST = 256;                                                  // int[4 * 4096]
 constexpr size_t STATIC_OFF_TICKET = STATIC_OFF_HIST + sizeof(int) * MAX_LISTS * RADIX_BINS;   // int
@@ -1101,8 +1094,10 @@ static_assert(sizeof(SelectState) * MAX_LISTS <= STATIC_OFF_HIST, "selection sta
 static __device__ __align__(256) unsigned char g_static_select_scratch[STATIC_SCRATCH_BYTES];
 
 // In host code the array's name is only a stand-in for the symbol, not a device address: the address
-// is asked from the runtime once per device (with that device current) and remembered.
-constexpr int STATIC_MAX_DEVICES = 64;
+// is asked from the runtime once per device (with that device current) and remembered. The cache is
+// written without a lock by whichever host thread calls first on a device; every writer stores the same
+// value, so concurrent first calls are harmless.
+constexpr int STATIC_MAX_DEVICES = MAX_DEVICES;
 static unsigned char *g_static_scratch_addr[STATIC_MAX_DEVICES] = {nullptr};
 
 tsvm_status tsvm_select_working_set_static(int solver_kind, int n, const double *f_dev, const double *alpha_dev,
@@ -1207,13 +1202,12 @@ struct tsvm_solver {
     std::chrono::steady_clock::time_point t_begin;
 
     ~tsvm_solver() {
-        pool_free(ids); pool_free(y_ws); pool_free(rows); pool_free(kww); pool_free(diag_ws); pool_free(f_ws);
-        pool_free(a_ws); pool_free(alpha_diff); pool_free(diff); pool_free(red); pool_free(in_ws);
+        pool_free_many({ids, y_ws, rows, kww, diag_ws, f_ws, a_ws, alpha_diff, diff, red, in_ws, ws_hi, ws_lo, ws_sd,
+                        ws_unscale});
         tsvm_ws_destroy(sel);
         if (diff_host) pinned_free(diff_host);
         for (auto e : ev) if (e) cudaEventDestroy(e);
         for (auto e : {ev_fork, ev_join, ev_l0, ev_l1}) if (e) cudaEventDestroy(e);
-        pool_free(ws_hi); pool_free(ws_lo); pool_free(ws_sd); pool_free(ws_unscale);
         if (st2) cudaStreamDestroy(st2);
     }
 
@@ -1366,11 +1360,20 @@ struct tsvm_solver {
         }
         TSVM_CUDA(cudaEventRecord(ev[4], st));
         TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
+        int *got_host = reinterpret_cast<int *>(diff_host + 8);
+        TSVM_CUDA(cudaMemcpyAsync(got_host, sel->count, sizeof(int), cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaMemcpyAsync(km->status_host, km->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaStreamSynchronize(st));
         if (km->status_host[0] != 0) {
             set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", km->status_host[0]);
             return TSVM_ERR_DEVICE;
+        }
+        const int wanted = iter == 0 ? ws : q;
+        if (*got_host < wanted) {
+            // the reference's selection loop never ends here (csmosolver.cpp:131-164); the empty slots were inert
+            set_error("working-set selection found %d eligible instances for %d slots (is a class weight or C zero?)",
+                      *got_host, wanted);
+            return TSVM_ERR_INVALID;
         }
         float ms;
         cudaEventElapsedTime(&ms, ev[0], ev[1]); t_sel += ms;
@@ -1587,9 +1590,8 @@ struct tsvm_shard {
     std::chrono::steady_clock::time_point t_begin;
 
     ~tsvm_shard() {
-        pool_free(ids); pool_free(y_ws); pool_free(rows); pool_free(kww); pool_free(m_hi); pool_free(m_lo); pool_free(m_sd);
-        pool_free(m_unscale); pool_free(m_diag); pool_free(f_ws); pool_free(a_ws); pool_free(alpha_diff); pool_free(diff);
-        pool_free(grp_f); pool_free(grp_id); pool_free(in_ws);
+        pool_free_many({ids, y_ws, rows, kww, m_hi, m_lo, m_sd, m_unscale, m_diag, f_ws, a_ws, alpha_diff, diff, grp_f,
+                        grp_id, in_ws});
         tsvm_ws_destroy(sel);
         if (diff_host) pinned_free(diff_host);
         for (auto e : {ev_fork, ev_join, ev_r0, ev_r1, ev_b0, ev_b1}) if (e) cudaEventDestroy(e);
@@ -1715,11 +1717,18 @@ struct tsvm_shard {
                     rows, ld, rows_vec_ok(rows, ld), iter == 0 ? 0 : q, ws, update_f_cols(n_local));
         TSVM_LAUNCH(shard_scatter_kernel, ceil_div(ws, 256), 256, 0, st, ids, ws, lo, hi, a_ws, alpha);
         TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
+        int *got_host = reinterpret_cast<int *>(diff_host + 2);
+        TSVM_CUDA(cudaMemcpyAsync(got_host, sel->count, sizeof(int), cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaMemcpyAsync(km->status_host, km->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaStreamSynchronize(st));
         if (km->status_host[0] != 0) {
             set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", km->status_host[0]);
             return TSVM_ERR_DEVICE;
+        }
+        if (*got_host < n_new) {
+            set_error("working-set selection found %d eligible instances for %d slots (is a class weight or C zero?)",
+                      *got_host, n_new);
+            return TSVM_ERR_INVALID;
         }
         float ms_ev = 0;
         cudaEventElapsedTime(&ms_ev, ev_r0, ev_r1); t_rows += ms_ev;
