@@ -296,11 +296,24 @@ tsvm_status tsvm_update_f(double *f_dev, int n, const double *alpha_diff_dev, in
  * nb = n_classes (n_classes - 1) / 2, pairs ordered (0,1),(0,2),...; coef_dev is the
  * (n_classes - 1) x n_sv layout of include/thundersvm/model/svmmodel.h:155-164, sv_count_host
  * the per-class support-vector counts, rho_dev[nb]. km_sv holds the support vectors. The test
- * batch is dense (T_dev != NULL) or CSR. Batching over the test rows is internal. */
+ * batch is dense (T_dev != NULL) or CSR. Batching over the test rows is internal. With dense support
+ * vectors of more than 32 features the coefficient sums are part of the contraction's epilogue (FP32
+ * partial sums over 128 support vectors, combined in FP64) and the test x SV kernel block is never stored;
+ * otherwise it is computed in slabs of at most max_mem_bytes (0 = a quarter of the free memory). */
 tsvm_status tsvm_predict_dec(tsvm_km *km_sv, const double *coef_dev, const int *sv_count_host,
                              const double *rho_dev, int n_classes, int m, const float *T_dev, int dt, int ldt,
                              const float *tval_dev, const int *trow_ptr_dev, const int *tcol_dev, long long tnnz,
                              double *dec_dev, size_t max_mem_bytes, void *stream);
+
+/* The same contraction with the vote on the device: labels_dev[r] = index of the winning class (first
+ * maximum wins), and no decision value leaves the device - they live in a scratch of one slab of test rows.
+ * Replaces SvmModel::predict_dec_values_instant (src/thundersvm/model/svmmodel.cpp:119-154) and
+ * svm_kernel::sum_kernel_values_instant (kernelmatrix_kernel.cu:99-138,164-172), which the reference uses
+ * for models with more than 10,000 class pairs (svc.cpp:180-181). */
+tsvm_status tsvm_predict_labels(tsvm_km *km_sv, const double *coef_dev, const int *sv_count_host,
+                                const double *rho_dev, int n_classes, int m, const float *T_dev, int dt, int ldt,
+                                const float *tval_dev, const int *trow_ptr_dev, const int *tcol_dev, long long tnnz,
+                                int *labels_dev, size_t max_mem_bytes, void *stream);
 
 /* SVC::predict_label voting (src/thundersvm/model/svc.cpp:265-289): out_dev[r] = index of the
  * winning class. */

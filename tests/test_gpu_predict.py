@@ -59,3 +59,58 @@ def test_reference_fixture_decision_values(capi, golden_dir):
     labels = np.array([0.0, 2.0, 3.0])[capi.vote(dec, 3).cpu().numpy()]
     assert np.array_equal(labels, g["svc_pred"])
     assert abs((labels == y).mean() - 0.98) < 1e-5
+
+
+def _fused_case(capi, nc, cnt, d, m, kernel="rbf", gamma=0.02, coef0=0.0, degree=3, engine=None, csr_batch=False,
+                seed=5):
+    """Dense support vectors with more than 32 features: the coefficient sums are the contraction's epilogue."""
+    rng = np.random.default_rng(seed)
+    cnt = np.asarray(cnt, dtype=np.int32)
+    n_sv = int(cnt.sum())
+    SVd = (rng.standard_normal((n_sv, d)) * (rng.random((n_sv, d)) < 0.6)).astype(np.float32)
+    T = (rng.standard_normal((m, d)) * (rng.random((m, d)) < 0.6)).astype(np.float32)
+    coef = rng.standard_normal((nc - 1, n_sv)) * 3
+    rho = rng.standard_normal(nc * (nc - 1) // 2)
+    kw = dict(kernel=kernel, gamma=gamma, coef0=coef0, degree=degree)
+    want = P.predict_dec(P.Csr(dense=SVd), coef.reshape(-1), cnt, rho, nc, P.Csr(dense=T), **kw)
+    km = capi.KernelMatrix(dense=_t(SVd), **kw)
+    if engine:
+        km.set_dense_engine(engine)
+    if csr_batch:
+        c = P.Csr(dense=T)
+        nz = c.val != 0                          # drop the explicit zeros: a genuinely sparse batch
+        rp = np.concatenate([[0], np.cumsum(np.add.reduceat(nz, c.row_ptr[:-1]))]).astype(np.int32)
+        batch = dict(csr=(_t(c.val[nz]), _t(rp), _t(c.col[nz])))
+    else:
+        batch = dict(dense=_t(T))
+    dec = capi.predict_dec(km, _t(coef.reshape(-1)), cnt, _t(rho), nc, **batch).cpu().numpy()
+    scale = max(1.0, float(np.max(np.abs(want))))
+    assert np.max(np.abs(dec - want)) < 1e-3 * scale, np.max(np.abs(dec - want))
+    lab = capi.predict_labels(km, _t(coef.reshape(-1)), cnt, _t(rho), nc, **batch).cpu().numpy()
+    assert np.array_equal(lab, capi.vote(_t(dec), nc).cpu().numpy())
+    assert np.mean(lab == P.vote(want, nc)) >= 0.999
+    km.close()
+
+
+@pytest.mark.parametrize("engine", [None, "tensor2"])
+def test_fused_prediction_multiclass_ragged_classes(capi, engine):
+    """Class blocks that start and end inside a 128-instance tile, a tail tile, a tail row block."""
+    _fused_case(capi, 4, [300, 37, 401, 262], d=200, m=700, engine=engine)
+
+
+def test_fused_prediction_binary_tails_and_sparse_batch(capi):
+    _fused_case(capi, 2, [513, 258], d=136, m=257)
+    _fused_case(capi, 2, [100, 29], d=72, m=5, csr_batch=True)
+    _fused_case(capi, 3, [1, 1, 1], d=40, m=300)
+
+
+@pytest.mark.parametrize("kernel,kw", [("linear", {}), ("poly", dict(gamma=0.01, coef0=0.5, degree=3)),
+                                       ("sigmoid", dict(gamma=0.01, coef0=0.1))])
+def test_fused_prediction_other_kernels(capi, kernel, kw):
+    _fused_case(capi, 3, [150, 200, 90], d=96, m=333, kernel=kernel, **kw)
+
+
+def test_fused_prediction_many_classes(capi):
+    """20 classes: 19 coefficient rows per support vector (more than the shared-memory table holds) and 190 pairs;
+    several launches over the test rows."""
+    _fused_case(capi, 20, [17 + 3 * c for c in range(20)], d=64, m=4500)

@@ -27,7 +27,7 @@ EXPORTS = [
     "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_set_overlap", "tsvm_solver_destroy", "tsvm_shard_create", "tsvm_shard_candidates", "tsvm_shard_select", "tsvm_shard_iterate", "tsvm_nccl_unique_id", "tsvm_nccl_comm_create", "tsvm_nccl_comm_destroy", "tsvm_shard_attach_nccl", "tsvm_shard_step", "tsvm_shard_get_stats", "tsvm_shard_destroy", "tsvm_working_set_size",
     "tsvm_ws_create", "tsvm_ws_destroy", "tsvm_ws_candidates", "tsvm_ws_merge", "tsvm_ws_sort_candidates", "tsvm_ws_merge_sorted", "tsvm_select_working_set",
     "tsvm_select_working_set_static",
-    "tsvm_local_smo", "tsvm_update_f", "tsvm_predict_dec", "tsvm_vote",
+    "tsvm_local_smo", "tsvm_update_f", "tsvm_predict_dec", "tsvm_predict_labels", "tsvm_vote",
 ]
 
 
@@ -114,6 +114,7 @@ def lib():
     L.tsvm_local_smo.argtypes = [i, i, vp, vp, vp, vp, vp, vp, d, d, d, i, vp, vp]
     L.tsvm_update_f.argtypes = [vp, i, vp, i, vp, ll, vp]
     L.tsvm_predict_dec.argtypes = [vp, vp, C.POINTER(i), vp, i, i, vp, i, i, vp, vp, vp, ll, vp, sz, vp]
+    L.tsvm_predict_labels.argtypes = [vp, vp, C.POINTER(i), vp, i, i, vp, i, i, vp, vp, vp, ll, vp, sz, vp]
     L.tsvm_vote.argtypes = [vp, i, i, vp, vp]
     _lib = L
     return L
@@ -487,6 +488,24 @@ def predict_dec(km_sv, coef, sv_count, rho, n_classes, dense=None, csr=None, max
         check(lib().tsvm_predict_dec(km_sv.handle, _ptr(coef), cnt, _ptr(rho), n_classes, m, None, 0, 0, _ptr(val),
                                      _ptr(row_ptr), _ptr(col), val.numel(), _ptr(dec), max_mem_bytes, _stream()))
     return dec
+
+
+def predict_labels(km_sv, coef, sv_count, rho, n_classes, dense=None, csr=None, max_mem_bytes=0):
+    """-> int32 [m] index of the winning class per test row; the decision values stay inside the library."""
+    cnt = (C.c_int * n_classes)(*[int(v) for v in sv_count])
+    if dense is not None:
+        m = dense.shape[0]
+        out = torch.empty(m, dtype=torch.int32, device="cuda")
+        check(lib().tsvm_predict_labels(km_sv.handle, _ptr(coef), cnt, _ptr(rho), n_classes, m, _ptr(dense),
+                                        dense.shape[1], dense.stride(0), None, None, None, 0, _ptr(out),
+                                        max_mem_bytes, _stream()))
+    else:
+        val, row_ptr, col = csr
+        m = row_ptr.numel() - 1
+        out = torch.empty(m, dtype=torch.int32, device="cuda")
+        check(lib().tsvm_predict_labels(km_sv.handle, _ptr(coef), cnt, _ptr(rho), n_classes, m, None, 0, 0, _ptr(val),
+                                        _ptr(row_ptr), _ptr(col), val.numel(), _ptr(out), max_mem_bytes, _stream()))
+    return out
 
 
 def vote(dec, n_classes):

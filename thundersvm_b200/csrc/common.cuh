@@ -231,6 +231,11 @@ tsvm_status km_rows_staged_on(tsvm_km *km, const InstancePlanes &X, int q, float
                               cudaStream_t st);
 tsvm_status km_rows_planes_on(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int q, float *out,
                               long long ld_out, cudaStream_t st);
+tsvm_status km_stage_instances_dense(tsvm_km *km, const float *T, int mm, int dt, int ldt, cudaStream_t st);
+tsvm_status km_stage_instances_csr(tsvm_km *km, const float *tval, const int *rp, const int *tcol, int mm,
+                                   cudaStream_t st);
+tsvm_status launch_dense_tc2_predict(tsvm_km *km, int m, const double *coef_dev, const int *sv_class_dev,
+                                     int n_classes, double *dec_dev, cudaStream_t st);
 tsvm_status km_stage_rows_features(tsvm_km *km, const float *T_dev, int ldt, const float *sd_T_dev, int m,
                                    cudaStream_t st);
 }  // namespace tsvm

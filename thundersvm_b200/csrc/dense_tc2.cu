@@ -44,7 +44,12 @@ constexpr int REGS_CONTROL = 56, REGS_EPILOGUE = 224;
 constexpr int EPI_CHUNK = 16;
 constexpr uint32_t EPI_STAGE_BYTES = EPI_CHUNK * EPI_WARPS * 32 * 4;
 constexpr uint32_t EPI_CONST_BYTES = EPI_WARPS * 2 * COLS_PER_THREAD * 4;
+// prediction form: coefficients (up to PRED_NC_SMEM coefficient rows) and class ids of this CTA's 128 instances
+constexpr int PRED_NC_SMEM = 16;
+constexpr uint32_t PRED_BYTES = PRED_NC_SMEM * BM * 4 + BM * 4;
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_STAGE_BYTES + EPI_CONST_BYTES;
+constexpr uint32_t SMEM_BYTES_PREDICT = SMEM_BYTES + PRED_BYTES;
+static_assert(SMEM_BYTES_PREDICT <= 227 * 1024, "prediction form does not fit the shared memory of an SM");
 constexpr uint32_t TMEM_COLS = 512;
 // D=F32, K-major, N=256, M=256 (two CTAs x 128); A=B=TF32 (format 2) or F16 (format 0)
 constexpr uint32_t IDESC_SHAPE = (1u << 4) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
@@ -103,13 +108,30 @@ __device__ __forceinline__ void stage_chunk(const float (&sum)[tc2::COLS_PER_THR
     for (int c = 0; c < tc2::EPI_CHUNK; ++c) priv[c * (tc2::EPI_WARPS * 32)] = sum[CH * tc2::EPI_CHUNK + c];
 }
 
-template <int EPI, bool F16>
+// Prediction form of the kernel (PREDICT = true): the instances are the support vectors, the requested rows
+// the test rows, and instead of writing the kernel values the epilogue multiplies them by the support
+// vectors' coefficients and adds the sums to the decision values - svm_kernel::sum_kernel_values
+// (src/thundersvm/kernel/kernelmatrix_kernel.cu:69-97) folded into the contraction, so that the
+// test x SV kernel block never reaches HBM.
+struct PredictArgs {
+    const double *coef;        // (n_classes - 1) x n_sv, the model's layout (include/thundersvm/model/svmmodel.h:155-164)
+    const int *sv_class;       // class of every support vector [n_sv]
+    double *dec;               // [m][n_pairs], preset to -rho; this launch adds its sums
+    int n_classes, n_pairs;
+};
+
+__device__ __forceinline__ int pair_index(int n_classes, int i, int j) {      // i < j, pairs ordered (0,1),(0,2),...
+    return i * (2 * n_classes - i - 1) / 2 + (j - i - 1);
+}
+
+template <int EPI, bool F16, bool PREDICT>
 __global__ void __launch_bounds__(tc2::THREADS, 1)
 dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
                       const __grid_constant__ CUtensorMap map_whi, const __grid_constant__ CUtensorMap map_wlo,
                       int n, int m, int row_len, const float *__restrict__ sd, const float *__restrict__ sd_rows,
                       const float *__restrict__ x_unscale, const float *__restrict__ w_unscale,
-                      KernelFn fn, float *__restrict__ out, long long ld_out, int *__restrict__ status) {
+                      KernelFn fn, float *__restrict__ out, long long ld_out, int *__restrict__ status,
+                      const PredictArgs pa) {
     using namespace tc2;
     constexpr int BK = F16 ? 64 : 32;          // elements per k slab
     constexpr int PROMO = F16 ? TSVM_PROMO : 1;   // k slabs summed in tensor memory before the FP32 promotion
@@ -121,6 +143,7 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
     const uint32_t tfull_bar = empty_bar + 8 * STAGES, tempty_bar = tfull_bar + 16;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile int *epi_abort = reinterpret_cast<volatile int *>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -134,6 +157,7 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar + 8 * a, 1); mbar_init(tempty_bar + 8 * a, 2 * EPI_WARPS); }
         *abort_flag = 0;
+        *epi_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -216,6 +240,10 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
         float *priv = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256) + (warp - EPI_WARP0) * 32 + lane;
         float *rowc = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES) +
                       (warp - EPI_WARP0) * 2 * COLS_PER_THREAD;
+        // prediction form: coefficient table [coefficient row][instance of this CTA] and class ids
+        float *coef_sm = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES + EPI_CONST_BYTES);
+        int *cls_sm = reinterpret_cast<int *>(coef_sm + PRED_NC_SMEM * BM);
+        const int nc = PREDICT ? pa.n_classes - 1 : 0;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         for (int item = cluster_id; item < n_items && ok; item += n_clusters) {
@@ -223,6 +251,18 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
             const int j = pt * 2 * BM + (int) rank * BM + quarter * 32 + lane;
             const float sdj = j < n ? sd[j] : 0.0f;
             const float uxj = (F16 && j < n) ? x_unscale[j] : 1.0f;
+            if constexpr (PREDICT) {
+                // coefficients and classes of this CTA's 128 instances, staged by the first four epilogue warps
+                // while the k loop runs; both column halves read them after the k loop
+                if (half == 0) {
+                    const int s0 = quarter * 32 + lane;                     // instance of this CTA, 0..127
+                    const int js = pt * 2 * BM + (int) rank * BM + s0;
+                    cls_sm[s0] = js < n ? pa.sv_class[js] : -1;
+                    if (nc <= PRED_NC_SMEM)
+                        for (int cr = 0; cr < nc; ++cr)
+                            coef_sm[cr * BM + s0] = js < n ? (float) pa.coef[(size_t) cr * n + js] : 0.0f;
+                }
+            }
             {
                 // Self dot and 1/scale of this warp's 128 requested rows go to shared memory by asynchronous
                 // copies while the k loop runs: with nearly all of the SM's memory configured as shared, the
@@ -255,7 +295,16 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                     if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar + 8 * acc, 0));
                     if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 }
-                if (!ok) break;
+                if constexpr (PREDICT) {
+                    // The prediction form exchanges data between the epilogue warps through named barriers, so
+                    // all eight warps must leave together: a warp whose wait gave up says so before the
+                    // barrier, and every warp reads the word after it.
+                    if (!ok && lane == 0) *epi_abort = 1;
+                    asm volatile("bar.sync 3, 256;" ::: "memory");       // also: coefficient table is complete
+                    if (*epi_abort) { ok = false; break; }
+                } else {
+                    if (!ok) break;
+                }
                 // The sums live in registers, so a loop over them has to be fully unrolled; with the kernel
                 // function in its body that is 128 copies of it, and the instruction fetch of such an
                 // epilogue cost several times its arithmetic. Instead the sums pass 32 at a time through a
@@ -275,19 +324,74 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                         case 6: stage_chunk<6>(sum, priv); break;
                         default: stage_chunk<7>(sum, priv); break;
                     }
-                    if (j < n) {
-                        const int cbase = ch * EPI_CHUNK;
-                        const int lim = m - (i0 + cbase) < EPI_CHUNK ? m - (i0 + cbase) : EPI_CHUNK;
-                        float *o = out + (size_t) (i0 + cbase) * ld_out + j;
+                    const int cbase = ch * EPI_CHUNK;
+                    if constexpr (!PREDICT) {
+                        if (j < n) {
+                            const int lim = m - (i0 + cbase) < EPI_CHUNK ? m - (i0 + cbase) : EPI_CHUNK;
+                            float *o = out + (size_t) (i0 + cbase) * ld_out + j;
 #pragma unroll 8
-                        for (int c = 0; c < lim; ++c) {
+                            for (int c = 0; c < lim; ++c) {
+                                float dot = priv[c * (EPI_WARPS * 32)];
+                                if constexpr (F16) dot = dot * uxj * rowc[COLS_PER_THREAD + cbase + c];
+                                o[(size_t) c * ld_out] = epilogue_value<EPI>(fn, dot, rowc[cbase + c], sdj);
+                            }
+                        }
+                    } else {
+                        // kernel values of the own instance for the chunk's 16 test rows, back into the staging block
+#pragma unroll 8
+                        for (int c = 0; c < EPI_CHUNK; ++c) {
                             float dot = priv[c * (EPI_WARPS * 32)];
                             if constexpr (F16) dot = dot * uxj * rowc[COLS_PER_THREAD + cbase + c];
-                            o[(size_t) c * ld_out] = epilogue_value<EPI>(fn, dot, rowc[cbase + c], sdj);
+                            priv[c * (EPI_WARPS * 32)] = j < n ? epilogue_value<EPI>(fn, dot, rowc[cbase + c], sdj) : 0.0f;
                         }
+                        // the four warps of this column half exchange: every warp takes four of the 16 test rows
+                        // and sums coefficient x kernel value over the CTA's 128 instances
+                        asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+                        const float *blk = reinterpret_cast<const float *>(ring_ptr + STAGES * STAGE_BYTES + 256) + half * 128;
+                        const int c_first = cls_sm[0];
+                        int c_last = cls_sm[BM - 1];
+                        if (c_last < 0) {          // tail tile: class of the last real instance
+                            const int last_real = n - 1 - (pt * 2 * BM + (int) rank * BM);
+                            c_last = last_real >= 0 ? cls_sm[last_real] : c_first;
+                        }
+                        int cq[4];
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) cq[q4] = cls_sm[q4 * 32 + lane];
+                        for (int cc = 0; cc < 4; ++cc) {
+                            const int c = quarter * 4 + cc;
+                            const int r = i0 + cbase + c;
+                            if (r >= m || c_first < 0) continue;
+                            float kv[4];
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4) kv[q4] = blk[c * (EPI_WARPS * 32) + q4 * 32 + lane];
+                            for (int cl = c_first; cl <= c_last; ++cl)
+                                for (int cr = 0; cr < nc; ++cr) {
+                                    float p = 0.0f;
+#pragma unroll
+                                    for (int q4 = 0; q4 < 4; ++q4) {
+                                        float cf;
+                                        if (nc <= PRED_NC_SMEM) cf = coef_sm[cr * BM + q4 * 32 + lane];
+                                        else {
+                                            const int js = pt * 2 * BM + (int) rank * BM + q4 * 32 + lane;
+                                            cf = js < n ? (float) pa.coef[(size_t) cr * n + js] : 0.0f;
+                                        }
+                                        p = fmaf(cq[q4] == cl ? cf : 0.0f, kv[q4], p);
+                                    }
+#pragma unroll
+                                    for (int o = 16; o; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+                                    if (lane == 0 && p != 0.0f) {
+                                        const int other = cr < cl ? cr : cr + 1;
+                                        const int k = other > cl ? pair_index(pa.n_classes, cl, other)
+                                                                 : pair_index(pa.n_classes, other, cl);
+                                        atomicAdd(pa.dec + (size_t) r * pa.n_pairs + k, (double) p);
+                                    }
+                                }
+                        }
+                        asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");   // staging block is reused
                     }
                 }
                 __syncwarp();          // the next item's copies overwrite rowc
+                if constexpr (PREDICT) asm volatile("bar.sync 3, 256;" ::: "memory");   // ... and the coefficient table
             }
         }
     }
@@ -308,10 +412,11 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
 tsvm_status make_map(CUtensorMap *map, const void *ptr, int rows, int row_len, long long ld, int box_rows,
                      bool f16);   // dense_tc.cu
 
-template <int EPI, bool F16>
+template <int EPI, bool F16, bool PREDICT>
 static tsvm_status launch_pair_kernel(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int m, float *out,
-                                      long long ld_out, cudaStream_t st) {
-    auto kernel = dense_rows_tc2_kernel<EPI, F16>;
+                                      long long ld_out, const PredictArgs &pa, cudaStream_t st) {
+    auto kernel = dense_rows_tc2_kernel<EPI, F16, PREDICT>;
+    constexpr uint32_t smem_bytes = PREDICT ? tc2::SMEM_BYTES_PREDICT : tc2::SMEM_BYTES;
     static int clusters_of_device[MAX_DEVICES] = {0};      // per instantiation and per device ordinal
     int dev = 0;
     TSVM_CUDA(cudaGetDevice(&dev));
@@ -319,12 +424,12 @@ static tsvm_status launch_pair_kernel(tsvm_km *km, const InstancePlanes &X, cons
     if (!max_clusters) {
         int sms = 0;
         TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        TSVM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) tc2::SMEM_BYTES));
+        TSVM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes));
         cudaLaunchConfig_t probe = {};
         cudaLaunchAttribute pattr[1];
         pattr[0].id = cudaLaunchAttributeClusterDimension;
         pattr[0].val.clusterDim.x = 2; pattr[0].val.clusterDim.y = 1; pattr[0].val.clusterDim.z = 1;
-        probe.gridDim = dim3(sms & ~1); probe.blockDim = dim3(tc2::THREADS); probe.dynamicSmemBytes = tc2::SMEM_BYTES;
+        probe.gridDim = dim3(sms & ~1); probe.blockDim = dim3(tc2::THREADS); probe.dynamicSmemBytes = smem_bytes;
         probe.attrs = pattr; probe.numAttrs = 1;
         int nc = 0;
         if (cudaOccupancyMaxActiveClusters(&nc, kernel, &probe) != cudaSuccess || nc < 1) {
@@ -347,28 +452,44 @@ static tsvm_status launch_pair_kernel(tsvm_km *km, const InstancePlanes &X, cons
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(tc2::THREADS); cfg.dynamicSmemBytes = tc2::SMEM_BYTES;
+    cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(tc2::THREADS); cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
     TSVM_CUDA(cudaLaunchKernelEx(&cfg, kernel, mxh, mxl, mwh, mwl, X.n, m, len, X.sd, W.sd, X.unscale, W.unscale,
-                                 km->fn, out, ld_out, km->status_dev));
+                                 km->fn, out, ld_out, km->status_dev, pa));
     count_launch();
     return TSVM_OK;
+}
+
+template <bool PREDICT>
+static tsvm_status launch_pair_any(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int m, float *out,
+                                   long long ld_out, const PredictArgs &pa, cudaStream_t st) {
+    TSVM_REQUIRE(km->plane_kind == 1 || km->plane_kind == 2, "tensor engine: operand planes are not built");
+    const int epi = epilogue_kind(km->fn);
+    if (km->plane_kind == 2) {
+        if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, true, PREDICT>(km, X, W, m, out, ld_out, pa, st);
+        if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, true, PREDICT>(km, X, W, m, out, ld_out, pa, st);
+        return launch_pair_kernel<EPI_GENERIC, true, PREDICT>(km, X, W, m, out, ld_out, pa, st);
+    }
+    if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, false, PREDICT>(km, X, W, m, out, ld_out, pa, st);
+    if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, false, PREDICT>(km, X, W, m, out, ld_out, pa, st);
+    return launch_pair_kernel<EPI_GENERIC, false, PREDICT>(km, X, W, m, out, ld_out, pa, st);
 }
 
 // Kernel values of the m staged requested rows against a set of instances given by its operand planes
 // (kind 1 = TF32 words, 2 = row-scaled FP16, the handle's plane kind), self dots and 1/scale.
 tsvm_status launch_dense_tc2_planes(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int m, float *out,
                                     long long ld_out, cudaStream_t st) {
-    TSVM_REQUIRE(km->plane_kind == 1 || km->plane_kind == 2, "tensor engine: operand planes are not built");
-    const int epi = epilogue_kind(km->fn);
-    if (km->plane_kind == 2) {
-        if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, true>(km, X, W, m, out, ld_out, st);
-        if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, true>(km, X, W, m, out, ld_out, st);
-        return launch_pair_kernel<EPI_GENERIC, true>(km, X, W, m, out, ld_out, st);
-    }
-    if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, false>(km, X, W, m, out, ld_out, st);
-    if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, false>(km, X, W, m, out, ld_out, st);
-    return launch_pair_kernel<EPI_GENERIC, false>(km, X, W, m, out, ld_out, st);
+    return launch_pair_any<false>(km, X, W, m, out, ld_out, PredictArgs{}, st);
+}
+
+// Prediction form: the m staged rows are test rows, the kernel matrix holds the support vectors; adds
+// sum_sv coef * K(sv, test row) to dec_dev[r * n_pairs + pair] (preset by the caller) without writing K.
+tsvm_status launch_dense_tc2_predict(tsvm_km *km, int m, const double *coef_dev, const int *sv_class_dev,
+                                     int n_classes, double *dec_dev, cudaStream_t st) {
+    const InstancePlanes all{km->Xhi, km->Xlo, km->self_dot, km->x_unscale, km->n};
+    const RowPlanes staged{km->Whi, km->Wlo, km->sd_rows, km->w_unscale};
+    const PredictArgs pa{coef_dev, sv_class_dev, dec_dev, n_classes, n_classes * (n_classes - 1) / 2};
+    return launch_pair_any<true>(km, all, staged, m, nullptr, 0, pa, st);
 }
 
 // Requested rows = the m rows staged in the handle's scratch.

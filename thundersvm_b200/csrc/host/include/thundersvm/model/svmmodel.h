@@ -6,6 +6,7 @@
 #include <thundersvm/dataset.h>
 #include <thundersvm/svmparam.h>
 #include <thundersvm/kernelmatrix.h>
+#include <memory>
 
 class SvmModel {
 public:
@@ -45,6 +46,10 @@ public:
 protected:
     virtual void model_setup(const DataSet &dataset, SvmParam &param);
     int get_working_set_size(int n_instances, int n_features);
+    /// Kernel matrix of the support vectors, built on the first prediction and kept until the support vectors
+    /// change (the reference rebuilds it on every predict call, svmmodel.cpp:84).
+    const KernelMatrix &sv_matrix() const;
+    void invalidate_sv_matrix() { sv_kmat_.reset(); }
 
     SvmParam param;
     SyncArray<float_type> coef;
@@ -62,5 +67,6 @@ protected:
     SyncArray<float_type> dec_values;
     vector<float> prob_predict;
     int sv_max_index = 0;
+    mutable std::unique_ptr<KernelMatrix> sv_kmat_;
 };
 #endif

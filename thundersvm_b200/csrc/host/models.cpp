@@ -53,7 +53,13 @@ void SvmModel::model_setup(const DataSet &dataset, SvmParam &param) {
     n_sv.resize(n_classes);
     sv.clear();
     sv_indices.clear();
+    invalidate_sv_matrix();
     this->param = param;
+}
+
+const KernelMatrix &SvmModel::sv_matrix() const {
+    if (!sv_kmat_ || sv_kmat_->n_instances() != sv.size()) sv_kmat_.reset(new KernelMatrix(sv, param));
+    return *sv_kmat_;
 }
 
 int SvmModel::get_working_set_size(int n_instances, int n_features) {
@@ -92,7 +98,7 @@ void SvmModel::predict_dec_values(const DataSet::node2d &instances, SyncArray<fl
             for (size_t k = 0; k < n_binary_models; ++k) d[r * n_binary_models + k] = -rho.host_data()[k];
         return;
     }
-    KernelMatrix k_mat(sv, param);          // rebuilt on every call, as in the reference (svmmodel.cpp:84)
+    const KernelMatrix &k_mat = sv_matrix();
     // test batch as CSR on the device
     size_t nnz = 0;
     for (auto &r : instances) nnz += r.size();
@@ -115,16 +121,54 @@ void SvmModel::predict_dec_values(const DataSet::node2d &instances, SyncArray<fl
                                 (long long) nnz, dec_values.device_data(), budget, nullptr));
 }
 
+// Test batch as CSR arrays on the device.
+struct DeviceBatch {
+    SyncArray<kernel_type> val;
+    SyncArray<int> col, row_ptr;
+    size_t nnz = 0;
+    explicit DeviceBatch(const DataSet::node2d &instances) {
+        for (auto &r : instances) nnz += r.size();
+        val.resize(std::max<size_t>(nnz, 1));
+        col.resize(std::max<size_t>(nnz, 1));
+        row_ptr.resize(instances.size() + 1);
+        kernel_type *v = val.host_data();
+        int *c = col.host_data(), *rp = row_ptr.host_data();
+        size_t p = 0;
+        rp[0] = 0;
+        for (size_t r = 0; r < instances.size(); ++r) {
+            for (auto &nd : instances[r]) { v[p] = nd.value; c[p] = nd.index; ++p; }
+            rp[r + 1] = (int) p;
+        }
+    }
+};
+
 void SvmModel::predict_dec_values_instant(const DataSet::node2d &instances, SyncArray<float_type> &predict_instant,
                                           int batch_size) const {
-    // decision values + on-device vote (the reference's variant for > 10000 binary models)
+    // svmmodel.cpp:119-154 + sum_kernel_values_instant: only the winning class index of every row leaves the
+    // device; the decision values live in a slab-sized scratch inside tsvm_predict_labels
     const size_t m = instances.size();
-    SyncArray<float_type> dec(m * n_binary_models);
-    predict_dec_values(instances, dec, batch_size);
-    SyncArray<int> winner(m);
-    b200_check(tsvm_vote(dec.device_data(), (int) m, n_classes, winner.device_data(), nullptr));
-    const int *w = winner.host_data();
+    if (m == 0) return;
     float_type *out = predict_instant.host_data();
+    if (sv.empty()) {                       // every decision value is -rho: the vote is the same for all rows
+        for (size_t r = 0; r < m; ++r) {
+            vector<int> votes(n_classes, 0);
+            size_t k = 0;
+            for (int i = 0; i < n_classes; ++i)
+                for (int j = i + 1; j < n_classes; ++j, ++k) votes[-rho.host_data()[k] > 0 ? i : j]++;
+            out[r] = (float_type) (std::max_element(votes.begin(), votes.end()) - votes.begin());
+        }
+        return;
+    }
+    const KernelMatrix &k_mat = sv_matrix();
+    DeviceBatch batch(instances);
+    size_t budget = 0;
+    if (batch_size > 0) budget = (size_t) batch_size * (((size_t) sv.size() + 3) & ~3ul) * sizeof(kernel_type);
+    SyncArray<int> winner(m);
+    b200_check(tsvm_predict_labels(k_mat.handle(), coef.device_data(), n_sv.host_data(), rho.device_data(), n_classes,
+                                   (int) m, nullptr, 0, 0, batch.val.device_data(), batch.row_ptr.device_data(),
+                                   batch.col.device_data(), (long long) batch.nnz, winner.device_data(), budget,
+                                   nullptr));
+    const int *w = winner.host_data();
     for (size_t r = 0; r < m; ++r) out[r] = w[r];
 }
 
@@ -240,6 +284,7 @@ void SvmModel::load_from_string(string data) {
             if (!w.empty()) linear_coef.copy_from(w.data(), w.size());
         } else if (key == "SV") {
             sv.clear();
+            invalidate_sv_matrix();
             coef.resize((size_t) (n_classes - 1) * n_total_sv);
             float_type *cf = coef.host_data();
             string line;

@@ -711,6 +711,32 @@ tsvm_status km_stage_rows_features(tsvm_km *km, const float *T_dev, int ldt, con
     return TSVM_OK;
 }
 
+// Stages mm new instances as the requested rows of a dense kernel matrix (self dots accumulated in storage
+// order as kernelmatrix.cpp:288-296 does, rows in the engine's operand form): the first half of
+// tsvm_km_rows_by_instances_*, shared with the fused prediction.
+tsvm_status km_stage_instances_dense(tsvm_km *km, const float *T, int mm, int dt, int ldt, cudaStream_t st) {
+    TSVM_TRY(ensure_scratch(km, mm));
+    TSVM_LAUNCH(self_dot_seq_dense_kernel, ceil_div(mm, 128), 128, 0, st, T, mm, dt, ldt, km->sd_rows);
+    TSVM_TRY(ensure_planes(km, st));
+    TSVM_LAUNCH(stage_rows_dense_kernel, mm, 256, 0, st, T, ldt, dt, km->d, mm, row_dst(km));
+    return TSVM_OK;
+}
+
+tsvm_status km_stage_instances_csr(tsvm_km *km, const float *tval, const int *rp, const int *tcol, int mm,
+                                   cudaStream_t st) {
+    TSVM_TRY(ensure_scratch(km, mm));
+    TSVM_LAUNCH(self_dot_seq_csr_kernel, ceil_div(mm, 128), 128, 0, st, tval, rp, mm, km->sd_rows);
+    TSVM_TRY(ensure_planes(km, st));
+    const RowDst dst = row_dst(km);
+    if (dst.W) TSVM_CUDA(cudaMemsetAsync(dst.W, 0, row_dst_bytes(dst, mm), st));
+    else {
+        TSVM_CUDA(cudaMemsetAsync(dst.hi, 0, row_dst_bytes(dst, mm), st));
+        TSVM_CUDA(cudaMemsetAsync(dst.lo, 0, row_dst_bytes(dst, mm), st));
+    }
+    TSVM_LAUNCH(scatter_csr_to_w_kernel, mm, 128, 0, st, tval, rp, tcol, (const int *) nullptr, mm, km->d, dst);
+    return TSVM_OK;
+}
+
 }  // namespace tsvm
 
 using namespace tsvm;
@@ -842,13 +868,12 @@ tsvm_status tsvm_km_rows_by_instances_dense(tsvm_km *km, const float *T_dev, int
         const int mm = min(chunk, m - r0);
         const float *T = T_dev + (size_t) r0 * ldt;
         float *o = out_dev + (size_t) r0 * ld_out;
-        TSVM_TRY(ensure_scratch(km, mm));
-        TSVM_LAUNCH(self_dot_seq_dense_kernel, ceil_div(mm, 128), 128, 0, st, T, mm, dt, ldt, km->sd_rows);
         if (km->dense) {
-            TSVM_TRY(ensure_planes(km, st));
-            TSVM_LAUNCH(stage_rows_dense_kernel, mm, 256, 0, st, T, ldt, dt, km->d, mm, row_dst(km));
+            TSVM_TRY(km_stage_instances_dense(km, T, mm, dt, ldt, st));
             TSVM_TRY(rows_common(km, mm, o, ld_out, st));
         } else {
+            TSVM_TRY(ensure_scratch(km, mm));
+            TSVM_LAUNCH(self_dot_seq_dense_kernel, ceil_div(mm, 128), 128, 0, st, T, mm, dt, ldt, km->sd_rows);
             dim3 grid(ceil_div(km->d, 32), ceil_div(mm, 32)), block(32, 8);
             TSVM_LAUNCH(transpose_dense_to_wt_kernel, grid, block, 0, st, T, ldt, dt, km->d, mm, km->wt_ld, km->WT,
                         false);
@@ -888,20 +913,12 @@ tsvm_status tsvm_km_rows_by_instances_csr(tsvm_km *km, const float *tval_dev, co
         const int mm = min(chunk, m - r0);
         const int *rp = trow_ptr_dev + r0;     // row_ptr entries stay absolute offsets into tval/tcol
         float *o = out_dev + (size_t) r0 * ld_out;
-        TSVM_TRY(ensure_scratch(km, mm));
-        TSVM_LAUNCH(self_dot_seq_csr_kernel, ceil_div(mm, 128), 128, 0, st, tval_dev, rp, mm, km->sd_rows);
         if (km->dense) {
-            TSVM_TRY(ensure_planes(km, st));
-            const RowDst dst = row_dst(km);
-            if (dst.W) TSVM_CUDA(cudaMemsetAsync(dst.W, 0, row_dst_bytes(dst, mm), st));
-            else {
-                TSVM_CUDA(cudaMemsetAsync(dst.hi, 0, row_dst_bytes(dst, mm), st));
-                TSVM_CUDA(cudaMemsetAsync(dst.lo, 0, row_dst_bytes(dst, mm), st));
-            }
-            TSVM_LAUNCH(scatter_csr_to_w_kernel, mm, 128, 0, st, tval_dev, rp, tcol_dev, (const int *) nullptr, mm,
-                        km->d, dst);
+            TSVM_TRY(km_stage_instances_csr(km, tval_dev, rp, tcol_dev, mm, st));
             TSVM_TRY(rows_common(km, mm, o, ld_out, st));
         } else {
+            TSVM_TRY(ensure_scratch(km, mm));
+            TSVM_LAUNCH(self_dot_seq_csr_kernel, ceil_div(mm, 128), 128, 0, st, tval_dev, rp, mm, km->sd_rows);
             TSVM_LAUNCH(scatter_csr_to_wt_kernel, mm, 128, 0, st, tval_dev, rp, tcol_dev, (const int *) nullptr, mm,
                         km->d, km->wt_ld, km->WT, (const float *) nullptr, (float *) nullptr, false);
             TSVM_TRY(rows_common(km, mm, o, ld_out, st));
