@@ -6,16 +6,19 @@
 A "step" is one outer iteration of the batched SMO solver: working-set selection over all
 instances, 512 new kernel rows of length n, the local solver on the 1024-wide working set and the
 f update. The metric is kernel rows per second (rows of length n = 400,000):
-  value : K timed steps with the data already resident in HBM (CUDA events, max over ranks)
-  e2e   : the same K-step job through the C ABI starting from pinned HOST buffers - the
+  value : K timed steps with the data already resident in HBM (CUDA events, max over ranks); the
+          window is repeated `--windows` times and the median window is reported
+  e2e   : a (W+K)-step job through the C ABI starting from pinned HOST buffers - the
           host->device copy of X / y / alpha / f, the operand-plane split, the solver set-up and the
           device->host read of alpha / f / rho are inside the timed region
-plus, when --full-train is on (default at N=1), the whole training run to eps = 1e-3.
+plus the whole training run to eps = 1e-3, the prediction of the 100,000 test rows, the HBM-bound
+kernels one by one (`rooflines`), and the four smaller configurations end to end (`configs`).
 `--impl reference` times the reference's own CPU implementation (oracle/_ref, built from the
-reference sources) or, if that library is absent, the C restatement, on a bounded sample.
-Prints exactly one JSON line on rank 0.
+reference sources with the Eigen products restated) or, if that library is absent, the C
+restatement, on a bounded sample. Prints exactly one JSON line on rank 0.
 """
 import argparse
+import hashlib
 import json
 import os
 import subprocess
@@ -31,6 +34,10 @@ sys.path.insert(0, ROOT)
 N_FULL, D_FULL, WS, Q = 400000, 2000, 1024, 512
 GAMMA, C_SVC, EPS = 0.5, 1.0, 1e-3
 TRAFFIC_37888 = 388.7e6   # dram read + write bytes of one 37,888-instance launch of the kernel (ncu capture summarised in profiles/)
+WORKLOAD = ("config5: binary C-SVC, RBF gamma=0.5 C=1 eps=1e-3, %dx%d dense fp32, ws=1024, 512 new kernel rows per "
+            "outer iteration")
+NO_CPU_CONVERGENCE = ("the CPU build cannot converge this configuration in bounded time (26,042 s published for the "
+                      "same shape on 20 cores); configs c1, c2, c4 carry train-to-eps seconds of both sides")
 
 
 def parse():
@@ -38,45 +45,113 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--windows", type=int, default=5, help="timed windows of --steps steps each; the median is reported")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=N_FULL, help="instances (default: the full configuration)")
-    ap.add_argument("--full-train", type=int, default=-1, help="1/0: also train to eps (default: on for 1 GPU)")
+    ap.add_argument("--full-train", type=int, default=-1, help="1/0: also train to eps (default: on)")
     ap.add_argument("--train-budget-s", type=float, default=150.0)
     ap.add_argument("--cpu-sample-rows", type=int, default=20000)
     ap.add_argument("--cpu-sample-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--predict-rows", type=int, default=100000, help="test rows of the prediction measurement (0: skip)")
+    ap.add_argument("--configs", default="c1,c2,c3,c4", help="smaller configurations measured end to end ('' = none)")
+    ap.add_argument("--cpu-configs", default="c1,c2,c4",
+                    help="configurations the CPU reference also trains to convergence (c3 takes minutes)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-kernel rooflines and the smaller configurations")
     return ap.parse_args()
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 # ----------------------------------------------------------------------------------------------
 # CPU arms (reference build or restatement) on a bounded sample of the same workload
 # ----------------------------------------------------------------------------------------------
+def cpu_backend():
+    """-> (module, kind, cores). The launcher of multi-rank runs exports OMP_NUM_THREADS=1; the CPU arm uses
+    every host thread it may run on, set explicitly."""
+    cores = host_threads()
+    from oracle import ref_binding as R
+    if R.available():
+        R.lib().ref_set_threads(cores)
+        return R, "reference+eigenfree", int(R.lib().ref_max_threads())
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    from oracle import port_binding as P
+    return P, "port", cores
+
+
 def cpu_sample(rows, steps):
     """Times `steps` outer iterations of the reference CPU solver on the first `rows` instances of
     the workload. -> dict(value=rows/s in full-length-row equivalents, ...)."""
     from thundersvm_b200 import synth
-    from oracle import ref_binding as R
+    B, kind, cores = cpu_backend()
     prob = synth.config5(rows)
     y = np.where(prob["y"] > 0, 1, -1).astype(np.int32)
     a0, f0 = np.zeros(rows), -y.astype(np.float64)
-    if R.available():
-        kind, cores = "reference", R.lib().ref_max_threads()
-        D = R.Data(dense=prob["X"])
-        _, _, _, sec = R.smo_solve(D, y, a0, f0, EPS, C_SVC, C_SVC, WS, max_iter=steps - 1, gamma=GAMMA)
+    if kind != "port":
+        D = B.Data(dense=prob["X"])
+        _, _, _, sec = B.smo_solve(D, y, a0, f0, EPS, C_SVC, C_SVC, WS, max_iter=steps - 1, gamma=GAMMA)
     else:
-        from oracle import port_binding as P
-        kind, cores = "port", os.cpu_count()
-        X = P.Csr(dense=prob["X"])
+        X = B.Csr(dense=prob["X"])
         t0 = time.perf_counter()
-        P.smo_solve(X, y, a0, f0, EPS, C_SVC, C_SVC, WS, max_iter=steps - 1, gamma=GAMMA)
+        B.smo_solve(X, y, a0, f0, EPS, C_SVC, C_SVC, WS, max_iter=steps - 1, gamma=GAMMA)
         sec = time.perf_counter() - t0
     rows_made = WS + Q * (steps - 1)
     # a row of the sample is rows/N_FULL of a full-length row
     value = rows_made / sec * (rows / N_FULL)
     return dict(value=value, unit="rows/s", cores=int(cores), kind=kind, seconds=sec, ms_per_step=sec / steps * 1e3,
+                build="reference CPU sources compiled -O3 -march=x86-64-v3 -fopenmp; its three Eigen products "
+                      "restated as plain loops (Eigen is not on the machine)" if kind != "port" else
+                      "C restatement of the reference algorithm, -O3 -march=x86-64-v3 -fopenmp",
                 sample="first %d of %d instances, %d outer iterations (%d kernel rows of length %d), scaled by "
                        "%d/%d to full-length rows" % (rows, N_FULL, steps, rows_made, rows, rows, N_FULL))
+
+
+def cpu_kernel_rows(rows, ids):
+    """Reference kernel rows K(x_ids, x_j), j < rows, of the workload's first `rows` instances (parity sample)."""
+    from thundersvm_b200 import synth
+    B, kind, _ = cpu_backend()
+    prob = synth.config5(rows)
+    if kind != "port":
+        out, _, _ = B.kernel_rows_idx(B.Data(dense=prob["X"]), ids, gamma=GAMMA)
+        return out
+    return B.kernel_rows_idx(B.Csr(dense=prob["X"]), ids, gamma=GAMMA)
+
+
+def cpu_train_config(tag):
+    """The CPU reference trained to convergence on one of the smaller configurations -> dict."""
+    from thundersvm_b200 import synth
+    B, kind, cores = cpu_backend()
+    if tag == "c3":
+        if kind == "port":
+            return None
+        prob = synth.config3()
+        m = B.Model("c_svc", B.Data(dense=prob["X"]), prob["y"], gamma=prob["gamma"], C_=prob["C"], eps=prob["eps"])
+        out = dict(train_seconds=m.train_seconds, total_sv=int(m.total_sv), cores=cores, kind=kind)
+        m.close()
+        return out
+    prob = {"c1": synth.config1, "c2": synth.config2, "c4": synth.config4}[tag]()
+    y = np.where(prob["y"] > 0, 1, -1).astype(np.int32)
+    n = len(y)
+    if kind != "port":
+        D = B.Data(dense=prob["X"]) if "X" in prob else B.Data(csr=prob["csr"], d=prob["d"])
+        t0 = time.perf_counter()
+        a, f, rho, _ = B.smo_solve(D, y, np.zeros(n), -y.astype(np.float64), prob["eps"], prob["C"], prob["C"], WS,
+                                   gamma=prob["gamma"])
+        sec = time.perf_counter() - t0
+    else:
+        X = B.Csr(dense=prob["X"]) if "X" in prob else B.Csr(csr=prob["csr"], d=prob["d"])
+        t0 = time.perf_counter()
+        r = B.smo_solve(X, y, np.zeros(n), -y.astype(np.float64), prob["eps"], prob["C"], prob["C"], WS,
+                        gamma=prob["gamma"])
+        sec = time.perf_counter() - t0
+        a, f, rho = r["alpha"], r["f"], r["rho"]
+    return dict(train_seconds=sec, objective=-float(np.sum(a - (f + y) * a * y / 2)), rho=float(rho),
+                n_sv=int((a != 0).sum()), cores=cores, kind=kind)
 
 
 def run_reference_arm(args):
@@ -89,9 +164,8 @@ def run_reference_arm(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": s["ms_per_step"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 kernel values, f64 solver",
         "data": "synthetic",
-        "config": {"workload": "config5: binary C-SVC, RBF gamma=0.5 C=1 eps=1e-3, 400000x2000 dense fp32, ws=1024, "
-                               "512 new kernel rows per outer iteration", "l2": "inputs larger than L2"},
-        "cpu_baseline": {k: s[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "config": {"workload": WORKLOAD % (N_FULL, D_FULL), "l2": "inputs larger than L2"},
+        "cpu_baseline": {k: s[k] for k in ("value", "unit", "cores", "kind", "sample", "build")},
         "e2e": {"value": s["value"], "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -102,7 +176,7 @@ def run_reference_arm(args):
 # B200 arm
 # ----------------------------------------------------------------------------------------------
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons during the timed region."""
+    """nvidia-smi clocks / throttle reasons during the timed region (started well before it)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -110,21 +184,29 @@ class ClockSampler:
     def __init__(self, gpu_index):
         self.idx, self.proc, self.path = gpu_index, None, None
 
-    def start(self):
+    def start(self, settle_s=0.6):
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            time.sleep(settle_s)          # the sampler's start-up must not fall into the timed window
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def mark(self):
+        """Number of samples written so far (samples taken before the window are left out of the summary)."""
+        try:
+            return sum(1 for _ in open(self.path))
+        except Exception:
+            return 0
+
+    def stop(self, skip=0):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
-        time.sleep(0.15)
+        time.sleep(0.12)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -132,7 +214,9 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         try:
-            for line in open(self.path):
+            for k, line in enumerate(open(self.path)):
+                if k < skip:
+                    continue
                 t = [x.strip() for x in line.split(",")]
                 if len(t) < 9:
                     continue
@@ -170,14 +254,162 @@ def measure_f16_peak(torch):
 
 
 def measured_peaks():
-    """(burst, sustained, source) dense 16-bit tensor TFLOP/s: the driver-written file at the repo root,
-    else the pool's earlier measurement."""
+    """(burst TF/s, sustained TF/s, HBM GB/s, source): the driver-written file at the repo root, else the pool's
+    earlier measurement."""
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
             m = json.load(fh)
-        return float(m["bf16_tflops"]), float(m["bf16_tflops_sustained"]), "of measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+        return (float(m["bf16_tflops"]), float(m["bf16_tflops_sustained"]), float(m["hbm_gbs"]),
+                "of measured (MEASURED_PEAKS.json)")
     except Exception:
-        return 1590.0, 1400.0, "of fallback (1.59 PFLOP/s burst)"
+        return 1590.0, 1400.0, 6650.0, "of fallback (1.59 PFLOP/s burst, 6.65 TB/s)"
+
+
+def sha(t):
+    return hashlib.sha256(np.ascontiguousarray(t).tobytes()).hexdigest()[:16]
+
+
+def timed_windows(torch, run_window, windows, barrier=None):
+    """-> list of ms, one per window; run_window() runs exactly K steps and returns False when nothing is left."""
+    out = []
+    for _ in range(windows):
+        if barrier:
+            barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        alive = run_window()
+        e1.record()
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        out.append(e0.elapsed_time(e1))
+        if not alive:
+            break
+    return out
+
+
+def hbm_roofline(name, bytes_per_call, us, hbm_peak, peak_src, note):
+    gbs = bytes_per_call / (us * 1e-6) / 1e9
+    return {"kernel": name, "bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+            "algorithmic_bytes": bytes_per_call, "us_per_call": us, "peak_source": peak_src, "note": note}
+
+
+def time_calls(torch, fn, reps, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps        # us per call
+
+
+def extra_rooflines(torch, capi, synth, hbm_peak, peak_src, n):
+    """The HBM-bound kernels one by one, CUDA events over many calls: f update, working-set selection, CSR rows."""
+    out = []
+    # f update: all 1024 rows carry a non-zero alpha_diff (the byte formula's upper case)
+    rows = torch.rand((WS, n), dtype=torch.float32, device="cuda")
+    f = torch.zeros(n, dtype=torch.float64, device="cuda")
+    ad = torch.rand(WS, dtype=torch.float64, device="cuda") + 0.5
+    us = time_calls(torch, lambda: capi.update_f(f, ad, rows), 20)
+    out.append(hbm_roofline("update_f_kernel (config 5: 1024 rows x %d)" % n, WS * n * 4 + 16 * n, us, hbm_peak, peak_src,
+                            "bytes = ws_nz*n*4 + 2*n*8, every row non-zero"))
+    del rows
+    # selection of 512 new members out of n
+    yv = torch.where(torch.rand(n, device="cuda") < 0.5, 1, -1).to(torch.int32)
+    fv = torch.randn(n, dtype=torch.float64, device="cuda")
+    av = torch.where(torch.rand(n, device="cuda") < 0.3, 1.0, 0.0).to(torch.float64) * torch.rand(n, device="cuda").to(torch.float64)
+    flags = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    sel = capi.WorkingSetSelector(n, WS)
+    us = time_calls(torch, lambda: sel.select(fv, av, yv, 1.0, 1.0, Q, in_ws=flags), 50)
+    out.append(hbm_roofline("working-set selection (radix top-k + merge, config 5: 512 of %d)" % n, n * 21, us, hbm_peak,
+                            peak_src, "bytes = n*(8 f + 8 alpha + 4 y + 1 flag) read once; the selection is several "
+                                      "short launches, so this is launch-latency-bound, not bandwidth-bound"))
+    sel.close()
+    del yv, fv, av, flags, f
+    # CSR kernel rows, 512 rows per call
+    for tag, make in (("c2", synth.config2), ("c4", synth.config4)):
+        prob = make()
+        val, rp, col = prob["csr"]
+        km = capi.KernelMatrix(csr=(torch.from_numpy(val).cuda(), torch.from_numpy(rp).cuda(),
+                                    torch.from_numpy(col).cuda()), d=prob["d"], gamma=prob["gamma"])
+        nn = km.n
+        idx_np = np.random.default_rng(0).choice(nn, Q, replace=False).astype(np.int32)
+        idx = torch.from_numpy(idx_np).cuda()
+        buf = torch.empty((Q, nn), dtype=torch.float32, device="cuda")
+        us = time_calls(torch, lambda: km.get_rows(idx, buf), 100)
+        nnz, nnz_ws = int(rp[-1]), int(np.diff(rp)[idx_np].sum())
+        r = hbm_roofline("CSR kernel rows (%s: 512 rows x %d, nnz %d)" % (tag, nn, nnz),
+                         Q * nn * 4 + nnz * 8 + (nn + 1) * 4 + nnz_ws * 8, us, hbm_peak, peak_src,
+                         "bytes = q*n*4 out + nnz*8 + (n+1)*4 CSR read once + nnz(requested rows)*8")
+        r["kernel_rows_per_s"] = Q / (us * 1e-6)
+        out.append(r)
+        km.close()
+        del buf
+    return out
+
+
+def small_configs(torch, capi, synth, which, cpu_which):
+    """Configurations 1-4 end to end through the C ABI from host arrays (upload inside the timed region), and the
+    CPU reference trained to convergence beside them."""
+    from thundersvm_b200 import sharded
+    out = {}
+    for tag in which:
+        if tag == "c3":
+            prob = synth.config3()
+            ops = sharded.CapiOps()
+            Xh = torch.from_numpy(prob["X"]).pin_memory()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            X = Xh.cuda(non_blocking=True)
+            model = sharded.train_ovo(ops, X, prob["y"].astype(np.int64), prob["C"], prob["eps"], gamma=prob["gamma"])
+            torch.cuda.synchronize()
+            sec = time.perf_counter() - t0
+            test = synth.config3(10000, seed=5)
+            Th = torch.from_numpy(test["X"]).pin_memory()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            lab = sharded.predict_ovo(ops, model, X, Th.cuda(non_blocking=True), gamma=prob["gamma"]).cpu().numpy()
+            sec_p = time.perf_counter() - t0
+            out[tag] = {"workload": "10-class one-vs-one C-SVC, 60000x784 dense, 45 binary problems", "train_seconds": sec,
+                        "total_sv": int(sum(model["n_sv"])), "predict_rows": 10000, "predict_rows_per_s": 10000 / sec_p,
+                        "test_accuracy": float((lab == test["y"]).mean())}
+            del X
+        else:
+            prob = {"c1": synth.config1, "c2": synth.config2, "c4": synth.config4}[tag]()
+            y_np = np.where(prob["y"] > 0, 1, -1).astype(np.int32)
+            n = len(y_np)
+            best = None
+            for _ in range(2):                      # the second run has the library's memory pool warm
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                if "X" in prob:
+                    km = capi.KernelMatrix(dense=prob["X"], gamma=prob["gamma"])
+                else:
+                    km = capi.KernelMatrix(csr=prob["csr"], d=prob["d"], gamma=prob["gamma"])
+                y = torch.from_numpy(y_np).cuda()
+                a = torch.zeros(n, dtype=torch.float64, device="cuda")
+                f = -y.to(torch.float64)
+                rho, st = capi.smo_solve(km, y, a, f, prob["eps"], prob["C"], prob["C"], WS)
+                a_h = a.cpu()
+                torch.cuda.synchronize()
+                sec = time.perf_counter() - t0
+                km.close()
+                if best is None or sec < best["train_seconds"]:
+                    best = {"workload": prob["name"], "train_seconds": sec, "objective": st["objective"], "rho": rho,
+                            "n_sv": int((a_h != 0).sum()), "outer_iters": st["outer_iters"],
+                            "local_iters": st["local_iters"], "kernel_rows_per_s": st["kernel_rows"] / max(st["seconds_rows"], 1e-9)}
+            out[tag] = best
+        if tag in cpu_which:
+            try:
+                out[tag]["cpu_reference"] = cpu_train_config(tag)
+            except Exception as exc:
+                out[tag]["cpu_reference"] = {"failed": repr(exc)}
+    return out
 
 
 def run_b200_arm(args):
@@ -221,36 +453,42 @@ def run_b200_arm(args):
     ah = torch.zeros(n, dtype=torch.float64).pin_memory()
 
     f16_peak_in_run = measure_f16_peak(torch)
-    peak, peak_sustained, peak_src = measured_peaks()
+    peak, peak_sustained, hbm_peak, peak_src = measured_peaks()
 
-    # ---- (1) resident: K timed steps ------------------------------------------------------------
+    # ---- (1) resident: W warm-up steps, then `windows` windows of exactly K timed steps ----------------
     Xd = Xh.cuda(non_blocking=True)
     yd, fd, ad = yh.cuda(), fh.cuda(), ah.cuda()
     km = capi.KernelMatrix(dense=Xd, gamma=GAMMA)
     solver = capi.Solver(km, yd, ad, fd, EPS, C_SVC, C_SVC, WS)
-    solver.iterate(W)
-    torch.cuda.synchronize()
-    s0 = solver.stats()
     clocks = ClockSampler(local_rank)
     clocks.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    solver.iterate(W)
     torch.cuda.synchronize()
-    e0.record()
-    solver.iterate(K)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    clk = clocks.stop()
-    s1 = solver.stats()
+    skip = clocks.mark()
+    stats = [solver.stats()]
+
+    def window():
+        done = solver.iterate(K)
+        stats.append(solver.stats())
+        return not done and stats[-1]["outer_iters"] - stats[-2]["outer_iters"] == K
+
+    win_ms = timed_windows(torch, window, max(1, args.windows))
+    clk = clocks.stop(skip)
+    full = [i for i in range(len(win_ms)) if stats[i + 1]["outer_iters"] - stats[i]["outer_iters"] == K]
+    pick = sorted(full, key=lambda i: win_ms[i])[len(full) // 2] if full else 0
+    s0, s1 = stats[pick], stats[pick + 1]
+    ms = win_ms[pick]
     steps_done = s1["outer_iters"] - s0["outer_iters"]
     rows_timed = s1["kernel_rows"] - s0["kernel_rows"]
     ms_per_step = ms / max(1, steps_done)
     value = rows_timed / (ms * 1e-3)
     launches = s1["gpu_launches"] - s0["gpu_launches"]
-    t_rows = (s1["seconds_rows"] - s0["seconds_rows"]) / max(1, steps_done)
-    phases = {k: (s1["seconds_" + k] - s0["seconds_" + k]) / max(1, steps_done) * 1e3
-              for k in ("select", "rows", "local", "update")}
-    flops = 2.0 * Q * n * d
+    sa, sb = stats[0], stats[-1]                                   # phase means over all windows
+    all_steps = max(1, sb["outer_iters"] - sa["outer_iters"])
+    t_rows = (sb["seconds_rows"] - sa["seconds_rows"]) / all_steps
+    phases = {k: (sb["seconds_" + k] - sa["seconds_" + k]) / all_steps * 1e3 for k in ("select", "rows", "local", "update")}
+    rows_per_launch = (sb["kernel_rows"] - sa["kernel_rows"]) / all_steps
+    flops = 2.0 * rows_per_launch * n * d
     achieved = flops / t_rows / 1e12
     # DRAM traffic per launch: ncu capture of a 37,888-instance launch of the same kernel (same d, same q),
     # scaled by the instances (the X planes and the output grow with n; the planes of the 512 rows do not)
@@ -260,19 +498,22 @@ def run_b200_arm(args):
                           "3 MMAs per product, FP32 promotion every two k slabs, fused RBF epilogue)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "issued_frac": 3 * achieved / peak, "traffic": traffic,
-                "peak_source": peak_src + "; sustained figure %.0f; torch.matmul fp16 8192^3 best-of-10 in this run "
-                               "%.0f. achieved = algorithmic 2*q*n*d flops per launch / mean CUDA-event time of the "
-                               "kernel-row phase; the two-plane scheme issues 3x these flops (issued_frac)"
-                               % (peak_sustained, f16_peak_in_run),
-                "peak_in_run": f16_peak_in_run, "ms_per_launch": t_rows * 1e3}
+                "peak_source": peak_src + " bf16_tflops burst; sustained figure %.0f; torch.matmul fp16 8192^3 best-of-10 "
+                               "in this run %.0f. achieved = algorithmic 2*q*n*d flops per launch / mean CUDA-event time "
+                               "of the kernel-row phase over all windows; the two-plane scheme issues 3x these flops "
+                               "(issued_frac)" % (peak_sustained, f16_peak_in_run),
+                "peak_in_run": f16_peak_in_run, "ms_per_launch": t_rows * 1e3, "rows_per_launch": rows_per_launch}
+    cache = solver.cache_stats() if hasattr(solver, "cache_stats") else None
+    # 16 of the timed launches' requested rows (the current working set's new half) for the parity sample
+    parity_ids = None
     solver.close()
-    km.close()
-    del Xd, km, solver
+    km_keep = km
+    del Xd, solver
     torch.cuda.empty_cache()
 
-    # ---- (2) end to end from host buffers: the same K-step job ------------------------------------
+    # ---- (2) end to end from host buffers: the same (W+K)-step job -----------------------------------
     def job(max_iter, budget_s=None):
-        """C-ABI job from pinned host buffers; returns (seconds, stats, rho, alpha_host)."""
+        """C-ABI job from pinned host buffers; returns (seconds, stats, rho, alpha_host, f_host, done)."""
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         km2 = capi.KernelMatrix(dense=Xh, gamma=GAMMA)               # H2D of X + split inside
@@ -293,23 +534,38 @@ def run_b200_arm(args):
         sv.close(); km2.close()
         return sec, st, rho, a_host, f_host, done
 
-    sec_e2e, st_e2e, _, _, _, _ = job(W + K)
+    # kernel-row parity sample on the resident matrix, taken before it is released
+    km_rows_sample = None
+    if not args.no_cpu_baseline:
+        pr = min(args.cpu_sample_rows, n)
+        parity_ids = (np.arange(16, dtype=np.int64) * 1013 + 7) % pr
+        km_rows_sample = km_keep.get_rows(torch.from_numpy(parity_ids.astype(np.int32)).cuda())[:, :pr].cpu().numpy()
+    km_keep.close()
+    del km_keep
+    torch.cuda.empty_cache()
+
+    sec_e2e, st_e2e, rho_e2e, a_e2e, _, _ = job(W + K)
     h2d = n * d * 4 + n * (4 + 8 + 8)
     d2h = n * 16 + 8
     e2e = {"value": st_e2e["kernel_rows"] / sec_e2e, "unit": "rows/s", "h2d_bytes_per_step": h2d / (W + K),
            "d2h_bytes_per_step": d2h / (W + K), "seconds": sec_e2e, "steps": W + K,
-           "note": "one K+W-step job through the C ABI from pinned host buffers: H2D of X/y/alpha/f, operand-plane split, "
-                   "solver set-up, steps, D2H of alpha/f/rho all inside the timed region"}
+           "note": "one (W+K)-step job through the C ABI from pinned host buffers: H2D of X/y/alpha/f, operand-plane split, "
+                   "solver set-up, steps, D2H of alpha/f/rho all inside the timed region. " + NO_CPU_CONVERGENCE}
+    check = {"steps": W + K, "alpha_sha256_16": sha(a_e2e.numpy()), "rho": rho_e2e,
+             "note": "state after exactly W+K outer iterations; runs on several GPUs print the same digest and compare "
+                     "it with a one-GPU run of their own"}
 
     # ---- (3) the whole training run to eps --------------------------------------------------------
     train = None
-    full = args.full_train if args.full_train >= 0 else 1
-    if full:
+    full_train = args.full_train if args.full_train >= 0 else 1
+    if full_train:
         sec, st, rho, a_host, f_host, done = job(10 ** 9, budget_s=args.train_budget_s)
         train = {"seconds": sec, "converged": bool(done), "outer_iters": st["outer_iters"],
                  "local_iters": st["local_iters"], "final_diff": st["final_diff"], "objective": st["objective"],
                  "rho": rho, "n_sv": int((a_host != 0).sum()), "kernel_rows_per_s": st["kernel_rows"] / sec,
-                 "phase_seconds": {k: st["seconds_" + k] for k in ("select", "rows", "local", "update")}}
+                 "kernel_rows": st["kernel_rows"],
+                 "phase_seconds": {k: st["seconds_" + k] for k in ("select", "rows", "local", "update")},
+                 "cpu_reference": NO_CPU_CONVERGENCE}
 
     # ---- (4) prediction with the trained model: decision values + vote for the test rows -----------
     predict = None
@@ -328,51 +584,75 @@ def run_b200_arm(args):
         counts = [n_pos, len(order) - n_pos]
 
         def run_predict(T):
-            dec = capi.predict_dec(km_sv, coef_d, counts, rho_d, 2, dense=T)
-            return capi.vote(dec, 2)
+            return capi.predict_labels(km_sv, coef_d, counts, rho_d, 2, dense=T)
 
-        warm = run_predict(Th[:2048].cuda())
+        warm = run_predict(Th[:4096].cuda())
         Td = Th.cuda()
         torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         labels = run_predict(Td)
         e1.record()
         torch.cuda.synchronize()
         ms_res = e0.elapsed_time(e1)
+        grown = free_before - torch.cuda.mem_get_info()[0]
         del Td
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         lab_h = run_predict(Th.cuda(non_blocking=True)).cpu()
         sec_host = time.perf_counter() - t0
         n_sv = len(order)
+        tfl = 2.0 * m * n_sv * d / (ms_res * 1e-3) / 1e12
         predict = {"rows": m, "n_sv": n_sv, "rows_per_s": m / (ms_res * 1e-3), "e2e_rows_per_s": m / sec_host,
-                   "algorithmic_tflops": 2.0 * m * n_sv * d / (ms_res * 1e-3) / 1e12,
+                   "algorithmic_tflops": tfl, "frac_of_tensor_peak": tfl / peak, "issued_frac": 3 * tfl / peak,
+                   "device_bytes_allocated_during_call": int(grown),
                    "positive_fraction": float((lab_h == 0).float().mean()),
                    "accuracy": float(((lab_h == 0).numpy() == (y_test > 0)).mean()),
-                   "note": "decision values + vote of the seed-8 test rows against the trained model; resident: test "
+                   "note": "decision values + vote of the seed-8 test rows against the trained model, coefficient sums "
+                           "fused into the contraction's epilogue (no test x SV kernel block in memory); resident: test "
                            "rows in HBM, CUDA events; e2e: from pinned host rows, labels back on the host"}
         km_sv.close()
         del Xsv, warm, labels
+    del Xh
+    torch.cuda.empty_cache()
+    capi.lib().tsvm_release_cached_memory()
 
-    cpu = None
+    # ---- (5) the HBM-bound kernels and the smaller configurations ----------------------------------
+    rooflines, configs = None, None
+    if not args.no_extras:
+        rooflines = extra_rooflines(torch, capi, synth, hbm_peak, peak_src, n)
+        which = [t for t in args.configs.split(",") if t]
+        cpu_which = [] if args.no_cpu_baseline else [t for t in args.cpu_configs.split(",") if t]
+        configs = small_configs(torch, capi, synth, which, cpu_which)
+
+    cpu, parity = None, None
     if not args.no_cpu_baseline:
         try:
             s = cpu_sample(args.cpu_sample_rows, args.cpu_sample_steps)
-            cpu = {k: s[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            cpu = {k: s[k] for k in ("value", "unit", "cores", "kind", "sample", "build")}
+            want = cpu_kernel_rows(min(args.cpu_sample_rows, n), parity_ids.astype(np.int32))
+            err = np.abs(km_rows_sample.astype(np.float64) - want) / np.maximum(np.abs(want), 1e-300)
+            parity = {"kernel_rows_max_rel_err": float(err.max()),
+                      "kernel_rows_max_rel_err_floored_1e-4": float((np.abs(km_rows_sample.astype(np.float64) - want)
+                                                                     / np.maximum(np.abs(want), 1e-4)).max()),
+                      "bound": 1e-5, "rows": 16, "columns": int(want.shape[1]),
+                      "note": "16 kernel rows of the resident matrix against the CPU reference on the first %d "
+                              "instances (the values do not depend on n)" % want.shape[1]}
         except Exception as exc:   # the baseline is reporting only; never fail the bench on it
-            cpu = {"value": None, "unit": "rows/s", "cores": os.cpu_count(), "kind": "port", "sample": "failed: %r" % exc}
+            cpu = {"value": None, "unit": "rows/s", "cores": host_threads(), "kind": "port", "sample": "failed: %r" % exc}
 
     line = {
         "metric": "kernel_rows_per_s", "value": value, "unit": "rows/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32 kernel values (two-plane FP16 tensor-core contraction with FP32 accumulation), f64 solver state", "data": "synthetic",
-        "config": {"workload": "config5: binary C-SVC, RBF gamma=0.5 C=1 eps=1e-3, %dx%d dense fp32, ws=1024, "
-                               "512 new kernel rows per outer iteration" % (n, d),
+        "config": {"workload": WORKLOAD % (n, d),
                    "l2": "inputs larger than L2 (X planes %.1f GB, row buffer %.1f GB)" % (2 * n * d * 2 / 1e9,
                                                                                           WS * n * 4 / 1e9)},
-        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
-        "phase_ms_per_step": phases, "train_to_eps": train, "predict": predict,
+        "windows_ms": win_ms, "window_reported": "median of %d windows of %d steps" % (len(full), K),
+        "roofline": roofline, "rooflines": rooflines, "cpu_baseline": cpu, "parity": parity, "e2e": e2e,
+        "gpu_launches": int(launches), "clocks": clk, "phase_ms_per_step": phases, "kernel_row_cache": cache,
+        "check": check, "train_to_eps": train, "predict": predict, "configs": configs,
     }
     print(json.dumps(line))
 

@@ -3,6 +3,7 @@
     python profile_case.py dense_rows --rows 20000 --reps 3
     python profile_case.py csr_rows   --rows 20242 --reps 3
     python profile_case.py solver     --rows 20000 --steps 5
+    python profile_case.py predict    --rows 100000 --q 8192 --reps 3
 
 Each case builds seeded synthetic data of the benchmark's shape at a reduced row count (larger than
 L2, a few hundred MB on the device), runs the kernel `reps` times and prints CUDA-event timings.
@@ -30,7 +31,7 @@ def _time(fn, reps):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["dense_rows", "csr_rows", "solver"])
+    ap.add_argument("case", choices=["dense_rows", "csr_rows", "solver", "predict"])
     ap.add_argument("--rows", type=int, default=20000)
     ap.add_argument("--q", type=int, default=512)
     ap.add_argument("--reps", type=int, default=3)
@@ -40,6 +41,24 @@ def main():
     ap.add_argument("--engine", default="auto", help="dense engine: auto, simt, tensor1, tensor2, tensor")
     args = ap.parse_args()
     capi.lib()
+    if args.case == "predict":
+        # fused prediction: --rows support vectors, --q test rows, binary model
+        prob = synth.config5(args.rows, d=args.d)
+        km = capi.KernelMatrix(dense=torch.from_numpy(prob["X"]).cuda(), gamma=prob["gamma"])
+        T = torch.from_numpy(synth.config5(args.q, d=args.d, seed=8)["X"]).cuda()
+        coef = torch.randn(args.rows, dtype=torch.float64, device="cuda")
+        rho = torch.zeros(1, dtype=torch.float64, device="cuda")
+        cnt = [args.rows // 2, args.rows - args.rows // 2]
+        capi.predict_labels(km, coef, cnt, rho, 2, dense=T)
+        torch.cuda.synchronize()
+        ms = _time(lambda: capi.predict_labels(km, coef, cnt, rho, 2, dense=T), args.reps)
+        out = torch.empty((args.q, km.n), dtype=torch.float32, device="cuda")
+        ms2 = _time(lambda: km.get_rows_instances(dense=T, out=out), args.reps)
+        fl = 2.0 * args.rows * args.q * args.d
+        print("predict n_sv=%d rows=%d d=%d: fused ms %s (%.0f TFLOP/s), kernel block only ms %s (%.0f TFLOP/s)" % (
+            args.rows, args.q, args.d, ["%.3f" % t for t in ms], fl / min(ms) / 1e9, ["%.3f" % t for t in ms2],
+            fl / min(ms2) / 1e9))
+        return
     if args.case in ("dense_rows", "solver"):
         prob = synth.config5(args.rows, d=args.d)
         km = capi.KernelMatrix(dense=torch.from_numpy(prob["X"]).cuda(), gamma=prob["gamma"])

@@ -44,9 +44,9 @@ constexpr int REGS_CONTROL = 56, REGS_EPILOGUE = 224;
 constexpr int EPI_CHUNK = 16;
 constexpr uint32_t EPI_STAGE_BYTES = EPI_CHUNK * EPI_WARPS * 32 * 4;
 constexpr uint32_t EPI_CONST_BYTES = EPI_WARPS * 2 * COLS_PER_THREAD * 4;
-// prediction form: coefficients (up to PRED_NC_SMEM coefficient rows) and class ids of this CTA's 128 instances
-constexpr int PRED_NC_SMEM = 16;
-constexpr uint32_t PRED_BYTES = PRED_NC_SMEM * BM * 4 + BM * 4;
+// prediction form: up to PRED_NC_SMEM coefficients of every epilogue thread's own instance (thread-private columns)
+constexpr int PRED_NC_SMEM = 9;
+constexpr uint32_t PRED_BYTES = PRED_NC_SMEM * EPI_WARPS * 32 * 4;
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_STAGE_BYTES + EPI_CONST_BYTES;
 constexpr uint32_t SMEM_BYTES_PREDICT = SMEM_BYTES + PRED_BYTES;
 static_assert(SMEM_BYTES_PREDICT <= 227 * 1024, "prediction form does not fit the shared memory of an SM");
@@ -143,7 +143,6 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
     const uint32_t tfull_bar = empty_bar + 8 * STAGES, tempty_bar = tfull_bar + 16;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    volatile int *epi_abort = reinterpret_cast<volatile int *>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -157,7 +156,6 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar + 8 * a, 1); mbar_init(tempty_bar + 8 * a, 2 * EPI_WARPS); }
         *abort_flag = 0;
-        *epi_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -240,9 +238,9 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
         float *priv = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256) + (warp - EPI_WARP0) * 32 + lane;
         float *rowc = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES) +
                       (warp - EPI_WARP0) * 2 * COLS_PER_THREAD;
-        // prediction form: coefficient table [coefficient row][instance of this CTA] and class ids
-        float *coef_sm = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES + EPI_CONST_BYTES);
-        int *cls_sm = reinterpret_cast<int *>(coef_sm + PRED_NC_SMEM * BM);
+        // prediction form: the coefficients of the thread's own instance, one thread-private column
+        float *coef_priv = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES + EPI_CONST_BYTES) +
+                           (warp - EPI_WARP0) * 32 + lane;
         const int nc = PREDICT ? pa.n_classes - 1 : 0;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
@@ -251,17 +249,16 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
             const int j = pt * 2 * BM + (int) rank * BM + quarter * 32 + lane;
             const float sdj = j < n ? sd[j] : 0.0f;
             const float uxj = (F16 && j < n) ? x_unscale[j] : 1.0f;
+            int cls_own = 0, cls_lo = 0, cls_hi = -1;
+            float coef_one = 0.0f;
             if constexpr (PREDICT) {
-                // coefficients and classes of this CTA's 128 instances, staged by the first four epilogue warps
-                // while the k loop runs; both column halves read them after the k loop
-                if (half == 0) {
-                    const int s0 = quarter * 32 + lane;                     // instance of this CTA, 0..127
-                    const int js = pt * 2 * BM + (int) rank * BM + s0;
-                    cls_sm[s0] = js < n ? pa.sv_class[js] : -1;
-                    if (nc <= PRED_NC_SMEM)
-                        for (int cr = 0; cr < nc; ++cr)
-                            coef_sm[cr * BM + s0] = js < n ? (float) pa.coef[(size_t) cr * n + js] : 0.0f;
-                }
+                // class and coefficients of the thread's own instance (a lane beyond the last instance takes the
+                // last one's class; its kernel values are forced to zero)
+                cls_own = pa.sv_class[j < n ? j : n - 1];
+                if (nc == 1) coef_one = j < n ? (float) pa.coef[j] : 0.0f;
+                else if (nc <= PRED_NC_SMEM)
+                    for (int cr = 0; cr < nc; ++cr)
+                        coef_priv[cr * (EPI_WARPS * 32)] = j < n ? (float) pa.coef[(size_t) cr * n + j] : 0.0f;
             }
             {
                 // Self dot and 1/scale of this warp's 128 requested rows go to shared memory by asynchronous
@@ -295,16 +292,7 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                     if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar + 8 * acc, 0));
                     if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 }
-                if constexpr (PREDICT) {
-                    // The prediction form exchanges data between the epilogue warps through named barriers, so
-                    // all eight warps must leave together: a warp whose wait gave up says so before the
-                    // barrier, and every warp reads the word after it.
-                    if (!ok && lane == 0) *epi_abort = 1;
-                    asm volatile("bar.sync 3, 256;" ::: "memory");       // also: coefficient table is complete
-                    if (*epi_abort) { ok = false; break; }
-                } else {
-                    if (!ok) break;
-                }
+                if (!ok) break;
                 // The sums live in registers, so a loop over them has to be fully unrolled; with the kernel
                 // function in its body that is 128 copies of it, and the instruction fetch of such an
                 // epilogue cost several times its arithmetic. Instead the sums pass 32 at a time through a
@@ -312,6 +300,28 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                 // what it wrote), 16 at a time, and a short rolled loop applies the kernel function and stores.
                 asm volatile("cp.async.wait_all;" ::: "memory");
                 __syncwarp();
+                // prediction form, RBF: K = 2^(A_i + B_j + S_i * dot) with per-test-row constants A_i, S_i (they
+                // replace the row's self dot and 1/scale in rowc) and the own instance's B_j: four instructions
+                // per kernel value. The exponent is formed in FP32 without the residual correction the stored
+                // kernel rows use (relative error up to |exponent| * 2^-23), which decision values do not need.
+                float pred_b = 0.0f;
+                if constexpr (PREDICT && EPI == EPI_RBF) {
+                    constexpr float LOG2E = 1.4426950408889634f;
+                    cls_lo = __reduce_min_sync(0xffffffffu, cls_own);
+                    cls_hi = __reduce_max_sync(0xffffffffu, cls_own);
+                    pred_b = -fn.gamma * LOG2E * sdj;
+#pragma unroll
+                    for (int c = lane; c < COLS_PER_THREAD; c += 32) {
+                        const float sd_i = rowc[c];
+                        const float uw_i = F16 ? rowc[COLS_PER_THREAD + c] : 1.0f;
+                        rowc[c] = -fn.gamma * LOG2E * sd_i;
+                        rowc[COLS_PER_THREAD + c] = 2.0f * fn.gamma * LOG2E * uw_i;
+                    }
+                    __syncwarp();
+                } else if constexpr (PREDICT) {
+                    cls_lo = __reduce_min_sync(0xffffffffu, cls_own);
+                    cls_hi = __reduce_max_sync(0xffffffffu, cls_own);
+                }
 #pragma unroll 1
                 for (int ch = 0; ch < COLS_PER_THREAD / EPI_CHUNK; ++ch) {
                     switch (ch) {           // register indices must be constants: one short case per chunk
@@ -337,61 +347,72 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                             }
                         }
                     } else {
-                        // kernel values of the own instance for the chunk's 16 test rows, back into the staging block
-#pragma unroll 8
-                        for (int c = 0; c < EPI_CHUNK; ++c) {
-                            float dot = priv[c * (EPI_WARPS * 32)];
-                            if constexpr (F16) dot = dot * uxj * rowc[COLS_PER_THREAD + cbase + c];
-                            priv[c * (EPI_WARPS * 32)] = j < n ? epilogue_value<EPI>(fn, dot, rowc[cbase + c], sdj) : 0.0f;
+                        // Kernel values of the own instance for the chunk's 16 test rows, times the instance's
+                        // coefficient; then the 32 lanes' products are added column by column with a butterfly
+                        // that halves the number of live columns per step (16 -> 8 -> 4 -> 2 -> 1 values per
+                        // lane, 31 shuffles for 16 columns), and one lane of every pair adds the warp's sum of
+                        // its column to the decision value. No exchange between warps: every warp adds the sums
+                        // of its own 32 instances.
+                        float kv[EPI_CHUNK];
+                        if constexpr (EPI == EPI_RBF) {
+                            float a_i[EPI_CHUNK], s_i[EPI_CHUNK];
+#pragma unroll
+                            for (int c4 = 0; c4 < EPI_CHUNK; c4 += 4) {
+                                const float4 av = *reinterpret_cast<const float4 *>(rowc + cbase + c4);
+                                const float4 sv = *reinterpret_cast<const float4 *>(rowc + COLS_PER_THREAD + cbase + c4);
+                                a_i[c4] = av.x; a_i[c4 + 1] = av.y; a_i[c4 + 2] = av.z; a_i[c4 + 3] = av.w;
+                                s_i[c4] = sv.x; s_i[c4 + 1] = sv.y; s_i[c4 + 2] = sv.z; s_i[c4 + 3] = sv.w;
+                            }
+#pragma unroll
+                            for (int c = 0; c < EPI_CHUNK; ++c) {
+                                float dot = priv[c * (EPI_WARPS * 32)];
+                                if constexpr (F16) dot *= uxj;
+                                const float arg = fmaf(dot, s_i[c], a_i[c]) + pred_b;
+                                float e;
+                                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(arg));
+                                kv[c] = j < n ? e : 0.0f;
+                            }
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < EPI_CHUNK; ++c) {
+                                float dot = priv[c * (EPI_WARPS * 32)];
+                                if constexpr (F16) dot = dot * uxj * rowc[COLS_PER_THREAD + cbase + c];
+                                kv[c] = j < n ? epilogue_value<EPI>(fn, dot, rowc[cbase + c], sdj) : 0.0f;
+                            }
                         }
-                        // the four warps of this column half exchange: every warp takes four of the 16 test rows
-                        // and sums coefficient x kernel value over the CTA's 128 instances
-                        asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
-                        const float *blk = reinterpret_cast<const float *>(ring_ptr + STAGES * STAGE_BYTES + 256) + half * 128;
-                        const int c_first = cls_sm[0];
-                        int c_last = cls_sm[BM - 1];
-                        if (c_last < 0) {          // tail tile: class of the last real instance
-                            const int last_real = n - 1 - (pt * 2 * BM + (int) rank * BM);
-                            c_last = last_real >= 0 ? cls_sm[last_real] : c_first;
-                        }
-                        int cq[4];
+                        const int col = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+                        const int r = i0 + cbase + col;
+                        for (int cl = cls_lo; cl <= cls_hi; ++cl)
+                            for (int cr = 0; cr < nc; ++cr) {
+                                float cf;
+                                if (nc == 1) cf = coef_one;
+                                else if (nc <= PRED_NC_SMEM) cf = coef_priv[cr * (EPI_WARPS * 32)];
+                                else cf = j < n ? (float) pa.coef[(size_t) cr * n + j] : 0.0f;
+                                if (cls_own != cl) cf = 0.0f;
+                                float w[EPI_CHUNK];
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) cq[q4] = cls_sm[q4 * 32 + lane];
-                        for (int cc = 0; cc < 4; ++cc) {
-                            const int c = quarter * 4 + cc;
-                            const int r = i0 + cbase + c;
-                            if (r >= m || c_first < 0) continue;
-                            float kv[4];
+                                for (int c = 0; c < EPI_CHUNK; ++c) w[c] = cf * kv[c];
 #pragma unroll
-                            for (int q4 = 0; q4 < 4; ++q4) kv[q4] = blk[c * (EPI_WARPS * 32) + q4 * 32 + lane];
-                            for (int cl = c_first; cl <= c_last; ++cl)
-                                for (int cr = 0; cr < nc; ++cr) {
-                                    float p = 0.0f;
+                                for (int half_n = EPI_CHUNK / 2; half_n >= 1; half_n >>= 1) {
+                                    const bool upper = (lane & (half_n * 2)) != 0;     // lane bit 4, 3, 2, 1
 #pragma unroll
-                                    for (int q4 = 0; q4 < 4; ++q4) {
-                                        float cf;
-                                        if (nc <= PRED_NC_SMEM) cf = coef_sm[cr * BM + q4 * 32 + lane];
-                                        else {
-                                            const int js = pt * 2 * BM + (int) rank * BM + q4 * 32 + lane;
-                                            cf = js < n ? (float) pa.coef[(size_t) cr * n + js] : 0.0f;
-                                        }
-                                        p = fmaf(cq[q4] == cl ? cf : 0.0f, kv[q4], p);
-                                    }
-#pragma unroll
-                                    for (int o = 16; o; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-                                    if (lane == 0 && p != 0.0f) {
-                                        const int other = cr < cl ? cr : cr + 1;
-                                        const int k = other > cl ? pair_index(pa.n_classes, cl, other)
-                                                                 : pair_index(pa.n_classes, other, cl);
-                                        atomicAdd(pa.dec + (size_t) r * pa.n_pairs + k, (double) p);
+                                    for (int c = 0; c < half_n; ++c) {
+                                        const float send = upper ? w[c] : w[c + half_n];
+                                        const float keep = upper ? w[c + half_n] : w[c];
+                                        w[c] = keep + __shfl_xor_sync(0xffffffffu, send, half_n * 2);
                                     }
                                 }
-                        }
-                        asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");   // staging block is reused
+                                const float total = w[0] + __shfl_xor_sync(0xffffffffu, w[0], 1);
+                                if ((lane & 1) == 0 && r < m && total != 0.0f) {
+                                    const int other = cr < cl ? cr : cr + 1;
+                                    const int k = other > cl ? pair_index(pa.n_classes, cl, other)
+                                                             : pair_index(pa.n_classes, other, cl);
+                                    atomicAdd(pa.dec + (size_t) r * pa.n_pairs + k, (double) total);
+                                }
+                            }
                     }
                 }
                 __syncwarp();          // the next item's copies overwrite rowc
-                if constexpr (PREDICT) asm volatile("bar.sync 3, 256;" ::: "memory");   // ... and the coefficient table
             }
         }
     }
