@@ -3,6 +3,7 @@
 // termination rules. Reference behaviour: src/thundersvm/solver/csmosolver.cpp:10-239,
 // src/thundersvm/solver/nusmosolver.cpp:9-136, src/thundersvm/kernel/smo_kernel.cu:28-315.
 #include "common.cuh"
+#include <cooperative_groups.h>
 #include <chrono>
 #include <limits.h>
 #include <string.h>
@@ -20,7 +21,12 @@ namespace tsvm {
 // the `want` smallest 96-bit keys (f-order, id) among the eligible instances:
 //   C-SMO : list 0 = I_up ascending (f, id);      list 1 = I_low descending (f, id)
 //   nu-SMO: lists 0/1 = I_up for y>0 / y<0;       lists 2/3 = I_low for y>0 / y<0
-// found with an 8-pass 12-bit radix select, followed by a compaction.
+// found with a 12-bit radix select of up to 8 passes, followed by a compaction (select_fused_kernel below).
+// One pass = histogram of the current digit over the eligible instances that match the prefix, all lists in
+// one sweep over the data; the last block to finish picks, per list, the digit that holds the wanted rank. A
+// list whose threshold digit holds few enough instances for the whole digit to fit the candidate capacity
+// `cap` is resolved on the spot (the threshold becomes "everything up to and including this digit" and the
+// exact order is left to the sort of the candidates), so that in practice two passes do the work.
 
 constexpr int RADIX_BITS = 12, RADIX_BINS = 1 << RADIX_BITS, RADIX_PASSES = 8, MAX_LISTS = 4;
 typedef unsigned __int128 key96_t;
@@ -52,150 +58,6 @@ __device__ __forceinline__ key96_t make_key(bool asc, double f, unsigned id) {
     return ((key96_t) h << 32) | id;
 }
 
-__global__ void select_init_kernel(SelectState *st, int *hist, int *ticket, int lists, int want) {
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < lists * RADIX_BINS; i += gridDim.x * blockDim.x) hist[i] = 0;
-    if (blockIdx.x == 0 && threadIdx.x < lists) {
-        SelectState s;
-        s.prefix_hi = 0; s.prefix_lo = 0; s.k_rem = want; s.take_all = 0; s.count = 0; s.resolved = 0;
-        st[threadIdx.x] = s;
-    }
-    if (blockIdx.x == 0 && threadIdx.x == 0) *ticket = 0;
-}
-
-// One radix pass: histogram of the current digit over the eligible instances that match the
-// prefix, all lists in one sweep over the data; the last block to finish picks, per list, the digit
-// that holds the wanted rank. A list whose threshold digit holds few enough instances for the whole
-// digit to fit the candidate capacity `cap` is resolved on the spot (the threshold becomes "everything
-// up to and including this digit" and the exact order is left to the sort of the candidates), so that
-// in practice two passes do the work and the remaining launches return at once.
-// Dynamic shared memory: lists x RADIX_BINS ints.
-__global__ void __launch_bounds__(256)
-select_hist_kernel(int solver_kind, int pass, int n, const double *__restrict__ f, const double *__restrict__ alpha,
-                   const int *__restrict__ y, const unsigned char *__restrict__ in_ws, double Cp, double Cn,
-                   SelectState *st, int *hist, int *ticket, int want, int cap) {
-    extern __shared__ int sh[];
-    __shared__ int scan[256];
-    __shared__ bool is_last;
-    const int lists = list_count(solver_kind);
-    const int shift = 96 - RADIX_BITS * (pass + 1);
-    unsigned active = 0;
-    key96_t prefix[MAX_LISTS];
-#pragma unroll
-    for (int l = 0; l < MAX_LISTS; ++l) {
-        prefix[l] = 0;
-        if (l < lists && !st[l].take_all && !st[l].resolved) {
-            active |= 1u << l;
-            prefix[l] = ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo;
-        }
-    }
-    if (!active) return;
-    for (int b = threadIdx.x; b < lists * RADIX_BINS; b += 256) sh[b] = 0;
-    __syncthreads();
-    for (int j = blockIdx.x * 256 + threadIdx.x; j < n; j += gridDim.x * 256) {
-        if (in_ws && in_ws[j]) continue;
-        const double a = alpha[j], fj = f[j];
-        const int yj = y[j];
-#pragma unroll
-        for (int l = 0; l < MAX_LISTS; ++l) {
-            if (!((active >> l) & 1u)) continue;
-            if (!in_list(solver_kind, l, a, yj, Cp, Cn)) continue;
-            const key96_t k = make_key(list_ascending(solver_kind, l), fj, (unsigned) j);
-            if (pass > 0 && (k >> (shift + RADIX_BITS)) != (prefix[l] >> (shift + RADIX_BITS))) continue;
-            const int bin = l * RADIX_BINS + ((int) (k >> shift) & (RADIX_BINS - 1));
-            if (pass == 0) {
-                // sign and exponent: nearly every instance lands in a handful of bins - one atomic per
-                // distinct bin and warp instead of one per instance
-                const unsigned peers = __match_any_sync(__activemask(), bin);
-                if ((int) (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&sh[bin], __popc(peers));
-            } else {
-                atomicAdd(&sh[bin], 1);
-            }
-        }
-    }
-    __syncthreads();
-    for (int b = threadIdx.x; b < lists * RADIX_BINS; b += 256)
-        if (sh[b]) atomicAdd(&hist[b], sh[b]);
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) is_last = (atomicAdd(ticket, 1) == (int) gridDim.x - 1);
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    for (int l = 0; l < lists; ++l) {
-        if (!((active >> l) & 1u)) continue;
-        volatile int *h = hist + l * RADIX_BINS;
-        // 16 consecutive bins per thread, block-wide exclusive scan of the per-thread sums
-        int local[16], sum = 0;
-#pragma unroll
-        for (int b = 0; b < 16; ++b) { local[b] = h[threadIdx.x * 16 + b]; sum += local[b]; }
-        scan[threadIdx.x] = sum;
-        __syncthreads();
-        for (int o = 1; o < 256; o <<= 1) {
-            int v = threadIdx.x >= o ? scan[threadIdx.x - o] : 0;
-            __syncthreads();
-            scan[threadIdx.x] += v;
-            __syncthreads();
-        }
-        const int total = scan[255];
-        const int before = scan[threadIdx.x] - sum;
-        const int k_rem = st[l].k_rem;
-        __syncthreads();
-        if (total < k_rem) {
-            if (threadIdx.x == 0) st[l].take_all = 1;   // can only happen in pass 0
-        } else if (before < k_rem && k_rem <= before + sum) {
-            int run = before;
-#pragma unroll
-            for (int b = 0; b < 16; ++b) {
-                if (run < k_rem && k_rem <= run + local[b]) {
-                    key96_t p = prefix[l] | ((key96_t) (threadIdx.x * 16 + b) << shift);
-                    const int k_new = k_rem - run;
-                    // instances below this digit: want - k_new; with the whole digit: + local[b]
-                    if (shift > 0 && (want - k_new) + local[b] <= cap) {
-                        p |= ((key96_t) 1 << shift) - 1;
-                        st[l].resolved = 1;
-                    }
-                    st[l].prefix_hi = (unsigned long long) (p >> 32);
-                    st[l].prefix_lo = (unsigned int) p;
-                    st[l].k_rem = k_new;
-                }
-                run += local[b];
-            }
-        }
-#pragma unroll
-        for (int b = 0; b < 16; ++b) h[threadIdx.x * 16 + b] = 0;
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) *ticket = 0;
-}
-
-// Compaction: every eligible instance whose key is <= the threshold goes to the list's
-// candidate array (unordered, `cap` entries per list). Unused tail entries keep id -1.
-__global__ void select_collect_kernel(int solver_kind, int n, const double *__restrict__ f,
-                                      const double *__restrict__ alpha, const int *__restrict__ y,
-                                      const unsigned char *__restrict__ in_ws, double Cp, double Cn, SelectState *st,
-                                      int cap, int id_offset, double *__restrict__ cand_f, int *__restrict__ cand_id) {
-    const int lists = list_count(solver_kind);
-    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x) {
-        if (in_ws && in_ws[j]) continue;
-        const double a = alpha[j], fj = f[j];
-        const int yj = y[j];
-        for (int l = 0; l < lists; ++l) {
-            if (!in_list(solver_kind, l, a, yj, Cp, Cn)) continue;
-            if (!st[l].take_all) {
-                const key96_t thr = ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo;
-                if (make_key(list_ascending(solver_kind, l), fj, (unsigned) j) > thr) continue;
-            }
-            const int pos = atomicAdd(&st[l].count, 1);
-            if (pos < cap) { cand_f[(size_t) l * cap + pos] = fj; cand_id[(size_t) l * cap + pos] = j + id_offset; }
-        }
-    }
-}
-
-__global__ void fill_int_kernel(int *p, int n, int v) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) p[i] = v;
-}
-
 // ---- merge: sort every candidate list, keep its first `want`, then the reference's alternating
 // walk with "already taken" checks (csmosolver.cpp:123-165 / nusmosolver.cpp:48-118). ------------
 constexpr int MERGE_THREADS = 1024, MERGE_MAX_LEN = 8192, MERGE_MAX_WANT = 1024, HASH_SLOTS = 4096;
@@ -204,10 +66,9 @@ __device__ __forceinline__ bool key_less(unsigned long long ah, unsigned al, uns
     return ah < bh || (ah == bh && al < bl);
 }
 
-__global__ void __launch_bounds__(MERGE_THREADS)
-select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const int *__restrict__ cand_id, int len,
-                    int want, int *__restrict__ out_ids, int *__restrict__ out_count, int seg_len) {
-    extern __shared__ unsigned char smem[];
+__device__ void merge_lists(int solver_kind, const double *__restrict__ cand_f, const int *__restrict__ cand_id, int len,
+                            int want, int *__restrict__ out_ids, int *__restrict__ out_count, int seg_len,
+                            unsigned char *smem) {
     const int lists = list_count(solver_kind);
     int P = 1;
     while (P < len) P <<= 1;
@@ -230,9 +91,9 @@ select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const in
             unsigned long long h = ~0ull;
             unsigned lo = ~0u;
             if (e < len) {
-                const int id = cand_id[(size_t) l * len + e];
+                const int id = __ldcg(cand_id + (size_t) l * len + e);      // written by other blocks: from L2
                 if (id >= 0) {
-                    h = ordered_key(cand_f[(size_t) l * len + e]);
+                    h = ordered_key(__ldcg(cand_f + (size_t) l * len + e));
                     lo = (unsigned) id;
                     if (!asc) { h = ~h; lo = ~lo; }
                     // keep real keys distinct from the padding key
@@ -411,13 +272,18 @@ select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const in
     }
 }
 
-// Sorts every candidate list in place by its list key (padding, id -1, last): one block per list, bitonic in
-// shared memory. The runs of several ranks can then be merged by rank computation instead of a sort.
 __global__ void __launch_bounds__(MERGE_THREADS)
-select_sort_candidates_kernel(int solver_kind, const double *cand_f, const int *cand_id, int len, double *out_f,
-                              int *out_id, int out_len) {
+select_merge_kernel(int solver_kind, const double *__restrict__ cand_f, const int *__restrict__ cand_id, int len,
+                    int want, int *__restrict__ out_ids, int *__restrict__ out_count, int seg_len) {
     extern __shared__ unsigned char smem[];
-    const int l = blockIdx.x, tid = threadIdx.x;
+    merge_lists(solver_kind, cand_f, cand_id, len, want, out_ids, out_count, seg_len, smem);
+}
+
+// Sorts a candidate list by its list key (padding, id -1, last): one block per list, bitonic in shared
+// memory. The runs of several ranks can then be merged by rank computation instead of a sort.
+__device__ void sort_list(int solver_kind, int l, const double *cand_f, const int *cand_id, int len, double *out_f,
+                          int *out_id, int out_len, unsigned char *smem) {
+    const int tid = threadIdx.x;
     int P = 1;
     while (P < len) P <<= 1;
     unsigned long long *kh = reinterpret_cast<unsigned long long *>(smem);
@@ -429,9 +295,9 @@ select_sort_candidates_kernel(int solver_kind, const double *cand_f, const int *
         unsigned lo = ~0u;
         double v = 0.0;
         if (e < len) {
-            const int id = cand_id[(size_t) l * len + e];
+            const int id = __ldcg(cand_id + (size_t) l * len + e);
             if (id >= 0) {
-                v = cand_f[(size_t) l * len + e];
+                v = __ldcg(cand_f + (size_t) l * len + e);
                 h = ordered_key(v);
                 lo = (unsigned) id;
                 if (!asc) { h = ~h; lo = ~lo; }
@@ -460,6 +326,210 @@ select_sort_candidates_kernel(int solver_kind, const double *cand_f, const int *
         const bool pad = kh[e] == ~0ull && kl[e] == ~0u;
         out_f[(size_t) l * out_len + e] = pad ? 0.0 : fv[e];
         out_id[(size_t) l * out_len + e] = pad ? -1 : (int) (asc ? kl[e] : ~kl[e]);
+    }
+}
+
+__global__ void __launch_bounds__(MERGE_THREADS)
+select_sort_candidates_kernel(int solver_kind, const double *cand_f, const int *cand_id, int len, double *out_f,
+                              int *out_id, int out_len) {
+    extern __shared__ unsigned char smem[];
+    sort_list(solver_kind, blockIdx.x, cand_f, cand_id, len, out_f, out_id, out_len, smem);
+}
+
+// ---- the whole selection as ONE cooperative launch -------------------------------------------------------
+// init -> radix passes (as many as the data needs, decided on the device) -> compaction -> sort / merge of the
+// candidates, with grid-wide barriers between the phases instead of one launch per phase. The launch is
+// cooperative (all blocks resident), so the barriers cannot deadlock. Every block takes the same path
+// through the barriers: the decisions between them depend only on state written before the previous barrier.
+namespace cg = cooperative_groups;
+constexpr int FUSED_THREADS = 1024;
+enum { FUSED_CANDIDATES = 0, FUSED_MERGE = 1, FUSED_SORT = 2 };
+
+struct SelectArgs {
+    int solver_kind, n;
+    const double *f, *alpha;
+    const int *y;
+    const unsigned char *in_ws;
+    double Cp, Cn;
+    SelectState *st;
+    int *hist, *ticket;
+    int want, cap, id_offset;
+    double *cand_f;             // [lists][cap]
+    int *cand_id;
+    int mode;                   // FUSED_*
+    int *out_ids, *out_count;   // FUSED_MERGE: the selected ids
+    double *sorted_f;           // FUSED_SORT: the `want` best of every list, sorted, [lists][want]
+    int *sorted_id;
+    // optional rotation of the working set before the selection (plain solver): ids[0..q) <- ids[q..2q),
+    // in-working-set flags of the leaving / staying members
+    int *shift_ids;
+    int shift_q;
+    unsigned char *shift_flags;
+};
+
+__device__ void merge_lists(int solver_kind, const double *cand_f, const int *cand_id, int len, int want, int *out_ids,
+                            int *out_count, int seg_len, unsigned char *smem);
+__device__ void sort_list(int solver_kind, int l, const double *cand_f, const int *cand_id, int len, double *out_f,
+                          int *out_id, int out_len, unsigned char *smem);
+
+__global__ void __launch_bounds__(FUSED_THREADS, 1) select_fused_kernel(const SelectArgs a) {
+    extern __shared__ unsigned char fused_smem[];
+    int *sh = reinterpret_cast<int *>(fused_smem);
+    __shared__ int scan[256];
+    __shared__ bool is_last;
+    cg::grid_group grid = cg::this_grid();
+    const int lists = list_count(a.solver_kind);
+    // the selection state is written by other blocks between the barriers: always read it from L2
+    volatile SelectState *st = a.st;
+    const int tid = threadIdx.x, gtid = blockIdx.x * FUSED_THREADS + tid, gsize = gridDim.x * FUSED_THREADS;
+
+    // ---- phase 0: state, histograms, candidate ids, optional rotation of the working set
+    for (int i = gtid; i < lists * RADIX_BINS; i += gsize) a.hist[i] = 0;
+    for (int i = gtid; i < lists * a.cap; i += gsize) a.cand_id[i] = -1;
+    if (blockIdx.x == 0) {
+        if (tid < lists) {
+            st[tid].prefix_hi = 0; st[tid].prefix_lo = 0; st[tid].k_rem = a.want; st[tid].take_all = 0;
+            st[tid].count = 0; st[tid].resolved = 0;
+        }
+        if (tid == 0) *a.ticket = 0;
+        if (a.shift_ids && tid < a.shift_q) {
+            const int leaving = a.shift_ids[tid], staying = a.shift_ids[a.shift_q + tid];
+            if (leaving >= 0) a.shift_flags[leaving] = 0;
+            if (staying >= 0) a.shift_flags[staying] = 1;
+            a.shift_ids[tid] = staying;
+        }
+    }
+    grid.sync();
+
+    // ---- radix passes: one sweep each; the last block to finish its sweep picks the digits
+    for (int pass = 0; pass < RADIX_PASSES; ++pass) {
+        const int shift = 96 - RADIX_BITS * (pass + 1);
+        unsigned active = 0;
+        key96_t prefix[MAX_LISTS];
+#pragma unroll
+        for (int l = 0; l < MAX_LISTS; ++l) {
+            prefix[l] = 0;
+            if (l < lists && !st[l].take_all && !st[l].resolved) {
+                active |= 1u << l;
+                prefix[l] = ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo;
+            }
+        }
+        if (!active) break;                      // the same for every block: the state was final before the barrier
+        for (int b = tid; b < lists * RADIX_BINS; b += FUSED_THREADS) sh[b] = 0;
+        __syncthreads();
+        for (int j = gtid; j < a.n; j += gsize) {
+            if (a.in_ws && a.in_ws[j]) continue;
+            const double al = a.alpha[j], fj = a.f[j];
+            const int yj = a.y[j];
+#pragma unroll
+            for (int l = 0; l < MAX_LISTS; ++l) {
+                if (!((active >> l) & 1u)) continue;
+                if (!in_list(a.solver_kind, l, al, yj, a.Cp, a.Cn)) continue;
+                const key96_t k = make_key(list_ascending(a.solver_kind, l), fj, (unsigned) j);
+                if (pass > 0 && (k >> (shift + RADIX_BITS)) != (prefix[l] >> (shift + RADIX_BITS))) continue;
+                const int bin = l * RADIX_BINS + ((int) (k >> shift) & (RADIX_BINS - 1));
+                if (pass == 0) {
+                    const unsigned peers = __match_any_sync(__activemask(), bin);
+                    if ((int) (tid & 31) == __ffs(peers) - 1) atomicAdd(&sh[bin], __popc(peers));
+                } else {
+                    atomicAdd(&sh[bin], 1);
+                }
+            }
+        }
+        __syncthreads();
+        for (int b = tid; b < lists * RADIX_BINS; b += FUSED_THREADS)
+            if (sh[b]) atomicAdd(&a.hist[b], sh[b]);
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) is_last = (atomicAdd(a.ticket, 1) == (int) gridDim.x - 1);
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            for (int l = 0; l < lists; ++l) {
+                if (!((active >> l) & 1u)) continue;
+                volatile int *h = a.hist + l * RADIX_BINS;
+                // threads 0..255: 16 consecutive bins each, block-wide exclusive scan of the per-thread sums
+                int local[16], sum = 0;
+                if (tid < 256) {
+#pragma unroll
+                    for (int b = 0; b < 16; ++b) { local[b] = h[tid * 16 + b]; sum += local[b]; }
+                    scan[tid] = sum;
+                }
+                __syncthreads();
+                for (int o = 1; o < 256; o <<= 1) {
+                    int v = (tid < 256 && tid >= o) ? scan[tid - o] : 0;
+                    __syncthreads();
+                    if (tid < 256) scan[tid] += v;
+                    __syncthreads();
+                }
+                const int total = scan[255];
+                const int before = tid < 256 ? scan[tid] - sum : 0;
+                const int k_rem = st[l].k_rem;
+                __syncthreads();
+                if (tid < 256) {
+                    if (total < k_rem) {
+                        if (tid == 0) st[l].take_all = 1;   // can only happen in pass 0
+                    } else if (before < k_rem && k_rem <= before + sum) {
+                        int run = before;
+#pragma unroll
+                        for (int b = 0; b < 16; ++b) {
+                            if (run < k_rem && k_rem <= run + local[b]) {
+                                key96_t p = prefix[l] | ((key96_t) (tid * 16 + b) << shift);
+                                const int k_new = k_rem - run;
+                                if (shift > 0 && (a.want - k_new) + local[b] <= a.cap) {
+                                    p |= ((key96_t) 1 << shift) - 1;
+                                    st[l].resolved = 1;
+                                }
+                                st[l].prefix_hi = (unsigned long long) (p >> 32);
+                                st[l].prefix_lo = (unsigned int) p;
+                                st[l].k_rem = k_new;
+                            }
+                            run += local[b];
+                        }
+                    }
+#pragma unroll
+                    for (int b = 0; b < 16; ++b) h[tid * 16 + b] = 0;
+                }
+                __syncthreads();
+            }
+            if (tid == 0) *a.ticket = 0;
+            __threadfence();
+        }
+        grid.sync();
+    }
+
+    // ---- compaction of the candidates
+    key96_t threshold[MAX_LISTS];
+    bool take_all[MAX_LISTS];
+#pragma unroll
+    for (int l = 0; l < MAX_LISTS; ++l) {
+        take_all[l] = l < lists ? st[l].take_all != 0 : true;
+        threshold[l] = l < lists ? ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo : 0;
+    }
+    for (int j = gtid; j < a.n; j += gsize) {
+        if (a.in_ws && a.in_ws[j]) continue;
+        const double al = a.alpha[j], fj = a.f[j];
+        const int yj = a.y[j];
+#pragma unroll
+        for (int l = 0; l < MAX_LISTS; ++l) {
+            if (l >= lists) continue;
+            if (!in_list(a.solver_kind, l, al, yj, a.Cp, a.Cn)) continue;
+            if (!take_all[l]) {
+                const key96_t thr = threshold[l];
+                if (make_key(list_ascending(a.solver_kind, l), fj, (unsigned) j) > thr) continue;
+            }
+            const int pos = atomicAdd(&a.st[l].count, 1);
+            if (pos < a.cap) { a.cand_f[(size_t) l * a.cap + pos] = fj; a.cand_id[(size_t) l * a.cap + pos] = j + a.id_offset; }
+        }
+    }
+    if (a.mode == FUSED_CANDIDATES) return;
+    __threadfence();
+    grid.sync();
+    // ---- the candidates are few: one block merges them / one block per list sorts them
+    if (a.mode == FUSED_MERGE) {
+        if (blockIdx.x == 0) merge_lists(a.solver_kind, a.cand_f, a.cand_id, a.cap, a.want, a.out_ids, a.out_count, 0, fused_smem);
+    } else if ((int) blockIdx.x < lists) {
+        sort_list(a.solver_kind, blockIdx.x, a.cand_f, a.cand_id, a.cap, a.sorted_f, a.sorted_id, a.want, fused_smem);
     }
 }
 
@@ -686,17 +756,6 @@ __global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *
         const int id = ids[a];
         if (id >= 0) { diag_ws[a] = diag[id]; y_ws[a] = y[id]; f_ws[a] = f[id]; alpha_ws[a] = alpha[id]; }
         else { diag_ws[a] = 1.0f; y_ws[a] = 0; f_ws[a] = 0.0; alpha_ws[a] = 0.0; }
-    }
-}
-
-// ids[0..q) <- ids[q..ws); flags: old first half leaves the working set, old second half stays.
-__global__ void shift_ws_kernel(int *ids, int q, unsigned char *in_ws) {
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;   // launched as one block, q <= 512
-    if (t < q) {
-        const int leaving = ids[t], staying = ids[q + t];  // distinct instances (-1: empty slot)
-        if (leaving >= 0) in_ws[leaving] = 0;
-        if (staying >= 0) in_ws[staying] = 1;
-        ids[t] = staying;
     }
 }
 
@@ -990,24 +1049,60 @@ void tsvm_ws_destroy(tsvm_ws *w) {
     delete w;
 }
 
-// Candidate lists of `cap` >= want entries each (stride cap): the `want` best of every list are among them.
+// The selection in one cooperative launch (select_fused_kernel). Candidate lists of `cap` >= want entries each
+// (stride cap): the `want` best of every list are among them; mode says what happens to them on the device.
+struct FusedExtra {
+    int mode = FUSED_CANDIDATES;
+    int *out_ids = nullptr;                       // FUSED_MERGE
+    double *sorted_f = nullptr;                   // FUSED_SORT
+    int *sorted_id = nullptr;
+    int *shift_ids = nullptr;                     // optional rotation of the working set first
+    int shift_q = 0;
+    unsigned char *shift_flags = nullptr;
+};
+
+static size_t fused_smem_bytes(int lists, int cap, int mode) {
+    size_t b = (size_t) lists * RADIX_BINS * sizeof(int);
+    int P = 1;
+    while (P < cap) P <<= 1;
+    if (mode == FUSED_MERGE && merge_smem_bytes(cap) > b) b = merge_smem_bytes(cap);
+    if (mode == FUSED_SORT && (size_t) P * 20 + 8 > b) b = (size_t) P * 20 + 8;
+    return b;
+}
+
 static tsvm_status ws_candidates_cap(tsvm_ws *w, int solver_kind, int n, const double *f_dev, const double *alpha_dev,
                                      const int *y_dev, const unsigned char *in_ws_dev, double Cp, double Cn, int want,
-                                     int cap, int id_offset, double *cand_f_dev, int *cand_id_dev, cudaStream_t st) {
+                                     int cap, int id_offset, double *cand_f_dev, int *cand_id_dev, cudaStream_t st,
+                                     const FusedExtra &x = FusedExtra()) {
     const int lists = solver_kind == TSVM_SOLVER_C ? 2 : 4;
-    int grid = ceil_div(n, 256 * 4);
-    if (grid > 296) grid = 296;
-    if (grid < 1) grid = 1;
-    const size_t hist_smem = (size_t) lists * RADIX_BINS * sizeof(int);
-    TSVM_ONCE_PER_DEVICE(TSVM_CUDA(cudaFuncSetAttribute(select_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                        (int) (MAX_LISTS * RADIX_BINS * sizeof(int)))));
-    TSVM_LAUNCH(select_init_kernel, 16, 256, 0, st, w->state, w->hist, w->ticket, lists, want);
-    TSVM_LAUNCH(fill_int_kernel, ceil_div(lists * cap, 256), 256, 0, st, cand_id_dev, lists * cap, -1);
-    for (int p = 0; p < RADIX_PASSES; ++p)
-        TSVM_LAUNCH(select_hist_kernel, grid, 256, hist_smem, st, solver_kind, p, n, f_dev, alpha_dev, y_dev, in_ws_dev,
-                    Cp, Cn, w->state, w->hist, w->ticket, want, cap);
-    TSVM_LAUNCH(select_collect_kernel, grid, 256, 0, st, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn,
-                w->state, cap, id_offset, cand_f_dev, cand_id_dev);
+    static int resident_blocks[MAX_DEVICES] = {0};
+    int dev = 0;
+    TSVM_CUDA(cudaGetDevice(&dev));
+    int &max_blocks = resident_blocks[dev & (MAX_DEVICES - 1)];
+    if (!max_blocks) {
+        const size_t smem_max = fused_smem_bytes(MAX_LISTS, MERGE_MAX_LEN, FUSED_SORT) > fused_smem_bytes(MAX_LISTS, MERGE_MAX_LEN, FUSED_MERGE)
+                                    ? fused_smem_bytes(MAX_LISTS, MERGE_MAX_LEN, FUSED_SORT)
+                                    : fused_smem_bytes(MAX_LISTS, MERGE_MAX_LEN, FUSED_MERGE);
+        TSVM_CUDA(cudaFuncSetAttribute(select_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_max));
+        int sms = 0, coop = 0;
+        TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        TSVM_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+        TSVM_REQUIRE(coop, "working-set selection needs a device that supports cooperative launches");
+        max_blocks = sms;                         // one 1024-thread block per SM: always resident together
+    }
+    SelectArgs a;
+    a.solver_kind = solver_kind; a.n = n; a.f = f_dev; a.alpha = alpha_dev; a.y = y_dev; a.in_ws = in_ws_dev;
+    a.Cp = Cp; a.Cn = Cn; a.st = w->state; a.hist = w->hist; a.ticket = w->ticket; a.want = want; a.cap = cap;
+    a.id_offset = id_offset; a.cand_f = cand_f_dev; a.cand_id = cand_id_dev; a.mode = x.mode; a.out_ids = x.out_ids;
+    a.out_count = w->count; a.sorted_f = x.sorted_f; a.sorted_id = x.sorted_id; a.shift_ids = x.shift_ids;
+    a.shift_q = x.shift_q; a.shift_flags = x.shift_flags;
+    int grid = ceil_div(n, FUSED_THREADS * 2);
+    if (grid > max_blocks) grid = max_blocks;
+    if (grid < (x.mode == FUSED_SORT ? lists : 1)) grid = x.mode == FUSED_SORT ? lists : 1;
+    void *args[] = {&a};
+    TSVM_CUDA(cudaLaunchCooperativeKernel((const void *) select_fused_kernel, dim3(grid), dim3(FUSED_THREADS), args,
+                                          fused_smem_bytes(lists, cap, x.mode), st));
+    count_launch();
     return TSVM_OK;
 }
 
@@ -1072,9 +1167,11 @@ tsvm_status tsvm_select_working_set(tsvm_ws *w, int solver_kind, int n, const do
                  solver_kind >= 0 && solver_kind <= 2, "select_working_set: bad arguments");
     const int cap = 2 * want <= w->cand_cap ? 2 * want : (want <= w->cand_cap ? w->cand_cap : want);
     TSVM_REQUIRE(cap >= want, "select_working_set: candidate buffers hold %d entries, %d wanted", w->cand_cap, want);
-    TSVM_TRY(ws_candidates_cap(w, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn, want, cap, 0, w->cand_f,
-                               w->cand_id, (cudaStream_t) stream));
-    return tsvm_ws_merge(w, solver_kind, w->cand_f, w->cand_id, cap, want, out_ids_dev, stream);
+    FusedExtra x;
+    x.mode = FUSED_MERGE;
+    x.out_ids = out_ids_dev;
+    return ws_candidates_cap(w, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn, want, cap, 0, w->cand_f,
+                             w->cand_id, (cudaStream_t) stream, x);
 }
 
 // ---- working-set selection without any allocation --------------------------------------------------
@@ -1127,8 +1224,8 @@ tsvm_status tsvm_select_working_set_static(int solver_kind, int n, const double 
     view.count = reinterpret_cast<int *>(base + STATIC_OFF_COUNT);
     view.cand_f = reinterpret_cast<double *>(base + STATIC_OFF_CAND_F);
     view.cand_id = reinterpret_cast<int *>(base + STATIC_OFF_CAND_ID);
-    // select_init_kernel zeroes the state, histograms and ticket and fill_int_kernel resets the candidate
-    // ids on every call, so nothing of an earlier call's contents is read.
+    // the selection kernel's first phase zeroes the state, the histograms and the ticket and resets the
+    // candidate ids on every call, so nothing of an earlier call's contents is read.
     return tsvm_select_working_set(&view, solver_kind, n, f_dev, alpha_dev, y_dev, in_ws_dev, Cp, Cn, want,
                                    out_ids_dev, stream);
 }
@@ -1300,8 +1397,14 @@ struct tsvm_solver {
             TSVM_TRY(tsvm_km_rows_by_index(km, ids, ws, rows, ld, st));
             rows_made += ws;
         } else {
-            TSVM_LAUNCH(shift_ws_kernel, 1, 1024, 0, st, ids, q, in_ws);
-            TSVM_TRY(tsvm_select_working_set(sel, kind, n, f, alpha, y, in_ws, Cp, Cn, q, ids + q, st));
+            // rotation of the working set (old second half -> first half, flags) and the selection of the new
+            // second half: one cooperative launch
+            FusedExtra x;
+            x.mode = FUSED_MERGE;
+            x.out_ids = ids + q;
+            x.shift_ids = ids; x.shift_q = q; x.shift_flags = in_ws;
+            TSVM_TRY(ws_candidates_cap(sel, kind, n, f, alpha, y, in_ws, Cp, Cn, q, 2 * q <= sel->cand_cap ? 2 * q : q, 0,
+                                       sel->cand_f, sel->cand_id, st, x));
             TSVM_CUDA(cudaEventRecord(ev[1], st));
             float *new_rows = rows + (size_t) (1 - first_half_phys) * q * ld;
             if (!overlapped) {
@@ -1646,12 +1749,14 @@ struct tsvm_shard {
                                       cudaMemcpyDeviceToDevice, st));
         }
         // Candidates into the selector's own lists with twice the wanted capacity where it fits (the radix
-        // select then stops after two sweeps, see select_hist_kernel), sorted, and the best n_new of every
+        // select then stops after two sweeps, see select_fused_kernel), sorted, and the best n_new of every
         // list handed over: the merge of the gathered sorted runs needs no sort.
         const int cap = 2 * n_new <= sel->cand_cap ? 2 * n_new : n_new;
+        FusedExtra x;
+        x.mode = FUSED_SORT;
+        x.sorted_f = cand_f; x.sorted_id = cand_id;
         TSVM_TRY(ws_candidates_cap(sel, kind, n_local, f, alpha, y, iter == 0 ? nullptr : in_ws, Cp, Cn, n_new, cap, lo,
-                                   sel->cand_f, sel->cand_id, st));
-        TSVM_TRY(ws_sort_impl(kind, sel->cand_f, sel->cand_id, cap, cand_f, cand_id, n_new, st));
+                                   sel->cand_f, sel->cand_id, st, x));
         *lists_out = lists;
         *want_out = n_new;
         phase = 1;
