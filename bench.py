@@ -58,6 +58,9 @@ def parse():
     ap.add_argument("--cpu-configs", default="c1,c2,c4",
                     help="configurations the CPU reference also trains to convergence (c3 takes minutes)")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-kernel rooflines and the smaller configurations")
+    ap.add_argument("--workload", default="c5", choices=["c5", "c3"],
+                    help="c5: the headline configuration (default); c3: the 10-class one-vs-one configuration, its 45 "
+                         "binary problems and its test rows split over the GPUs")
     return ap.parse_args()
 
 
@@ -432,6 +435,15 @@ def run_b200_arm(args):
     if world > 1:
         dist.barrier()
     capi.lib()
+
+    if args.workload == "c3":
+        from thundersvm_b200 import sharded
+        line = sharded.bench_ovo(args, rank, world)
+        if rank == 0:
+            print(json.dumps(line))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     if world > 1:
         from thundersvm_b200 import sharded
