@@ -112,11 +112,12 @@ tsvm_status tsvm_km_rows_for_features_dense(tsvm_km *km, const float *T_dev, int
 
 /* Selects the dense kernel-row engine: 0 = automatic (default: engine 4, or FP32 CUDA-core tiles when
  * there are at most 32 features, where a k loop of one slab gives the tensor core nothing to
- * pipeline), 1 = FP32 CUDA-core tiles, 2 = tcgen05 tiles on two TF32 planes with one CTA per tile,
- * 3 = the same planes with CTA pairs, 4 = tcgen05 CTA pairs on two row-scaled FP16 planes (every row
- * is multiplied by a power of two that brings its largest magnitude to [2^14, 2^15) before the split;
- * same accuracy class as engine 3 at twice the tensor-core rate and half the operand bytes). The
- * operand planes are built on the first call that needs them; changing the engine rebuilds them. */
+ * pipeline), 1 = FP32 CUDA-core tiles, 3 = tcgen05 CTA pairs on two TF32 planes (2 is accepted as an
+ * alias), 4 = tcgen05 CTA pairs on two row-scaled FP16 planes (every row is multiplied by a power of
+ * two that brings its largest magnitude to [2^14, 2^15) before the split; same accuracy class as
+ * engine 3 at twice the tensor-core rate and half the operand bytes). The operand planes are built on
+ * the first call that needs them; changing the engine rebuilds them. On a CSR matrix the setting is
+ * ignored. */
 tsvm_status tsvm_km_set_dense_engine(tsvm_km *km, int engine);
 
 /* ------------------------------------------------------------------------------------------
@@ -134,9 +135,23 @@ typedef struct {
     double seconds_local;
     double seconds_update;
     double seconds_total;
-    long long kernel_rows;      /* rows of length n produced by get_rows                     */
+    long long kernel_rows;      /* rows of length n delivered by get_rows (computed or cached) */
     long long gpu_launches;     /* kernels launched by this call                             */
+    long long cache_hits;       /* delivered rows that were found in the kernel-row cache    */
+    long long cache_misses;     /* delivered rows that the engine computed                   */
+    long long cache_rows;       /* capacity of the cache, rows                               */
+    long long row_blocks;       /* engine row blocks a cache-less solver would have computed */
+    long long row_blocks_saved; /* ... of which the cache made this many unnecessary         */
 } tsvm_solve_stats;
+
+/* Kernel-row cache. The solver's row buffer holds as many kernel rows as this budget allows (at least the
+ * working set plus one batch of new rows, at most one row per instance) and keeps the least recently
+ * used ones across outer iterations; a requested row that is still there is not computed again. The
+ * reference keeps only the previous iteration's rows (src/thundersvm/solver/csmosolver.cpp:33-42,69-76).
+ * bytes < 0 restores the default (the environment variable TSVM_ROW_CACHE_MB if set, else 45 % of the
+ * device's memory), 0 keeps no more than the minimum. Applies to solvers created afterwards. Results do
+ * not depend on the budget: a cached row holds the values the engine would compute again. */
+void tsvm_set_row_cache_bytes(long long bytes);
 
 /* CSMOSolver::solve / NuSMOSolver::solve. y_dev[n] (+1/-1), alpha_dev[n] and f_dev[n] are
  * read and updated in place on the device; *rho_host receives rho. max_iter = -1 means no

@@ -38,7 +38,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--d", type=int, default=2000, help="features of the dense cases")
     ap.add_argument("--no-overlap", action="store_true", help="solver case: run the steps one after the other")
-    ap.add_argument("--engine", default="auto", help="dense engine: auto, simt, tensor1, tensor2, tensor")
+    ap.add_argument("--engine", default="auto", help="dense engine: auto, simt, tensor2 (TF32 planes), tensor (FP16 planes)")
     args = ap.parse_args()
     capi.lib()
     if args.case == "predict":

@@ -38,7 +38,7 @@ def _check_rows(capi, prob, n, q, engine=None, force=None, kernel="rbf", coef0=0
     return km, X
 
 
-@pytest.mark.parametrize("engine", ["auto", "tensor", "tensor2", "tensor1", "simt"])
+@pytest.mark.parametrize("engine", ["auto", "tensor", "tensor2", "simt"])
 @pytest.mark.parametrize("n,q", [(1000, 64), (4097, 512), (300, 101), (129, 128), (128, 1), (2500, 1024)])
 def test_dense_rows_c1(capi, engine, n, q):
     """Config 1 has 20 features with |x| up to 3 and RBF arguments up to ~50. The automatic engine uses
@@ -48,13 +48,13 @@ def test_dense_rows_c1(capi, engine, n, q):
     _check_rows(capi, synth.config1(n), n, q, engine=engine, tol=3e-5 if engine.startswith("tensor") else REL_TOL)
 
 
-@pytest.mark.parametrize("engine", ["tensor", "tensor2", "tensor1", "simt"])
+@pytest.mark.parametrize("engine", ["tensor", "tensor2", "simt"])
 def test_dense_rows_c5_shape(capi, engine):
     """Unit-norm rows, d = 2000 (config 5's row length), n not a multiple of the tile."""
     _check_rows(capi, synth.config5(3001), 3001, 512, engine=engine)
 
 
-@pytest.mark.parametrize("engine", ["tensor", "tensor2", "tensor1", "simt"])
+@pytest.mark.parametrize("engine", ["tensor", "tensor2", "simt"])
 def test_dense_rows_c3_shape(capi, engine):
     """784 features in [0,1] (config 3). Same-class dot products reach ~100, where the oracle's own
     sequential FP32 accumulation noise is ~1e-5 relative on K; both are therefore also compared with an
@@ -79,7 +79,7 @@ def test_dense_rows_c3_shape(capi, engine):
 
 @pytest.mark.parametrize("kernel,kw", [("linear", {}), ("poly", dict(coef0=0.1, degree=3)),
                                        ("sigmoid", dict(coef0=0.1))])
-@pytest.mark.parametrize("engine", ["tensor", "tensor2", "tensor1", "simt"])
+@pytest.mark.parametrize("engine", ["tensor", "tensor2", "simt"])
 def test_dense_rows_other_kernels(capi, engine, kernel, kw):
     _check_rows(capi, synth.config1(1500), 1500, 200, engine=engine, kernel=kernel, **kw)
 

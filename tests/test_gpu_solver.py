@@ -320,3 +320,43 @@ def test_config5_generator_at_scale_against_the_reference_fixture(capi, golden_d
                            torch.tensor([rho], dtype=torch.float64, device="cuda"), 2,
                            dense=torch.from_numpy(test["X"]).cuda())
     assert np.max(np.abs(dec.cpu().numpy()[:, 0] - g["dec"])) < 1e-3
+
+
+@pytest.mark.parametrize("case", ["c1_simt", "c2_csr", "c5_tensor", "c5_tensor_sequential"])
+def test_row_cache_budget_does_not_change_results(capi, case):
+    """Kernel-row cache: with the minimum row buffer (working set + one batch) and with room for every row the
+    solver takes the same steps - alpha and f identical bit for bit - and the large cache serves hits."""
+    import torch
+    if case == "c1_simt":
+        prob, n = synth.config1(6000), 6000
+    elif case == "c2_csr":
+        prob, n = synth.config2(5000), 5000
+    else:
+        prob, n = synth.config5(6000, d=256), 6000
+    y = torch.from_numpy(binary_labels(prob)).cuda()
+    out = []
+    try:
+        for budget in (0, 1 << 40):
+            capi.set_row_cache_bytes(budget)
+            km = device_matrix(capi, prob, n)
+            alpha = torch.zeros(n, dtype=torch.float64, device="cuda")
+            f = -y.to(torch.float64)
+            sv = capi.Solver(km, y, alpha, f, 1e-3, prob["C"], prob["C"], 1024)
+            if case.endswith("sequential"):
+                sv.set_overlap(False)
+            done = False
+            while not done:
+                done = sv.iterate(50)
+            rho, st = sv.finish()
+            out.append((alpha.cpu().numpy(), f.cpu().numpy(), rho, st))
+            sv.close(); km.close()
+    finally:
+        capi.set_row_cache_bytes(-1)
+    (a0, f0, r0, s0), (a1, f1, r1, s1) = out
+    assert np.array_equal(a0, a1) and np.array_equal(f0, f1) and r0 == r1
+    assert s0["outer_iters"] == s1["outer_iters"] and s0["local_iters"] == s1["local_iters"]
+    assert s0["cache_rows"] == 1024 + 512 and s1["cache_rows"] == n
+    assert s1["cache_hits"] + s1["cache_misses"] == s1["kernel_rows"]
+    assert s1["cache_misses"] <= n and s1["cache_hits"] >= s0["cache_hits"]
+    if s1["outer_iters"] > 12:
+        assert s1["cache_hits"] > 0

@@ -19,7 +19,7 @@ HOST, DEVICE = 0, 1
 
 # every symbol include/thundersvm_b200.h declares
 EXPORTS = [
-    "tsvm_release_cached_memory",
+    "tsvm_release_cached_memory", "tsvm_set_row_cache_bytes",
     "tsvm_last_error", "tsvm_abi_version", "tsvm_km_create_dense", "tsvm_km_create_csr", "tsvm_km_destroy",
     "tsvm_km_n_instances", "tsvm_km_n_features", "tsvm_km_nnz", "tsvm_km_is_dense", "tsvm_km_diag_dev",
     "tsvm_km_self_dot_dev", "tsvm_km_rows_by_index", "tsvm_km_rows_by_instances_dense",
@@ -35,7 +35,9 @@ class SolveStats(C.Structure):
     _fields_ = [("outer_iters", C.c_longlong), ("local_iters", C.c_longlong), ("final_diff", C.c_double),
                 ("objective", C.c_double), ("seconds_select", C.c_double), ("seconds_rows", C.c_double),
                 ("seconds_local", C.c_double), ("seconds_update", C.c_double), ("seconds_total", C.c_double),
-                ("kernel_rows", C.c_longlong), ("gpu_launches", C.c_longlong)]
+                ("kernel_rows", C.c_longlong), ("gpu_launches", C.c_longlong), ("cache_hits", C.c_longlong),
+                ("cache_misses", C.c_longlong), ("cache_rows", C.c_longlong), ("row_blocks", C.c_longlong),
+                ("row_blocks_saved", C.c_longlong)]
 
     def as_dict(self):
         return {k: getattr(self, k) for k, _ in self._fields_}
@@ -62,6 +64,8 @@ def lib():
     L.tsvm_abi_version.restype = i
     L.tsvm_release_cached_memory.restype = None
     L.tsvm_release_cached_memory.argtypes = []
+    L.tsvm_set_row_cache_bytes.restype = None
+    L.tsvm_set_row_cache_bytes.argtypes = [ll]
     L.tsvm_km_create_dense.argtypes = [vp, i, i, i, i, i, i, f, f, vp, C.POINTER(vp)]
     L.tsvm_km_create_csr.argtypes = [vp, vp, vp, i, i, i, i, i, f, f, vp, C.POINTER(vp)]
     L.tsvm_km_destroy.argtypes = [vp]
@@ -251,6 +255,11 @@ class KernelMatrix:
             self.close()
         except Exception:
             pass
+
+
+def set_row_cache_bytes(nbytes):
+    """Budget of the kernel-row cache of solvers created from now on (< 0: default, 0: minimum)."""
+    lib().tsvm_set_row_cache_bytes(int(nbytes))
 
 
 def working_set_size(n, d, max_mem_bytes=8192 << 20, used_bytes=0):

@@ -215,6 +215,10 @@ struct tsvm_km {
     int wt_ld = 0;
     float *sd_rows = nullptr;       // self dots of the requested rows [w_cap]
     int reserve_clusters = 0;       // SM pairs the pair engine leaves free (a concurrent stream's kernels run there)
+    // Set by a caller around tsvm_km_rows_by_index-style launches (the solver's row cache): the number of
+    // requested rows is read from the device (at most the q of the call) and requested row i goes to row
+    // rows_slot_dev[i] of the output buffer instead of row i.
+    const int *rows_m_dev = nullptr, *rows_slot_dev = nullptr;
     int *status_dev = nullptr;      // device status word written by kernels with bounded waits
     int *status_host = nullptr;     // pinned mirror
 };
@@ -225,8 +229,9 @@ bool km_pair_engine(tsvm_km *km, cudaStream_t st);
 size_t km_plane_row_bytes(const tsvm_km *km);
 tsvm_status km_stage_rows_by_index(tsvm_km *km, const int *idx_dev, int q, cudaStream_t st);
 tsvm_status km_rows_staged(tsvm_km *km, int q, float *out, long long ld_out, cudaStream_t st);
-tsvm_status km_gather_planes(tsvm_km *km, const int *ids_dev, int m, float *hi, float *lo, float *sd, float *unscale,
-                             cudaStream_t st);
+// operand planes of instances ids[0..m) (m_dev: only the first *m_dev of them, read on the device)
+tsvm_status km_gather_planes(tsvm_km *km, const int *ids_dev, int m, const int *m_dev, float *hi, float *lo, float *sd,
+                             float *unscale, cudaStream_t st);
 tsvm_status km_rows_staged_on(tsvm_km *km, const InstancePlanes &X, int q, float *out, long long ld_out,
                               cudaStream_t st);
 tsvm_status km_rows_planes_on(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int q, float *out,

@@ -47,12 +47,17 @@ constexpr uint32_t EPI_CONST_BYTES = EPI_WARPS * 2 * COLS_PER_THREAD * 4;
 // prediction form: up to PRED_NC_SMEM coefficients of every epilogue thread's own instance (thread-private columns)
 constexpr int PRED_NC_SMEM = 9;
 constexpr uint32_t PRED_BYTES = PRED_NC_SMEM * EPI_WARPS * 32 * 4;
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_STAGE_BYTES + EPI_CONST_BYTES;
-constexpr uint32_t SMEM_BYTES_PREDICT = SMEM_BYTES + PRED_BYTES;
+// kernel-row form: output row (slot of the caller's row buffer) of every requested row, per epilogue warp
+constexpr uint32_t SLOT_BYTES = EPI_WARPS * COLS_PER_THREAD * 4;
+constexpr uint32_t SMEM_BASE = STAGES * STAGE_BYTES + 1024 + 256 + EPI_STAGE_BYTES + EPI_CONST_BYTES;
+constexpr uint32_t SMEM_BYTES = SMEM_BASE + SLOT_BYTES;
+constexpr uint32_t SMEM_BYTES_PREDICT = SMEM_BASE + PRED_BYTES;
+static_assert(SMEM_BYTES <= 227 * 1024, "kernel-row form does not fit the shared memory of an SM");
 static_assert(SMEM_BYTES_PREDICT <= 227 * 1024, "prediction form does not fit the shared memory of an SM");
 constexpr uint32_t TMEM_COLS = 512;
-// D=F32, K-major, N=256, M=256 (two CTAs x 128); A=B=TF32 (format 2) or F16 (format 0)
-constexpr uint32_t IDESC_SHAPE = (1u << 4) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
+// D=F32, K-major, M=256 (two CTAs x 128); A=B=TF32 (format 2) or F16 (format 0)
+// (the N field, bits 17.., is added per row block: a block's last rows may need fewer than 256 columns)
+constexpr uint32_t IDESC_SHAPE = (1u << 4) | ((uint32_t) (256 >> 4) << 24);
 constexpr uint32_t IDESC_TF32 = IDESC_SHAPE | (2u << 7) | (2u << 10);
 constexpr uint32_t IDESC_F16 = IDESC_SHAPE;
 }  // namespace tc2
@@ -80,20 +85,23 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
 }
+// idesc_n: the instruction descriptor's N field ((N >> 3) << 17); a row block with few requested rows left
+// issues narrower MMAs
 template <bool F16>
-__device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate,
+                                          uint32_t idesc_n) {
     if constexpr (F16)
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
             "setp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(tc2::IDESC_F16), "r"(accumulate) : "memory");
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(tc2::IDESC_F16 | idesc_n), "r"(accumulate) : "memory");
     else
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
             "setp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(tc2::IDESC_TF32), "r"(accumulate) : "memory");
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(tc2::IDESC_TF32 | idesc_n), "r"(accumulate) : "memory");
 }
 // arrives on the barrier at a shared::cluster address once all MMAs issued so far have retired
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
@@ -120,19 +128,35 @@ struct PredictArgs {
     int n_classes, n_pairs;
 };
 
+// Optional indirections of the kernel-row form, both read on the device so that a caller can decide them
+// without a host round trip: the number of requested rows actually wanted (at most the m the launch was
+// sized for) and, per requested row, the row of `out` it is written to.
+struct RowsExtra {
+    const int *m_dev;
+    const int *row_slot;
+};
+
 __device__ __forceinline__ int pair_index(int n_classes, int i, int j) {      // i < j, pairs ordered (0,1),(0,2),...
     return i * (2 * n_classes - i - 1) / 2 + (j - i - 1);
+}
+
+// Columns (requested rows) of row block nb that the MMAs cover: all 256, or the rows left rounded up to 32
+__device__ __forceinline__ int block_columns(int m, int nb) {
+    const int left = m - nb * tc2::BN;
+    return left >= tc2::BN ? tc2::BN : ((left + 31) & ~31);
 }
 
 template <int EPI, bool F16, bool PREDICT>
 __global__ void __launch_bounds__(tc2::THREADS, 1)
 dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
                       const __grid_constant__ CUtensorMap map_whi, const __grid_constant__ CUtensorMap map_wlo,
-                      int n, int m, int row_len, const float *__restrict__ sd, const float *__restrict__ sd_rows,
+                      int n, int m_launch, int row_len, const float *__restrict__ sd, const float *__restrict__ sd_rows,
                       const float *__restrict__ x_unscale, const float *__restrict__ w_unscale,
                       KernelFn fn, float *__restrict__ out, long long ld_out, int *__restrict__ status,
-                      const PredictArgs pa) {
+                      const PredictArgs pa, const RowsExtra ex) {
     using namespace tc2;
+    // the same value in every thread of the grid: the launch's m, or the smaller count found on the device
+    const int m = ex.m_dev ? min(m_launch, max(*ex.m_dev, 0)) : m_launch;
     constexpr int BK = F16 ? 64 : 32;          // elements per k slab
     constexpr int PROMO = F16 ? TSVM_PROMO : 1;   // k slabs summed in tensor memory before the FP32 promotion
     extern __shared__ uint8_t smem_raw[];
@@ -184,7 +208,8 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                         const uint32_t base = ring + stage * STAGE_BYTES;
                         const uint32_t leader_full = mapa_u32(full_bar + 8 * stage, 0);
                         if (rank == 0) mbar_expect_tx(full_bar + 8 * stage, 2 * STAGE_BYTES);
-                        const int xrow = pt * 2 * BM + (int) rank * BM, wrow = nb * BN + (int) rank * BN_HALF;
+                        // this CTA's half of the block's requested rows (a narrow last block has narrow halves)
+                        const int xrow = pt * 2 * BM + (int) rank * BM, wrow = nb * BN + (int) rank * (block_columns(m, nb) >> 1);
                         tma_load_2d_pair(base, &map_xhi, leader_full, kb * BK, xrow);
                         tma_load_2d_pair(base + A_BYTES, &map_xlo, leader_full, kb * BK, xrow);
                         tma_load_2d_pair(base + 2 * A_BYTES, &map_whi, leader_full, kb * BK, wrow);
@@ -198,7 +223,8 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
         if (lane == 0 && rank == 0) {
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (int item = cluster_id; item < n_items && ok; item += n_clusters)
+            for (int item = cluster_id; item < n_items && ok; item += n_clusters) {
+                    const uint32_t idesc_n = (uint32_t) (block_columns(m, item % n_blocks) >> 3) << 17;
                     for (int kb = 0; kb < k_blocks; ++kb) {
                         const bool unit_start = kb % PROMO == 0, unit_end = kb % PROMO == PROMO - 1 || kb == k_blocks - 1;
                         if (unit_start && !mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, 2)) { ok = false; break; }
@@ -210,14 +236,14 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                         for (int k = 0; k < K_STEPS; ++k) {
                             const uint32_t koff = k * 32;
                             umma_pair<F16>(d_tmem, smem_desc_sw128(base + A_BYTES + koff),
-                                           smem_desc_sw128(base + 2 * A_BYTES + koff), k != 0 || !unit_start);
+                                           smem_desc_sw128(base + 2 * A_BYTES + koff), k != 0 || !unit_start, idesc_n);
                             umma_pair<F16>(d_tmem, smem_desc_sw128(base + koff),
-                                           smem_desc_sw128(base + 2 * A_BYTES + B_BYTES + koff), 1);
+                                           smem_desc_sw128(base + 2 * A_BYTES + B_BYTES + koff), 1, idesc_n);
                         }
 #pragma unroll
                         for (int k = 0; k < K_STEPS; ++k) {
                             const uint32_t koff = k * 32;
-                            umma_pair<F16>(d_tmem, smem_desc_sw128(base + koff), smem_desc_sw128(base + 2 * A_BYTES + koff), 1);
+                            umma_pair<F16>(d_tmem, smem_desc_sw128(base + koff), smem_desc_sw128(base + 2 * A_BYTES + koff), 1, idesc_n);
                         }
                         // stage free / slab complete, signalled in both CTAs
                         umma_commit_pair(mapa_u32(empty_bar + 8 * stage, 0));
@@ -229,6 +255,7 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                         }
                     }
+            }
         }
     }
     } else {
@@ -238,6 +265,8 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
         float *priv = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256) + (warp - EPI_WARP0) * 32 + lane;
         float *rowc = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES) +
                       (warp - EPI_WARP0) * 2 * COLS_PER_THREAD;
+        int *slotc = reinterpret_cast<int *>(ring_ptr + STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES + EPI_CONST_BYTES) +
+                     (warp - EPI_WARP0) * COLS_PER_THREAD;
         // prediction form: the coefficients of the thread's own instance, one thread-private column
         float *coef_priv = reinterpret_cast<float *>(ring_ptr + STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES + EPI_CONST_BYTES) +
                            (warp - EPI_WARP0) * 32 + lane;
@@ -249,6 +278,7 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
             const int j = pt * 2 * BM + (int) rank * BM + quarter * 32 + lane;
             const float sdj = j < n ? sd[j] : 0.0f;
             const float uxj = (F16 && j < n) ? x_unscale[j] : 1.0f;
+            const int n_cols = block_columns(m, nb);
             int cls_own = 0, cls_lo = 0, cls_hi = -1;
             float coef_one = 0.0f;
             if constexpr (PREDICT) {
@@ -271,6 +301,9 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                         asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(rowc + c)), "l"(sd_rows + i0 + c) : "memory");
                         if constexpr (F16)
                             asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(rowc + COLS_PER_THREAD + c)), "l"(w_unscale + i0 + c) : "memory");
+                        if constexpr (!PREDICT)
+                            if (ex.row_slot)
+                                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(slotc + c)), "l"(ex.row_slot + i0 + c) : "memory");
                     }
                 }
                 float sum[COLS_PER_THREAD];
@@ -282,6 +315,7 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                     const uint32_t taddr = tmem_base + ((uint32_t) (quarter * 32) << 16) + acc * BN + half * COLS_PER_THREAD;
 #pragma unroll
                     for (int c0 = 0; c0 < COLS_PER_THREAD; c0 += 32) {
+                        if (half * COLS_PER_THREAD + c0 >= n_cols) break;      // columns the narrow MMAs did not write
                         uint32_t v[32];
                         tmem_ld32(taddr + c0, v);
 #pragma unroll
@@ -324,6 +358,7 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                 }
 #pragma unroll 1
                 for (int ch = 0; ch < COLS_PER_THREAD / EPI_CHUNK; ++ch) {
+                    if (half * COLS_PER_THREAD + ch * EPI_CHUNK >= n_cols) break;
                     switch (ch) {           // register indices must be constants: one short case per chunk
                         case 0: stage_chunk<0>(sum, priv); break;
                         case 1: stage_chunk<1>(sum, priv); break;
@@ -338,12 +373,21 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                     if constexpr (!PREDICT) {
                         if (j < n) {
                             const int lim = m - (i0 + cbase) < EPI_CHUNK ? m - (i0 + cbase) : EPI_CHUNK;
-                            float *o = out + (size_t) (i0 + cbase) * ld_out + j;
+                            if (!ex.row_slot) {
+                                float *o = out + (size_t) (i0 + cbase) * ld_out + j;
 #pragma unroll 8
-                            for (int c = 0; c < lim; ++c) {
-                                float dot = priv[c * (EPI_WARPS * 32)];
-                                if constexpr (F16) dot = dot * uxj * rowc[COLS_PER_THREAD + cbase + c];
-                                o[(size_t) c * ld_out] = epilogue_value<EPI>(fn, dot, rowc[cbase + c], sdj);
+                                for (int c = 0; c < lim; ++c) {
+                                    float dot = priv[c * (EPI_WARPS * 32)];
+                                    if constexpr (F16) dot = dot * uxj * rowc[COLS_PER_THREAD + cbase + c];
+                                    o[(size_t) c * ld_out] = epilogue_value<EPI>(fn, dot, rowc[cbase + c], sdj);
+                                }
+                            } else {
+#pragma unroll 8
+                                for (int c = 0; c < lim; ++c) {
+                                    float dot = priv[c * (EPI_WARPS * 32)];
+                                    if constexpr (F16) dot = dot * uxj * rowc[COLS_PER_THREAD + cbase + c];
+                                    out[(size_t) slotc[cbase + c] * ld_out + j] = epilogue_value<EPI>(fn, dot, rowc[cbase + c], sdj);
+                                }
                             }
                         }
                     } else {
@@ -435,7 +479,7 @@ tsvm_status make_map(CUtensorMap *map, const void *ptr, int rows, int row_len, l
 
 template <int EPI, bool F16, bool PREDICT>
 static tsvm_status launch_pair_kernel(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int m, float *out,
-                                      long long ld_out, const PredictArgs &pa, cudaStream_t st) {
+                                      long long ld_out, const PredictArgs &pa, const RowsExtra &ex, cudaStream_t st) {
     auto kernel = dense_rows_tc2_kernel<EPI, F16, PREDICT>;
     constexpr uint32_t smem_bytes = PREDICT ? tc2::SMEM_BYTES_PREDICT : tc2::SMEM_BYTES;
     static int clusters_of_device[MAX_DEVICES] = {0};      // per instantiation and per device ordinal
@@ -476,31 +520,31 @@ static tsvm_status launch_pair_kernel(tsvm_km *km, const InstancePlanes &X, cons
     cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(tc2::THREADS); cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
     TSVM_CUDA(cudaLaunchKernelEx(&cfg, kernel, mxh, mxl, mwh, mwl, X.n, m, len, X.sd, W.sd, X.unscale, W.unscale,
-                                 km->fn, out, ld_out, km->status_dev, pa));
+                                 km->fn, out, ld_out, km->status_dev, pa, ex));
     count_launch();
     return TSVM_OK;
 }
 
 template <bool PREDICT>
 static tsvm_status launch_pair_any(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int m, float *out,
-                                   long long ld_out, const PredictArgs &pa, cudaStream_t st) {
+                                   long long ld_out, const PredictArgs &pa, const RowsExtra &ex, cudaStream_t st) {
     TSVM_REQUIRE(km->plane_kind == 1 || km->plane_kind == 2, "tensor engine: operand planes are not built");
     const int epi = epilogue_kind(km->fn);
     if (km->plane_kind == 2) {
-        if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, true, PREDICT>(km, X, W, m, out, ld_out, pa, st);
-        if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, true, PREDICT>(km, X, W, m, out, ld_out, pa, st);
-        return launch_pair_kernel<EPI_GENERIC, true, PREDICT>(km, X, W, m, out, ld_out, pa, st);
+        if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, true, PREDICT>(km, X, W, m, out, ld_out, pa, ex, st);
+        if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, true, PREDICT>(km, X, W, m, out, ld_out, pa, ex, st);
+        return launch_pair_kernel<EPI_GENERIC, true, PREDICT>(km, X, W, m, out, ld_out, pa, ex, st);
     }
-    if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, false, PREDICT>(km, X, W, m, out, ld_out, pa, st);
-    if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, false, PREDICT>(km, X, W, m, out, ld_out, pa, st);
-    return launch_pair_kernel<EPI_GENERIC, false, PREDICT>(km, X, W, m, out, ld_out, pa, st);
+    if (epi == EPI_RBF) return launch_pair_kernel<EPI_RBF, false, PREDICT>(km, X, W, m, out, ld_out, pa, ex, st);
+    if (epi == EPI_LINEAR) return launch_pair_kernel<EPI_LINEAR, false, PREDICT>(km, X, W, m, out, ld_out, pa, ex, st);
+    return launch_pair_kernel<EPI_GENERIC, false, PREDICT>(km, X, W, m, out, ld_out, pa, ex, st);
 }
 
 // Kernel values of the m staged requested rows against a set of instances given by its operand planes
 // (kind 1 = TF32 words, 2 = row-scaled FP16, the handle's plane kind), self dots and 1/scale.
 tsvm_status launch_dense_tc2_planes(tsvm_km *km, const InstancePlanes &X, const RowPlanes &W, int m, float *out,
                                     long long ld_out, cudaStream_t st) {
-    return launch_pair_any<false>(km, X, W, m, out, ld_out, PredictArgs{}, st);
+    return launch_pair_any<false>(km, X, W, m, out, ld_out, PredictArgs{}, RowsExtra{km->rows_m_dev, km->rows_slot_dev}, st);
 }
 
 // Prediction form: the m staged rows are test rows, the kernel matrix holds the support vectors; adds
@@ -510,7 +554,7 @@ tsvm_status launch_dense_tc2_predict(tsvm_km *km, int m, const double *coef_dev,
     const InstancePlanes all{km->Xhi, km->Xlo, km->self_dot, km->x_unscale, km->n};
     const RowPlanes staged{km->Whi, km->Wlo, km->sd_rows, km->w_unscale};
     const PredictArgs pa{coef_dev, sv_class_dev, dec_dev, n_classes, n_classes * (n_classes - 1) / 2};
-    return launch_pair_any<true>(km, all, staged, m, nullptr, 0, pa, st);
+    return launch_pair_any<true>(km, all, staged, m, nullptr, 0, pa, RowsExtra{nullptr, nullptr}, st);
 }
 
 // Requested rows = the m rows staged in the handle's scratch.

@@ -92,9 +92,13 @@ tsvm_status pool_alloc(void **p, size_t bytes) {
 // that owns one of the blocks (the owning device, which need not be the caller's current one), then all of
 // them go to the free lists. Cached bytes above the cap go back to the driver, largest blocks first.
 static size_t pool_cache_cap() {
+    // TSVM_POOL_CACHE_MB, else 60 % of the current device's memory (a solver's row cache is the largest block and
+    // should come back from the pool when the next solver of the same problem is created)
     static const size_t cap = [] {
-        const char *e = getenv("TSVM_POOL_CACHE_MB");
-        return (size_t) (e ? strtoull(e, nullptr, 10) : 32768ull) << 20;
+        if (const char *e = getenv("TSVM_POOL_CACHE_MB")) return (size_t) strtoull(e, nullptr, 10) << 20;
+        size_t free_b = 0, total_b = 0;
+        if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) { cudaGetLastError(); return (size_t) 32 << 30; }
+        return (size_t) ((double) total_b * 0.6);
     }();
     return cap;
 }
@@ -321,9 +325,9 @@ __global__ void split_rows_kernel(const float *__restrict__ X, int n, int d, int
 // Requested row i = X[idx[i]][0..d) (zero padded to the destination's row length); sd_rows[i].
 __global__ void gather_rows_dense_kernel(const float *__restrict__ X, int ld, int d, const int *__restrict__ idx,
                                          int m, const float *__restrict__ sd, RowDst dst,
-                                         float *__restrict__ sd_rows) {
+                                         float *__restrict__ sd_rows, const int *__restrict__ m_dev) {
     int i = blockIdx.x;
-    if (i >= m) return;
+    if (i >= m || (m_dev && i >= *m_dev)) return;
     const int r = idx[i];
     const int dr = r >= 0 ? d : 0;           // id -1 (an empty working-set slot) is staged as an all-zero row
     const float *x = X + (size_t) (r >= 0 ? r : 0) * ld;
@@ -391,9 +395,9 @@ __global__ void scatter_csr_to_w_kernel(const float *__restrict__ val, const int
 __global__ void scatter_csr_to_wt_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr,
                                          const int *__restrict__ col, const int *__restrict__ idx, int m, int d,
                                          int wt_ld, float *__restrict__ WT, const float *__restrict__ sd,
-                                         float *__restrict__ sd_rows, bool clear) {
+                                         float *__restrict__ sd_rows, bool clear, const int *__restrict__ m_dev) {
     int i = blockIdx.x;
-    if (i >= m) return;
+    if (i >= m || (m_dev && i >= *m_dev)) return;
     int r = idx ? idx[i] : i;
     if (r < 0) {                             // an empty working-set slot: an all-zero row
         if (!clear && sd && threadIdx.x == 0) sd_rows[i] = 0.0f;
@@ -430,9 +434,9 @@ __global__ void gather_planes_kernel(const float *__restrict__ Xhi, const float 
                                      const int *__restrict__ ids, int m, const float *__restrict__ sd,
                                      const float *__restrict__ x_unscale, float *__restrict__ hi,
                                      float *__restrict__ lo, float *__restrict__ sd_out,
-                                     float *__restrict__ unscale_out) {
+                                     float *__restrict__ unscale_out, const int *__restrict__ m_dev) {
     const int i = blockIdx.x;
-    if (i >= m) return;
+    if (i >= m || (m_dev && i >= *m_dev)) return;
     const int r = ids[i] >= 0 ? ids[i] : 0;      // an empty slot copies some row; its y = 0 keeps it inert
     const size_t vecs = row_bytes / 16;
     const uint4 *sh = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(Xhi) + (size_t) r * row_bytes);
@@ -446,12 +450,15 @@ __global__ void gather_planes_kernel(const float *__restrict__ Xhi, const float 
 // ---- CUDA-core dense engine: out[i][j] = kfn(sum_k W[i][k] X[j][k]) -------------------------
 // 64 instances x 64 requested rows per block, 16-wide k slabs, 4x4 outputs per thread.
 __global__ void __launch_bounds__(256)
-dense_rows_simt_kernel(const float *__restrict__ X, int ldx, int n, const float *__restrict__ W, int ldw, int m,
+dense_rows_simt_kernel(const float *__restrict__ X, int ldx, int n, const float *__restrict__ W, int ldw, int m_launch,
                        int d_pad, const float *__restrict__ sd, const float *__restrict__ sd_rows, KernelFn fn,
-                       float *__restrict__ out, long long ld_out) {
+                       float *__restrict__ out, long long ld_out, const int *__restrict__ m_dev,
+                       const int *__restrict__ row_slot) {
     __shared__ float xs[16][64 + 4];
     __shared__ float wsm[16][64 + 4];
+    const int m = m_dev ? min(m_launch, max(*m_dev, 0)) : m_launch;     // the count found on the device, if any
     const int j0 = blockIdx.x * 64, i0 = blockIdx.y * 64;
+    if (i0 >= m) return;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     float acc[4][4];
 #pragma unroll
@@ -483,10 +490,11 @@ dense_rows_simt_kernel(const float *__restrict__ X, int ldx, int n, const float 
         int i = i0 + ty + 16 * b;
         if (i >= m) continue;
         float sdi = sd_rows[i];
+        const size_t orow = row_slot ? (size_t) row_slot[i] : (size_t) i;
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
             int j = j0 + tx + 16 * a;
-            if (j < n) out[(size_t) i * ld_out + j] = apply_kernel(fn, acc[b][a], sdi, sd[j]);
+            if (j < n) out[orow * ld_out + j] = apply_kernel(fn, acc[b][a], sdi, sd[j]);
         }
     }
 }
@@ -500,9 +508,11 @@ dense_rows_simt_kernel(const float *__restrict__ X, int ldx, int n, const float 
 template <int NV>
 __global__ void __launch_bounds__(256)
 csr_rows_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr, const int *__restrict__ col, int n,
-                const float *__restrict__ WT, int wt_ld, int m, const float *__restrict__ sd,
-                const float *__restrict__ sd_rows, KernelFn fn, float *__restrict__ out, long long ld_out) {
+                const float *__restrict__ WT, int wt_ld, int m_launch, const float *__restrict__ sd,
+                const float *__restrict__ sd_rows, KernelFn fn, float *__restrict__ out, long long ld_out,
+                const int *__restrict__ m_dev, const int *__restrict__ row_slot) {
     extern __shared__ float tile[];   // [NV*128][33]
+    const int m = m_dev ? min(m_launch, max(*m_dev, 0)) : m_launch;     // the count found on the device, if any
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int j0 = blockIdx.x * 32;
     for (int jj = warp; jj < 32; jj += 8) {
@@ -545,7 +555,8 @@ csr_rows_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr, 
     const int j = j0 + lane;
     const float sdj = j < n ? sd[j] : 0.0f;
     for (int c = warp; c < m; c += 8) {
-        if (j < n) out[(size_t) c * ld_out + j] = apply_kernel(fn, tile[c * 33 + lane], sd_rows[c], sdj);
+        const size_t orow = row_slot ? (size_t) row_slot[c] : (size_t) c;
+        if (j < n) out[orow * ld_out + j] = apply_kernel(fn, tile[c * 33 + lane], sd_rows[c], sdj);
     }
 }
 
@@ -574,8 +585,8 @@ static tsvm_status ensure_scratch(tsvm_km *km, int m) {
     return TSVM_OK;
 }
 
-// engine: 0 = automatic, 1 = CUDA cores, 2 / 3 = tensor cores on TF32 planes (one CTA per tile / CTA
-// pairs), 4 = tensor cores on row-scaled FP16 planes (CTA pairs; what "automatic" picks for d_pad > 32)
+// engine: 0 = automatic, 1 = CUDA cores, 3 (and its old alias 2) = tensor cores on TF32 planes, 4 = tensor
+// cores on row-scaled FP16 planes (what "automatic" picks for d_pad > 32); both tensor forms run on CTA pairs
 static inline bool use_tensor_engine(const tsvm_km *km) {
     return km->engine >= 2 || (km->engine == 0 && km->d_pad > 32);
 }
@@ -631,7 +642,7 @@ static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out,
         if (use_tensor_engine(km)) return launch_dense_tc(km, m, out, ld_out, st);
         dim3 grid(ceil_div(km->n, 64), ceil_div(m, 64));
         TSVM_LAUNCH(dense_rows_simt_kernel, grid, 256, 0, st, km->X, km->ldx, km->n, km->W, km->d_pad, m, km->d_pad,
-                    km->self_dot, km->sd_rows, km->fn, out, ld_out);
+                    km->self_dot, km->sd_rows, km->fn, out, ld_out, km->rows_m_dev, km->rows_slot_dev);
         return TSVM_OK;
     }
     const int nv = ceil_div(m, 128);
@@ -642,7 +653,8 @@ static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out,
         TSVM_CUDA(cudaFuncSetAttribute(csr_rows_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
                                        (int) smem));                                                             \
         TSVM_LAUNCH(csr_rows_kernel<NV>, grid, 256, smem, st, km->val, km->row_ptr, km->col, km->n, km->WT,      \
-                    km->wt_ld, m, km->self_dot, km->sd_rows, km->fn, out, ld_out);                               \
+                    km->wt_ld, m, km->self_dot, km->sd_rows, km->fn, out, ld_out, km->rows_m_dev,                \
+                    km->rows_slot_dev);                                                                          \
     }
     if (nv <= 1) CSR_CASE(1)
     else if (nv <= 2) CSR_CASE(2)
@@ -661,7 +673,7 @@ tsvm_status launch_dense_tc2_on(tsvm_km *km, const InstancePlanes &X, int m, flo
 // True when kernel rows of this matrix run on the CTA-pair tensor engine, whose requested-row staging and
 // launch can be issued separately and against a caller-chosen subset of instances.
 bool km_pair_engine(tsvm_km *km, cudaStream_t st) {
-    if (!km->dense || !use_tensor_engine(km) || km->engine == 2) return false;
+    if (!km->dense || !use_tensor_engine(km)) return false;
     return ensure_planes(km, st) == TSVM_OK && km->plane_kind != 0;
 }
 
@@ -673,7 +685,7 @@ tsvm_status km_stage_rows_by_index(tsvm_km *km, const int *idx_dev, int q, cudaS
     TSVM_TRY(ensure_scratch(km, q));
     TSVM_TRY(ensure_planes(km, st));
     TSVM_LAUNCH(gather_rows_dense_kernel, q, 256, 0, st, km->X, km->ldx, km->d, idx_dev, q, km->self_dot, row_dst(km),
-                km->sd_rows);
+                km->sd_rows, km->rows_m_dev);
     return TSVM_OK;
 }
 
@@ -681,10 +693,10 @@ tsvm_status km_rows_staged(tsvm_km *km, int q, float *out, long long ld_out, cud
     return rows_common(km, q, out, ld_out, st);
 }
 
-tsvm_status km_gather_planes(tsvm_km *km, const int *ids_dev, int m, float *hi, float *lo, float *sd, float *unscale,
-                             cudaStream_t st) {
+tsvm_status km_gather_planes(tsvm_km *km, const int *ids_dev, int m, const int *m_dev, float *hi, float *lo, float *sd,
+                             float *unscale, cudaStream_t st) {
     TSVM_LAUNCH(gather_planes_kernel, m, 128, 0, st, km->Xhi, km->Xlo, km_plane_row_bytes(km), ids_dev, m,
-                km->self_dot, km->plane_kind == 2 ? km->x_unscale : nullptr, hi, lo, sd, unscale);
+                km->self_dot, km->plane_kind == 2 ? km->x_unscale : nullptr, hi, lo, sd, unscale, m_dev);
     return TSVM_OK;
 }
 
@@ -744,7 +756,7 @@ using namespace tsvm;
 extern "C" {
 
 const char *tsvm_last_error(void) { return tsvm::g_err; }
-int tsvm_abi_version(void) { return 1; }
+int tsvm_abi_version(void) { return 2; }
 void tsvm_release_cached_memory(void) { tsvm::pool_release(); }
 
 tsvm_status tsvm_km_create_dense(const float *X, int n, int d, int ld, int loc, int kernel_type, int degree,
@@ -846,15 +858,15 @@ tsvm_status tsvm_km_rows_by_index(tsvm_km *km, const int *idx_dev, int q, float 
     if (km->dense) {
         TSVM_TRY(ensure_planes(km, st));
         TSVM_LAUNCH(gather_rows_dense_kernel, q, 256, 0, st, km->X, km->ldx, km->d, idx_dev, q, km->self_dot,
-                    row_dst(km), km->sd_rows);
+                    row_dst(km), km->sd_rows, km->rows_m_dev);
         return rows_common(km, q, out_dev, ld_out, st);
     }
     TSVM_REQUIRE(q <= 1024, "CSR engine handles at most 1024 rows per call, got %d", q);
     TSVM_LAUNCH(scatter_csr_to_wt_kernel, q, 128, 0, st, km->val, km->row_ptr, km->col, idx_dev, q, km->d, km->wt_ld,
-                km->WT, km->self_dot, km->sd_rows, false);
+                km->WT, km->self_dot, km->sd_rows, false, km->rows_m_dev);
     TSVM_TRY(rows_common(km, q, out_dev, ld_out, st));
     TSVM_LAUNCH(scatter_csr_to_wt_kernel, q, 128, 0, st, km->val, km->row_ptr, km->col, idx_dev, q, km->d, km->wt_ld,
-                km->WT, nullptr, nullptr, true);
+                km->WT, nullptr, nullptr, true, km->rows_m_dev);
     return TSVM_OK;
 }
 
@@ -920,10 +932,10 @@ tsvm_status tsvm_km_rows_by_instances_csr(tsvm_km *km, const float *tval_dev, co
             TSVM_TRY(ensure_scratch(km, mm));
             TSVM_LAUNCH(self_dot_seq_csr_kernel, ceil_div(mm, 128), 128, 0, st, tval_dev, rp, mm, km->sd_rows);
             TSVM_LAUNCH(scatter_csr_to_wt_kernel, mm, 128, 0, st, tval_dev, rp, tcol_dev, (const int *) nullptr, mm,
-                        km->d, km->wt_ld, km->WT, (const float *) nullptr, (float *) nullptr, false);
+                        km->d, km->wt_ld, km->WT, (const float *) nullptr, (float *) nullptr, false, (const int *) nullptr);
             TSVM_TRY(rows_common(km, mm, o, ld_out, st));
             TSVM_LAUNCH(scatter_csr_to_wt_kernel, mm, 128, 0, st, tval_dev, rp, tcol_dev, (const int *) nullptr, mm,
-                        km->d, km->wt_ld, km->WT, (const float *) nullptr, (float *) nullptr, true);
+                        km->d, km->wt_ld, km->WT, (const float *) nullptr, (float *) nullptr, true, (const int *) nullptr);
         }
     }
     return TSVM_OK;

@@ -7,6 +7,7 @@
 #include <chrono>
 #include <limits.h>
 #include <string.h>
+#include <stdlib.h>
 #include <dlfcn.h>
 #include <vector>
 
@@ -740,13 +741,13 @@ __global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *
                                  const int *__restrict__ y, const double *__restrict__ f,
                                  const double *__restrict__ alpha, float *__restrict__ kww,
                                  float *__restrict__ diag_ws, int *__restrict__ y_ws, double *__restrict__ f_ws,
-                                 double *__restrict__ alpha_ws, int block_rows) {
+                                 double *__restrict__ alpha_ws, int block_rows, const int *__restrict__ row_slot) {
     const int a = blockIdx.x;                      // logical slot of the row
     // rows >= block_rows of the block are written by someone else (the overlapped iteration computes them
     // directly); the slot vectors are gathered for every slot
     // a slot without an instance (id -1: fewer eligible instances than slots) is inert: y = 0 puts it in no set
     if (a < block_rows) {
-        const float *row = rows + (size_t) phys_row(a, q, first_half_phys) * ld;
+        const float *row = rows + (size_t) (row_slot ? row_slot[a] : phys_row(a, q, first_half_phys)) * ld;
         for (int b = threadIdx.x; b < ws; b += blockDim.x) {
             const int id = ids[b];
             kww[(size_t) a * ws + b] = id >= 0 ? row[id] : 0.0f;
@@ -760,6 +761,169 @@ __global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *
 }
 
 // =================================================================================================
+// Kernel-row cache: least-recently-used rows kept in HBM
+// =================================================================================================
+// The reference keeps only the previous iteration's q rows (csmosolver.cpp:69,75). Here the row buffer has
+// room for `cap` rows (as many as the memory budget allows, at least ws + q). A directory on the device maps
+// instance -> row (slot_of), row -> instance (inst_of) and row -> outer iteration of its last use (stamp).
+// After every selection one block looks the new members up: a hit only points the member's slot at the cached
+// row; the misses are compacted into the list the kernel-row engine then computes, and each gets the row of a
+// victim - the rows with the oldest stamps that do not belong to the current working set, found with a
+// histogram over the stamps; ties go to the lower row number, so the choice does not depend on thread timing.
+// Everything stays on the device: the engine reads the number of misses from memory.
+constexpr int CACHE_THREADS = 1024, CACHE_BINS = 2048;
+enum { CACHE_N_MISS = 0, CACHE_HITS = 1, CACHE_MISSES = 2, CACHE_BLOCKS = 3, CACHE_BLOCKS_SAVED = 4, CACHE_CTRS = 8 };
+
+__device__ __forceinline__ int cache_bin(int stamp, int now) {
+    // older -> smaller bin; never-used rows (stamp 0) are the oldest; rows used in this iteration are not candidates
+    if (stamp <= 0) return 0;
+    const int age = now - stamp;
+    return age >= CACHE_BINS - 1 ? 0 : CACHE_BINS - 1 - age;
+}
+
+__global__ void __launch_bounds__(CACHE_THREADS, 1)
+cache_assign_kernel(const int *__restrict__ ids, int t0, int n_new, int now, int *__restrict__ slot_of,
+                    int *__restrict__ inst_of, int *__restrict__ stamp, int cap, int *__restrict__ row_slot,
+                    int *__restrict__ miss_ids, int *__restrict__ miss_slot, int *__restrict__ victims,
+                    long long *__restrict__ ctr, int row_block) {
+    __shared__ int hist[CACHE_BINS];
+    __shared__ int miss_t[CACHE_THREADS];
+    __shared__ int wsum[32], wpre_b[32], wpre_sel[32];
+    __shared__ int n_miss_s, thr_bin, need_s, n_hit_s;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // the members that stay move to the front; their rows are in use now
+    int keep = 0;
+    if (tid < t0) keep = row_slot[t0 + tid];
+    for (int b = tid; b < CACHE_BINS; b += CACHE_THREADS) hist[b] = 0;
+    if (tid == 0) { n_miss_s = 0; n_hit_s = 0; }
+    __syncthreads();
+    if (tid < t0) { row_slot[tid] = keep; if (ids[tid] >= 0) stamp[keep] = now; }
+    // look the new members up; misses are compacted in member order
+    int id = -1, s = -1;
+    if (tid < n_new) {
+        id = ids[t0 + tid];
+        s = id >= 0 ? slot_of[id] : -1;
+        if (id < 0) row_slot[t0 + tid] = 0;            // an empty working-set slot is inert: any row will do
+        else if (s >= 0) { row_slot[t0 + tid] = s; stamp[s] = now; }
+    }
+    const bool miss = tid < n_new && id >= 0 && s < 0;
+    const unsigned mb = __ballot_sync(0xffffffffu, miss);
+    if (lane == 0) wsum[warp] = __popc(mb);
+    const unsigned hb = __ballot_sync(0xffffffffu, tid < n_new && id >= 0 && s >= 0);
+    if (lane == 0 && hb) atomicAdd(&n_hit_s, __popc(hb));
+    __syncthreads();
+    if (warp == 0) {
+        const int v = wsum[lane];
+        int inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int a = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += a; }
+        wsum[lane] = inc - v;
+        if (lane == 31) n_miss_s = inc;
+    }
+    __syncthreads();
+    if (miss) miss_t[wsum[warp] + __popc(mb & ((1u << lane) - 1))] = tid;
+    const int n_miss = n_miss_s;
+    // (the stamps written above must be visible to the sweeps below)
+    __threadfence_block();
+    __syncthreads();
+    if (n_miss > 0) {
+        // histogram of the candidates' stamps
+        for (int r = tid; r < cap; r += CACHE_THREADS) {
+            const int st = stamp[r];
+            if (st != now) atomicAdd(&hist[cache_bin(st, now)], 1);
+        }
+        __syncthreads();
+        // threshold bin: the n_miss oldest rows are all rows of the bins below it and `need` rows of the bin itself
+        if (warp == 0) {
+            int run = 0, found = 0;
+            for (int b0 = 0; b0 < CACHE_BINS && !found; b0 += 32) {
+                const int v = hist[b0 + lane];
+                int inc = v;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) { const int a = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += a; }
+                const unsigned reach = __ballot_sync(0xffffffffu, run + inc >= n_miss);
+                if (reach) {
+                    const int l = __ffs(reach) - 1;
+                    const int before = run + __shfl_sync(0xffffffffu, inc - v, l);
+                    if (lane == 0) { thr_bin = b0 + l; need_s = n_miss - before; }
+                    found = 1;
+                }
+                run += __shfl_sync(0xffffffffu, inc, 31);
+            }
+            if (!found && lane == 0) { thr_bin = CACHE_BINS; need_s = 0; }     // cannot happen: cap >= ws + q
+        }
+        __syncthreads();
+        const int B = thr_bin, need = need_s;
+        // ordered choice: every warp owns a contiguous range of rows
+        const int per = (cap + 31) / 32;
+        const int r0 = warp * per, r1 = min(cap, r0 + per);
+        int cnt_b = 0, cnt_l = 0;
+        for (int r = r0 + lane; r - lane < r1; r += 32) {
+            const int st = r < r1 ? stamp[r] : now;
+            const int bin = st != now ? cache_bin(st, now) : CACHE_BINS;
+            cnt_b += __popc(__ballot_sync(0xffffffffu, bin == B));
+            cnt_l += __popc(__ballot_sync(0xffffffffu, bin < B));
+        }
+        if (lane == 0) { wpre_b[warp] = cnt_b; wpre_sel[warp] = cnt_l; }
+        __syncthreads();
+        if (warp == 0) {
+            const int vb = wpre_b[lane], vl = wpre_sel[lane];
+            int ib = vb;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int a = __shfl_up_sync(0xffffffffu, ib, o); if (lane >= o) ib += a; }
+            const int pre_b = ib - vb;
+            const int take_b = max(0, min(vb, need - pre_b));
+            int isel = vl + take_b;
+            const int vsel = isel;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int a = __shfl_up_sync(0xffffffffu, isel, o); if (lane >= o) isel += a; }
+            wpre_b[lane] = pre_b;
+            wpre_sel[lane] = isel - vsel;
+        }
+        __syncthreads();
+        int run_b = wpre_b[warp], pos = wpre_sel[warp];
+        for (int r = r0 + lane; r - lane < r1; r += 32) {
+            const int st = r < r1 ? stamp[r] : now;
+            const int bin = st != now ? cache_bin(st, now) : CACHE_BINS;
+            const unsigned bb = __ballot_sync(0xffffffffu, bin == B);
+            const int rank_b = run_b + __popc(bb & ((1u << lane) - 1));
+            const bool sel = bin < B || (bin == B && rank_b < need);
+            const unsigned sb = __ballot_sync(0xffffffffu, sel);
+            if (sel) victims[pos + __popc(sb & ((1u << lane) - 1))] = r;
+            run_b += __popc(bb);
+            pos += __popc(sb);
+        }
+        __threadfence_block();
+        __syncthreads();
+        // the misses take the victims' rows
+        if (tid < n_miss) {
+            const int t = miss_t[tid];
+            const int mid = ids[t0 + t];
+            const int r = victims[tid];
+            const int old = inst_of[r];
+            if (old >= 0) slot_of[old] = -1;
+            inst_of[r] = mid;
+            slot_of[mid] = r;
+            stamp[r] = now;
+            row_slot[t0 + t] = r;
+            miss_ids[tid] = mid;
+            miss_slot[tid] = r;
+        }
+    }
+    if (tid == 0) {
+        reinterpret_cast<int *>(ctr)[0] = n_miss;                 // CACHE_N_MISS, read by the engines as an int
+        ctr[CACHE_HITS] += n_hit_s;
+        ctr[CACHE_MISSES] += n_miss;
+        ctr[CACHE_BLOCKS] += (n_new + row_block - 1) / row_block;
+        ctr[CACHE_BLOCKS_SAVED] += (n_new + row_block - 1) / row_block - (n_miss + row_block - 1) / row_block;
+    }
+}
+
+__global__ void fill_int_kernel(int *p, long long n, int v) {
+    for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long) gridDim.x * blockDim.x) p[i] = v;
+}
+
+// =================================================================================================
 // f update:  f[j] -= sum_t alpha_diff[t] * rows[phys(t)][j]   (smo_kernel.cu:289-310)
 // =================================================================================================
 // HBM-bound: every thread owns 4 consecutive columns and streams the rows whose alpha_diff is
@@ -767,7 +931,7 @@ __global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *
 __global__ void __launch_bounds__(128)
 update_f_kernel(double *__restrict__ f, int n, const double *__restrict__ alpha_diff, int ws, int q,
                 int first_half_phys, const float *__restrict__ rows, long long ld, int vec_ok, int t_begin,
-                int t_end, int cols) {
+                int t_end, int cols, const int *__restrict__ row_slot) {
     __shared__ double ad[1024];
     __shared__ int prow[1024];
     __shared__ int cnt;
@@ -784,7 +948,7 @@ update_f_kernel(double *__restrict__ f, int n, const double *__restrict__ alpha_
             if (dv != 0.0) {
                 const int p = base + __popc(m & ((1u << threadIdx.x) - 1));
                 ad[p] = dv;
-                prow[p] = q > 0 ? phys_row(t, q, first_half_phys) : t;
+                prow[p] = row_slot ? row_slot[t] : (q > 0 ? phys_row(t, q, first_half_phys) : t);
             }
             base += __popc(m);
         }
@@ -1016,6 +1180,19 @@ static tsvm_status launch_local_smo(int solver_kind, int ws, const float *kww, c
 
 using namespace tsvm;
 
+// Bytes a solver may use for its row buffer / kernel-row cache: what tsvm_set_row_cache_bytes or the environment
+// variable TSVM_ROW_CACHE_MB asked for, else 45 % of the device's memory (a fixed fraction of the total, not of
+// what happens to be free, so that consecutive solvers of the same problem ask for the same block and get it
+// back from the library's pool).
+static long long g_row_cache_bytes = -1;
+static size_t row_cache_budget() {
+    if (g_row_cache_bytes >= 0) return (size_t) g_row_cache_bytes;
+    if (const char *e = getenv("TSVM_ROW_CACHE_MB")) return (size_t) strtoull(e, nullptr, 10) << 20;
+    size_t free_b = 0, total_b = 0;
+    if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) { cudaGetLastError(); return (size_t) 8 << 30; }
+    return (size_t) ((double) total_b * 0.45);
+}
+
 struct tsvm_ws {
     int n_max = 0, ws_max = 0;
     int cand_cap = 0;               // entries per list of cand_f / cand_id
@@ -1026,6 +1203,8 @@ struct tsvm_ws {
 };
 
 extern "C" {
+
+void tsvm_set_row_cache_bytes(long long bytes) { g_row_cache_bytes = bytes; }
 
 tsvm_status tsvm_ws_create(int n_max, int ws_max, tsvm_ws **out) {
     TSVM_REQUIRE(out && n_max > 0 && ws_max > 0 && ws_max <= MERGE_MAX_WANT, "ws_create: bad arguments");
@@ -1251,7 +1430,7 @@ tsvm_status tsvm_update_f(double *f_dev, int n, const double *alpha_diff_dev, in
     TSVM_REQUIRE(f_dev && alpha_diff_dev && rows_dev && n > 0 && ws_size > 0 && ws_size <= 1024 && ld >= n,
                  "update_f: bad arguments (at most 1024 rows per call)");
     TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, (cudaStream_t) stream, f_dev, n, alpha_diff_dev, ws_size,
-                0, 0, rows_dev, ld, rows_vec_ok(rows_dev, ld), 0, ws_size, update_f_cols(n));
+                0, 0, rows_dev, ld, rows_vec_ok(rows_dev, ld), 0, ws_size, update_f_cols(n), (const int *) nullptr);
     return TSVM_OK;
 }
 
@@ -1290,6 +1469,13 @@ struct tsvm_solver {
     cudaStream_t st2 = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_l0 = nullptr, ev_l1 = nullptr;
     float *ws_hi = nullptr, *ws_lo = nullptr, *ws_sd = nullptr, *ws_unscale = nullptr;
+    // kernel-row cache (cache_assign_kernel): the row buffer holds cache_cap rows; directory and per-iteration lists
+    long long cache_cap = 0;
+    int *slot_of = nullptr, *inst_of = nullptr, *stamp = nullptr, *row_slot = nullptr, *miss_ids = nullptr,
+        *miss_slot = nullptr, *victims = nullptr;
+    long long *cache_ctr = nullptr, *ctr_host = nullptr;
+    float *miss_hi = nullptr, *miss_lo = nullptr, *miss_sd = nullptr, *miss_unscale = nullptr;
+    long long hits = 0, misses = 0, row_blocks = 0, row_blocks_saved = 0;
     // iteration state (csmosolver.cpp:51-57)
     long long iter = 0, local_iter = 0, rows_made = 0, launches0 = 0;
     int same_cnt = 0, swap_cnt = 0, local_max_iter = 0;
@@ -1300,9 +1486,11 @@ struct tsvm_solver {
 
     ~tsvm_solver() {
         pool_free_many({ids, y_ws, rows, kww, diag_ws, f_ws, a_ws, alpha_diff, diff, red, in_ws, ws_hi, ws_lo, ws_sd,
-                        ws_unscale});
+                        ws_unscale, slot_of, inst_of, stamp, row_slot, miss_ids, miss_slot, victims, cache_ctr, miss_hi,
+                        miss_lo, miss_sd, miss_unscale});
         tsvm_ws_destroy(sel);
         if (diff_host) pinned_free(diff_host);
+        if (ctr_host) pinned_free(ctr_host);
         for (auto e : ev) if (e) cudaEventDestroy(e);
         for (auto e : {ev_fork, ev_join, ev_l0, ev_l1}) if (e) cudaEventDestroy(e);
         if (st2) cudaStreamDestroy(st2);
@@ -1318,10 +1506,51 @@ struct tsvm_solver {
         return TSVM_OK;
     }
 
+    tsvm_status ensure_miss_planes() {
+        if (miss_hi) return TSVM_OK;
+        const size_t words = (km_plane_row_bytes(km) * (size_t) ws + 3) / 4;
+        TSVM_TRY(dev_alloc(&miss_hi, words));
+        TSVM_TRY(dev_alloc(&miss_lo, words));
+        TSVM_TRY(dev_alloc(&miss_sd, (size_t) ws));
+        TSVM_TRY(dev_alloc(&miss_unscale, (size_t) ws));
+        return TSVM_OK;
+    }
+
+    // Row buffer = kernel-row cache: as many rows as the budget allows (tsvm_set_row_cache_bytes), at least the
+    // working set plus one batch of new rows, at most one row per instance. A failed allocation halves the request.
+    tsvm_status alloc_rows() {
+        const long long floor_rows = (long long) ws + q;
+        long long want = (long long) (row_cache_budget() / (sizeof(float) * (size_t) ld));
+        if (want > n) want = n;
+        if (want < floor_rows) want = floor_rows;
+        for (;;) {
+            const tsvm_status s = dev_alloc(&rows, (size_t) want * ld);
+            if (s == TSVM_OK) break;
+            if (s != TSVM_ERR_OOM || want == floor_rows) return s;
+            want = want / 2 > floor_rows ? want / 2 : floor_rows;
+        }
+        cache_cap = want;
+        TSVM_TRY(dev_alloc(&slot_of, (size_t) n));
+        TSVM_TRY(dev_alloc(&inst_of, (size_t) cache_cap));
+        TSVM_TRY(dev_alloc(&stamp, (size_t) cache_cap));
+        TSVM_TRY(dev_alloc(&row_slot, (size_t) ws));
+        TSVM_TRY(dev_alloc(&miss_ids, (size_t) ws));
+        TSVM_TRY(dev_alloc(&miss_slot, (size_t) ws));
+        TSVM_TRY(dev_alloc(&victims, (size_t) ws));
+        TSVM_TRY(dev_alloc(&cache_ctr, (size_t) CACHE_CTRS));
+        TSVM_TRY(pinned_alloc((void **) &ctr_host, CACHE_CTRS * sizeof(long long)));
+        TSVM_LAUNCH(fill_int_kernel, 296, 256, 0, st, slot_of, (long long) n, -1);
+        TSVM_LAUNCH(fill_int_kernel, 296, 256, 0, st, inst_of, cache_cap, -1);
+        TSVM_CUDA(cudaMemsetAsync(stamp, 0, sizeof(int) * (size_t) cache_cap, st));
+        TSVM_CUDA(cudaMemsetAsync(row_slot, 0, sizeof(int) * (size_t) ws, st));
+        TSVM_CUDA(cudaMemsetAsync(cache_ctr, 0, sizeof(long long) * CACHE_CTRS, st));
+        return TSVM_OK;
+    }
+
     tsvm_status init() {
         TSVM_TRY(dev_alloc(&ids, (size_t) ws));
         TSVM_TRY(dev_alloc(&y_ws, (size_t) ws));
-        TSVM_TRY(dev_alloc(&rows, (size_t) ws * ld));
+        TSVM_TRY(alloc_rows());
         TSVM_TRY(dev_alloc(&kww, (size_t) ws * ws));
         TSVM_TRY(dev_alloc(&diag_ws, (size_t) ws));
         TSVM_TRY(dev_alloc(&f_ws, (size_t) ws));
@@ -1364,7 +1593,7 @@ struct tsvm_solver {
             TSVM_CUDA(cudaMemcpyAsync(alpha_diff, bd.data(), sizeof(double) * m, cudaMemcpyHostToDevice, st));
             TSVM_TRY(tsvm_km_rows_by_index(km, ids, m, rows, ld, st));
             TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, m, 0, 0, rows, ld,
-                        rows_vec_ok(rows, ld), 0, m, update_f_cols(n));
+                        rows_vec_ok(rows, ld), 0, m, update_f_cols(n), (const int *) nullptr);
             TSVM_CUDA(cudaStreamSynchronize(st));
             rows_made += m;
             bi.clear(); bd.clear();
@@ -1388,14 +1617,13 @@ struct tsvm_solver {
     // while the q x n launch - which leaves one SM pair free for it - fills the row buffer. Both meet before
     // the f update.
     tsvm_status outer_iteration() {
-        const int first_half_phys = (int) (iter & 1);   // iteration 0 fills both halves in logical order
+        const int t0 = iter == 0 ? 0 : q, n_new = iter == 0 ? ws : q;      // iteration 0 fills the whole working set
         const bool overlapped = overlap && iter > 0 && st2 && km_pair_engine(km, st);
+        const int row_block = km_pair_engine(km, st) ? 256 : 64;           // requested rows per tile of the engine
+        const int *n_miss_dev = reinterpret_cast<const int *>(cache_ctr);
         TSVM_CUDA(cudaEventRecord(ev[0], st));
         if (iter == 0) {
             TSVM_TRY(tsvm_select_working_set(sel, kind, n, f, alpha, y, nullptr, Cp, Cn, ws, ids, st));
-            TSVM_CUDA(cudaEventRecord(ev[1], st));
-            TSVM_TRY(tsvm_km_rows_by_index(km, ids, ws, rows, ld, st));
-            rows_made += ws;
         } else {
             // rotation of the working set (old second half -> first half, flags) and the selection of the new
             // second half: one cooperative launch
@@ -1405,42 +1633,58 @@ struct tsvm_solver {
             x.shift_ids = ids; x.shift_q = q; x.shift_flags = in_ws;
             TSVM_TRY(ws_candidates_cap(sel, kind, n, f, alpha, y, in_ws, Cp, Cn, q, 2 * q <= sel->cand_cap ? 2 * q : q, 0,
                                        sel->cand_f, sel->cand_id, st, x));
-            TSVM_CUDA(cudaEventRecord(ev[1], st));
-            float *new_rows = rows + (size_t) (1 - first_half_phys) * q * ld;
-            if (!overlapped) {
-                TSVM_TRY(tsvm_km_rows_by_index(km, ids + q, q, new_rows, ld, st));
-            } else {
-                TSVM_TRY(ensure_ws_planes());
-                TSVM_TRY(km_stage_rows_by_index(km, ids + q, q, st));
-                TSVM_TRY(km_gather_planes(km, ids, ws, ws_hi, ws_lo, ws_sd, ws_unscale, st));
-                TSVM_CUDA(cudaEventRecord(ev_fork, st));
-                // second stream: block rows q..ws-1 by the engine, rows 0..q-1 and the slot vectors by gather
-                TSVM_CUDA(cudaStreamWaitEvent(st2, ev_fork, 0));
-                const InstancePlanes members{ws_hi, ws_lo, ws_sd, ws_unscale, ws};
-                TSVM_TRY(km_rows_staged_on(km, members, q, kww + (size_t) q * ws, ws, st2));
-                TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st2, ws, q, first_half_phys, ids, rows, ld, km->diag, y, f,
-                            alpha, kww, diag_ws, y_ws, f_ws, a_ws, q);
-                TSVM_CUDA(cudaEventRecord(ev_l0, st2));
-                TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps,
-                                          local_max_iter, diff, ids, alpha, st2));
-                TSVM_CUDA(cudaEventRecord(ev_l1, st2));
-                // the rows that stayed in the buffer can be applied to f at once (HBM-bound, next to the
-                // tensor-bound launch); the new rows follow on the first stream
-                TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st2, f, n, alpha_diff, ws, q, first_half_phys,
-                            rows, ld, rows_vec_ok(rows, ld), 0, q, update_f_cols(n));
-                TSVM_CUDA(cudaEventRecord(ev_join, st2));
-                // first stream: the q full rows on all SM pairs but one
-                km->reserve_clusters = 1;
-                const tsvm_status rs = km_rows_staged(km, q, new_rows, ld, st);
-                km->reserve_clusters = 0;
-                TSVM_TRY(rs);
-            }
-            rows_made += q;
         }
+        // cache directory: hits point at their rows, misses get the least recently used rows
+        TSVM_LAUNCH(cache_assign_kernel, 1, CACHE_THREADS, 0, st, ids, t0, n_new, (int) (iter + 1), slot_of, inst_of, stamp,
+                    (int) cache_cap, row_slot, miss_ids, miss_slot, victims, cache_ctr, row_block);
+        TSVM_CUDA(cudaEventRecord(ev[1], st));
+        if (!overlapped) {
+            // the engine computes the missing rows only (their number is read on the device) into their cache rows
+            km->rows_m_dev = n_miss_dev; km->rows_slot_dev = miss_slot;
+            const tsvm_status rs = tsvm_km_rows_by_index(km, miss_ids, n_new, rows, ld, st);
+            km->rows_m_dev = nullptr; km->rows_slot_dev = nullptr;
+            TSVM_TRY(rs);
+        } else {
+            TSVM_TRY(ensure_ws_planes());
+            TSVM_TRY(ensure_miss_planes());
+            TSVM_TRY(km_gather_planes(km, ids, ws, nullptr, ws_hi, ws_lo, ws_sd, ws_unscale, st));
+            TSVM_TRY(km_gather_planes(km, miss_ids, q, n_miss_dev, miss_hi, miss_lo, miss_sd, miss_unscale, st));
+            TSVM_CUDA(cudaEventRecord(ev_fork, st));
+            // second stream: block rows q..ws-1 by the engine (new members against all members, from the members'
+            // own operand planes), rows 0..q-1 and the slot vectors by gather, then the local solver
+            TSVM_CUDA(cudaStreamWaitEvent(st2, ev_fork, 0));
+            const size_t rb = km_plane_row_bytes(km);
+            const InstancePlanes members{ws_hi, ws_lo, ws_sd, ws_unscale, ws};
+            const RowPlanes new_members{reinterpret_cast<const float *>(reinterpret_cast<const char *>(ws_hi) + (size_t) q * rb),
+                                        reinterpret_cast<const float *>(reinterpret_cast<const char *>(ws_lo) + (size_t) q * rb),
+                                        ws_sd + q, ws_unscale + q};
+            TSVM_TRY(km_rows_planes_on(km, members, new_members, q, kww + (size_t) q * ws, ws, st2));
+            TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st2, ws, q, 0, ids, rows, ld, km->diag, y, f, alpha, kww, diag_ws,
+                        y_ws, f_ws, a_ws, q, row_slot);
+            TSVM_CUDA(cudaEventRecord(ev_l0, st2));
+            TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter,
+                                      diff, ids, alpha, st2));
+            TSVM_CUDA(cudaEventRecord(ev_l1, st2));
+            // the rows that were in the buffer already can be applied to f at once (HBM-bound, next to the
+            // tensor-bound launch); the new rows follow on the first stream
+            TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st2, f, n, alpha_diff, ws, q, 0, rows, ld,
+                        rows_vec_ok(rows, ld), 0, q, update_f_cols(n), row_slot);
+            TSVM_CUDA(cudaEventRecord(ev_join, st2));
+            // first stream: the missing rows against all instances, on all SM pairs but one
+            const InstancePlanes all{km->Xhi, km->Xlo, km->self_dot, km->x_unscale, km->n};
+            const RowPlanes miss_rows{miss_hi, miss_lo, miss_sd, miss_unscale};
+            km->reserve_clusters = 1;
+            km->rows_m_dev = n_miss_dev; km->rows_slot_dev = miss_slot;
+            const tsvm_status rs = km_rows_planes_on(km, all, miss_rows, q, rows, ld, st);
+            km->reserve_clusters = 0;
+            km->rows_m_dev = nullptr; km->rows_slot_dev = nullptr;
+            TSVM_TRY(rs);
+        }
+        rows_made += n_new;
         TSVM_CUDA(cudaEventRecord(ev[2], st));
         if (!overlapped) {
-            TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st, ws, q, first_half_phys, ids, rows, ld, km->diag, y, f, alpha,
-                        kww, diag_ws, y_ws, f_ws, a_ws, ws);
+            TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st, ws, q, 0, ids, rows, ld, km->diag, y, f, alpha, kww, diag_ws,
+                        y_ws, f_ws, a_ws, ws, row_slot);
             TSVM_CUDA(cudaEventRecord(ev_l0, st));
             TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter,
                                       diff, ids, alpha, st));
@@ -1452,16 +1696,17 @@ struct tsvm_solver {
         // f -= sum over the old half's rows, then f -= sum over the new half's rows: two launches in every
         // form of the iteration, so that all of them round alike (the first iteration has new rows only)
         if (iter == 0) {
-            TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows,
-                        ld, rows_vec_ok(rows, ld), 0, ws, update_f_cols(n));
+            TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, 0, rows, ld,
+                        rows_vec_ok(rows, ld), 0, ws, update_f_cols(n), row_slot);
         } else {
             if (!overlapped)
-                TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys,
-                            rows, ld, rows_vec_ok(rows, ld), 0, q, update_f_cols(n));
-            TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, first_half_phys, rows,
-                        ld, rows_vec_ok(rows, ld), q, ws, update_f_cols(n));
+                TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, 0, rows, ld,
+                            rows_vec_ok(rows, ld), 0, q, update_f_cols(n), row_slot);
+            TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, 0, rows, ld,
+                        rows_vec_ok(rows, ld), q, ws, update_f_cols(n), row_slot);
         }
         TSVM_CUDA(cudaEventRecord(ev[4], st));
+        TSVM_CUDA(cudaMemcpyAsync(ctr_host, cache_ctr, CACHE_CTRS * sizeof(long long), cudaMemcpyDeviceToHost, st));
         TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
         int *got_host = reinterpret_cast<int *>(diff_host + 8);
         TSVM_CUDA(cudaMemcpyAsync(got_host, sel->count, sizeof(int), cudaMemcpyDeviceToHost, st));
@@ -1471,6 +1716,8 @@ struct tsvm_solver {
             set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", km->status_host[0]);
             return TSVM_ERR_DEVICE;
         }
+        hits = ctr_host[CACHE_HITS]; misses = ctr_host[CACHE_MISSES];
+        row_blocks = ctr_host[CACHE_BLOCKS]; row_blocks_saved = ctr_host[CACHE_BLOCKS_SAVED];
         const int wanted = iter == 0 ? ws : q;
         if (*got_host < wanted) {
             // the reference's selection loop never ends here (csmosolver.cpp:131-164); the empty slots were inert
@@ -1509,6 +1756,11 @@ struct tsvm_solver {
         out->seconds_total = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_begin).count();
         out->kernel_rows = rows_made;
         out->gpu_launches = launch_count() - launches0;
+        out->cache_hits = hits;
+        out->cache_misses = misses;
+        out->cache_rows = cache_cap;
+        out->row_blocks = row_blocks;
+        out->row_blocks_saved = row_blocks_saved;
     }
 
     // rho and objective (csmosolver.cpp:167-187,227-239; nusmosolver.cpp:9-46,120-126)
@@ -1806,7 +2058,7 @@ struct tsvm_shard {
         TSVM_CUDA(cudaEventRecord(ev_b1, st2));
         if (iter > 0)      // the old half's rows are in the buffer already
             TSVM_LAUNCH(update_f_kernel, update_f_grid(n_local), 128, 0, st2, f, n_local, alpha_diff, ws, q,
-                        first_half_phys, rows, ld, rows_vec_ok(rows, ld), 0, q, update_f_cols(n_local));
+                        first_half_phys, rows, ld, rows_vec_ok(rows, ld), 0, q, update_f_cols(n_local), (const int *) nullptr);
         TSVM_CUDA(cudaEventRecord(ev_join, st2));
         // first stream: the new rows against this rank's columns
         float *new_rows = rows + (size_t) (iter == 0 ? 0 : (1 - first_half_phys) * q) * ld;
@@ -1819,7 +2071,7 @@ struct tsvm_shard {
         rows_made += n_new;
         TSVM_CUDA(cudaStreamWaitEvent(st, ev_join, 0));
         TSVM_LAUNCH(update_f_kernel, update_f_grid(n_local), 128, 0, st, f, n_local, alpha_diff, ws, q, first_half_phys,
-                    rows, ld, rows_vec_ok(rows, ld), iter == 0 ? 0 : q, ws, update_f_cols(n_local));
+                    rows, ld, rows_vec_ok(rows, ld), iter == 0 ? 0 : q, ws, update_f_cols(n_local), (const int *) nullptr);
         TSVM_LAUNCH(shard_scatter_kernel, ceil_div(ws, 256), 256, 0, st, ids, ws, lo, hi, a_ws, alpha);
         TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
         int *got_host = reinterpret_cast<int *>(diff_host + 2);
