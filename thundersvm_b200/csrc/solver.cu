@@ -62,6 +62,7 @@ __device__ __forceinline__ key96_t make_key(bool asc, double f, unsigned id) {
 // ---- merge: sort every candidate list, keep its first `want`, then the reference's alternating
 // walk with "already taken" checks (csmosolver.cpp:123-165 / nusmosolver.cpp:48-118). ------------
 constexpr int MERGE_THREADS = 1024, MERGE_MAX_LEN = 8192, MERGE_MAX_WANT = 1024, HASH_SLOTS = 4096;
+constexpr int MERGE_JOINT_MAX = 2048;          // longest lists that merge_lists sorts side by side
 
 __device__ __forceinline__ bool key_less(unsigned long long ah, unsigned al, unsigned long long bh, unsigned bl) {
     return ah < bh || (ah == bh && al < bl);
@@ -86,7 +87,90 @@ __device__ void merge_lists(int solver_kind, const double *__restrict__ cand_f, 
     __shared__ int real_total;
     const int tid = threadIdx.x;
 
-    for (int l = 0; l < lists; ++l) {
+    // Lists that are not made of sorted runs and fit the shared memory side by side are sorted together: every
+    // step of the bitonic network handles all lists before its barrier (half the barriers for two lists).
+    const bool joint = seg_len == 0 && P <= MERGE_JOINT_MAX;
+    if (joint) {
+        for (int l = 0; l < lists; ++l) {
+            const bool asc = list_ascending(solver_kind, l);
+            for (int e = tid; e < P; e += MERGE_THREADS) {
+                unsigned long long h = ~0ull;
+                unsigned lo = ~0u;
+                if (e < len) {
+                    const int id = __ldcg(cand_id + (size_t) l * len + e);
+                    if (id >= 0) {
+                        h = ordered_key(__ldcg(cand_f + (size_t) l * len + e));
+                        lo = (unsigned) id;
+                        if (!asc) { h = ~h; lo = ~lo; }
+                    }
+                }
+                kh[(size_t) l * P + e] = h;
+            }
+        }
+        // (kl follows all lists' kh)
+        unsigned int *klj = reinterpret_cast<unsigned int *>(kh + (size_t) lists * P);
+        for (int l = 0; l < lists; ++l) {
+            const bool asc = list_ascending(solver_kind, l);
+            for (int e = tid; e < P; e += MERGE_THREADS) {
+                unsigned lo = ~0u;
+                if (e < len) {
+                    const int id = __ldcg(cand_id + (size_t) l * len + e);
+                    if (id >= 0) lo = asc ? (unsigned) id : ~(unsigned) id;
+                }
+                klj[(size_t) l * P + e] = lo;
+            }
+        }
+        __syncthreads();
+        for (int k = 2; k <= P; k <<= 1)
+            for (int j = k >> 1; j > 0; j >>= 1) {
+                for (int w = tid; w < lists * (P >> 1); w += MERGE_THREADS) {
+                    // comparison w of this step: list l, lower element e (bit j clear), partner e | j
+                    const int l = w / (P >> 1), c = w - l * (P >> 1);
+                    const int e = ((c & ~(j - 1)) << 1) | (c & (j - 1));
+                    const int x = e | j;
+                    unsigned long long *khl = kh + (size_t) l * P;
+                    unsigned int *kll = klj + (size_t) l * P;
+                    const bool up = (e & k) == 0;
+                    if (key_less(khl[x], kll[x], khl[e], kll[e]) == up) {
+                        unsigned long long th = khl[e]; khl[e] = khl[x]; khl[x] = th;
+                        unsigned tl = kll[e]; kll[e] = kll[x]; kll[x] = tl;
+                    }
+                }
+                __syncthreads();
+            }
+        int *top_id_j = reinterpret_cast<int *>(klj + (size_t) lists * P);
+        top_id = top_id_j;
+        partner = reinterpret_cast<short *>(top_id + MAX_LISTS * MERGE_MAX_WANT);
+        taken = reinterpret_cast<unsigned char *>(partner + MAX_LISTS * MERGE_MAX_WANT);
+        hash_id = reinterpret_cast<int *>(taken + MAX_LISTS * MERGE_MAX_WANT);
+        hash_pos = reinterpret_cast<short *>(hash_id + HASH_SLOTS);
+        for (int l = 0; l < lists; ++l) {
+            const bool asc = list_ascending(solver_kind, l);
+            const unsigned long long *khl = kh + (size_t) l * P;
+            const unsigned int *kll = klj + (size_t) l * P;
+            for (int e = tid; e < want; e += MERGE_THREADS) {
+                int id = -1;
+                if (e < P && !(khl[e] == ~0ull && kll[e] == ~0u)) id = (int) (asc ? kll[e] : ~kll[e]);
+                top_id[l * MERGE_MAX_WANT + e] = id;
+                partner[l * MERGE_MAX_WANT + e] = -1;
+                taken[l * MERGE_MAX_WANT + e] = 0;
+            }
+        }
+        __syncthreads();
+        if (tid < lists) {
+            const int l = tid;
+            const bool asc = list_ascending(solver_kind, l);
+            const unsigned long long *khl = kh + (size_t) l * P;
+            int c = want < P ? want : P;
+            int lo = 0, hi = c;
+            while (lo < hi) { int mid = (lo + hi) >> 1; if (top_id[l * MERGE_MAX_WANT + mid] >= 0) lo = mid + 1; else hi = mid; }
+            top_len[l] = lo;
+            last_fkey[l] = lo > 0 ? (asc ? khl[lo - 1] : ~khl[lo - 1]) : 0ull;
+        }
+        __syncthreads();
+    }
+
+    for (int l = 0; l < lists && !joint; ++l) {
         const bool asc = list_ascending(solver_kind, l);
         for (int e = tid; e < P; e += MERGE_THREADS) {
             unsigned long long h = ~0ull;
@@ -446,53 +530,57 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) select_fused_kernel(const Se
         __syncthreads();
         if (is_last) {
             __threadfence();
-            for (int l = 0; l < lists; ++l) {
-                if (!((active >> l) & 1u)) continue;
-                volatile int *h = a.hist + l * RADIX_BINS;
-                // threads 0..255: 16 consecutive bins each, block-wide exclusive scan of the per-thread sums
-                int local[16], sum = 0;
-                if (tid < 256) {
+            // All lists at once: threads 256 l .. 256 l + 255 own list l, 16 consecutive bins each. Exclusive scan of the
+            // per-thread sums inside the list: warp shuffles, then the list's eight warp totals through shared memory.
+            const int l = tid >> 8, t8 = tid & 255, lane = tid & 31;
+            const bool mine = l < lists && ((active >> l) & 1u);
+            int local[16], sum = 0;
+            int *h = a.hist + l * RADIX_BINS + t8 * 16;
+            if (mine) {
 #pragma unroll
-                    for (int b = 0; b < 16; ++b) { local[b] = h[tid * 16 + b]; sum += local[b]; }
-                    scan[tid] = sum;
+                for (int b4 = 0; b4 < 16; b4 += 4) {
+                    const int4 v = __ldcg(reinterpret_cast<const int4 *>(h + b4));
+                    local[b4] = v.x; local[b4 + 1] = v.y; local[b4 + 2] = v.z; local[b4 + 3] = v.w;
+                    sum += v.x + v.y + v.z + v.w;
                 }
-                __syncthreads();
-                for (int o = 1; o < 256; o <<= 1) {
-                    int v = (tid < 256 && tid >= o) ? scan[tid - o] : 0;
-                    __syncthreads();
-                    if (tid < 256) scan[tid] += v;
-                    __syncthreads();
-                }
-                const int total = scan[255];
-                const int before = tid < 256 ? scan[tid] - sum : 0;
-                const int k_rem = st[l].k_rem;
-                __syncthreads();
-                if (tid < 256) {
-                    if (total < k_rem) {
-                        if (tid == 0) st[l].take_all = 1;   // can only happen in pass 0
-                    } else if (before < k_rem && k_rem <= before + sum) {
-                        int run = before;
-#pragma unroll
-                        for (int b = 0; b < 16; ++b) {
-                            if (run < k_rem && k_rem <= run + local[b]) {
-                                key96_t p = prefix[l] | ((key96_t) (tid * 16 + b) << shift);
-                                const int k_new = k_rem - run;
-                                if (shift > 0 && (a.want - k_new) + local[b] <= a.cap) {
-                                    p |= ((key96_t) 1 << shift) - 1;
-                                    st[l].resolved = 1;
-                                }
-                                st[l].prefix_hi = (unsigned long long) (p >> 32);
-                                st[l].prefix_lo = (unsigned int) p;
-                                st[l].k_rem = k_new;
-                            }
-                            run += local[b];
-                        }
-                    }
-#pragma unroll
-                    for (int b = 0; b < 16; ++b) h[tid * 16 + b] = 0;
-                }
-                __syncthreads();
             }
+            int inc = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += v; }
+            if (lane == 31) scan[tid >> 5] = inc;              // 32 warp totals: 8 per list
+            __syncthreads();
+            if (mine) {
+                int before = inc - sum, total = 0;
+                for (int w = 0; w < 8; ++w) {
+                    const int v = scan[(l << 3) + w];
+                    if (w < (t8 >> 5)) before += v;
+                    total += v;
+                }
+                const int k_rem = st[l].k_rem;
+                if (total < k_rem) {
+                    if (t8 == 0) st[l].take_all = 1;   // can only happen in pass 0
+                } else if (before < k_rem && k_rem <= before + sum) {
+                    int run = before;
+#pragma unroll
+                    for (int b = 0; b < 16; ++b) {
+                        if (run < k_rem && k_rem <= run + local[b]) {
+                            key96_t p = prefix[l] | ((key96_t) (t8 * 16 + b) << shift);
+                            const int k_new = k_rem - run;
+                            if (shift > 0 && (a.want - k_new) + local[b] <= a.cap) {
+                                p |= ((key96_t) 1 << shift) - 1;
+                                st[l].resolved = 1;
+                            }
+                            st[l].prefix_hi = (unsigned long long) (p >> 32);
+                            st[l].prefix_lo = (unsigned int) p;
+                            st[l].k_rem = k_new;
+                        }
+                        run += local[b];
+                    }
+                }
+#pragma unroll
+                for (int b4 = 0; b4 < 16; b4 += 4) *reinterpret_cast<int4 *>(h + b4) = make_int4(0, 0, 0, 0);
+            }
+            __syncthreads();
             if (tid == 0) *a.ticket = 0;
             __threadfence();
         }
@@ -507,20 +595,35 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) select_fused_kernel(const Se
         take_all[l] = l < lists ? st[l].take_all != 0 : true;
         threshold[l] = l < lists ? ((key96_t) st[l].prefix_hi << 32) | st[l].prefix_lo : 0;
     }
-    for (int j = gtid; j < a.n; j += gsize) {
-        if (a.in_ws && a.in_ws[j]) continue;
-        const double al = a.alpha[j], fj = a.f[j];
-        const int yj = a.y[j];
+    for (int j0 = gtid - (tid & 31); j0 < a.n; j0 += gsize) {          // whole warps enter every round (ballots below)
+        const int j = j0 + (tid & 31);
+        const bool live = j < a.n && !(a.in_ws && a.in_ws[j]);
+        const double al = live ? a.alpha[j] : 0.0, fj = live ? a.f[j] : 0.0;
+        const int yj = live ? a.y[j] : 0;
+        unsigned hit = 0;
 #pragma unroll
         for (int l = 0; l < MAX_LISTS; ++l) {
-            if (l >= lists) continue;
+            if (l >= lists || !live) continue;
             if (!in_list(a.solver_kind, l, al, yj, a.Cp, a.Cn)) continue;
             if (!take_all[l]) {
                 const key96_t thr = threshold[l];
                 if (make_key(list_ascending(a.solver_kind, l), fj, (unsigned) j) > thr) continue;
             }
-            const int pos = atomicAdd(&a.st[l].count, 1);
-            if (pos < a.cap) { a.cand_f[(size_t) l * a.cap + pos] = fj; a.cand_id[(size_t) l * a.cap + pos] = j + a.id_offset; }
+            hit |= 1u << l;
+        }
+        // one atomic per warp and list instead of one per candidate
+#pragma unroll
+        for (int l = 0; l < MAX_LISTS; ++l) {
+            if (l >= lists) continue;
+            const unsigned peers = __ballot_sync(0xffffffffu, (hit >> l) & 1u);
+            if (!peers) continue;
+            int base = 0;
+            if ((tid & 31) == __ffs(peers) - 1) base = atomicAdd(&a.st[l].count, __popc(peers));
+            base = __shfl_sync(0xffffffffu, base, __ffs(peers) - 1);
+            if ((hit >> l) & 1u) {
+                const int pos = base + __popc(peers & ((1u << (tid & 31)) - 1));
+                if (pos < a.cap) { a.cand_f[(size_t) l * a.cap + pos] = fj; a.cand_id[(size_t) l * a.cap + pos] = j + a.id_offset; }
+            }
         }
     }
     if (a.mode == FUSED_CANDIDATES) return;
@@ -537,7 +640,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) select_fused_kernel(const Se
 static size_t merge_smem_bytes(int len) {
     int P = 1;
     while (P < len) P <<= 1;
-    return (size_t) P * 12 + (size_t) MAX_LISTS * MERGE_MAX_WANT * (4 + 2 + 1) + (size_t) HASH_SLOTS * 6 + 64;
+    // keys of one list, or of all lists side by side where merge_lists sorts them together
+    const size_t keys = (size_t) P * 12 * (P <= MERGE_JOINT_MAX ? MAX_LISTS : 1);
+    return keys + (size_t) MAX_LISTS * MERGE_MAX_WANT * (4 + 2 + 1) + (size_t) HASH_SLOTS * 6 + 64;
 }
 
 // =================================================================================================
