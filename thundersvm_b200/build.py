@@ -45,7 +45,7 @@ def build(force=False, verbose=False):
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(
                 [os.path.getmtime(src)] + [os.path.getmtime(h) for h in headers()]):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
+            cmd = [nvcc] + NVCC_FLAGS + os.environ.get("TSVM_NVCC_EXTRA", "").split() + (["-Xptxas", "-v"] if verbose else []) + [
                 "-x", "cu", "-I", os.path.join(HERE, "..", "include"), "-I", os.path.join(CSRC, "host", "include"),
                 "-c", src, "-o", obj]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

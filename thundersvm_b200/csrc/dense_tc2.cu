@@ -34,18 +34,33 @@ constexpr int BM = 128, BN = 256, BN_HALF = 128, STAGES = 3, K_STEPS = 4;
 constexpr uint32_t A_BYTES = BM * 128;               // 16 KB per plane (this CTA's instances)
 constexpr uint32_t B_BYTES = BN_HALF * 128;          // 16 KB per plane (this CTA's half of the requested rows)
 constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // 64 KB per CTA
-// 12 warps = 3 warpgroups: warpgroup 0 holds the TMA producer (warp 0), the MMA issuer (warp 1) and two idle
-// warps and gives most of its registers back; warpgroups 1 and 2 are the eight promotion / epilogue warps and
-// take them (a 384-thread CTA is compiled for 168 registers per thread: 128 * 56 + 256 * 224 = 64,512 too).
-constexpr int THREADS = 384, EPI_WARPS = 8, EPI_WARP0 = 4, COLS_PER_THREAD = 128;
-constexpr int REGS_CONTROL = 56, REGS_EPILOGUE = 224;
-// epilogue staging (see the epilogue): EPI_CHUNK sums of each of the 256 epilogue threads, and per warp the
-// self dots and 1/scale of its 128 requested rows
-constexpr int EPI_CHUNK = 16;
+// Warpgroup 0 holds the TMA producer (warp 0), the MMA issuer (warp 1) and two idle warps and gives most of its
+// registers back; the other warpgroups are the promotion / epilogue warps and take them. Default: 8 epilogue
+// warps (two per tensor-memory lane quarter, 128 columns = 128 sums per thread; a 384-thread CTA is compiled
+// for 168 registers: 128 * 56 + 256 * 224). TSVM_EPI_WARPS = 16 (four per quarter, 64 sums per thread, 640
+// threads) builds and passes the same tests; measured on the 400,000 x 2,000 launch it changes nothing
+// (1.90 ms against 1.88 ms) - the kernel waits for the tensor pipe, not for its epilogue.
+#ifndef TSVM_EPI_WARPS
+#define TSVM_EPI_WARPS 8
+#endif
+constexpr int EPI_WARPS = TSVM_EPI_WARPS, EPI_WARP0 = 4, THREADS = 32 * (EPI_WARP0 + EPI_WARPS);
+constexpr int COLS_PER_THREAD = BN / (EPI_WARPS / 4);
+// Registers can only move inside the CTA: what the epilogue warps take (setmaxnreg.inc blocks until it is there)
+// must have been given back by the control warps, counted from the per-thread figure the kernel is compiled and
+// launched with (168 for 384 threads, 96 for 640: the largest multiples of 8 that fit 65,536 registers).
+constexpr int REGS_LAUNCH = EPI_WARPS == 8 ? 168 : 96;
+constexpr int REGS_CONTROL = EPI_WARPS == 8 ? 56 : 32, REGS_EPILOGUE = EPI_WARPS == 8 ? 224 : 112;
+static_assert(EPI_WARPS == 8 || EPI_WARPS == 16, "two or four epilogue warps per tensor-memory lane quarter");
+static_assert(128 * REGS_CONTROL + 32 * EPI_WARPS * REGS_EPILOGUE <= THREADS * REGS_LAUNCH,
+              "the epilogue warps would wait for registers that nobody releases");
+static_assert(THREADS * REGS_LAUNCH <= 65536, "register file of an SM");
+// epilogue staging (see the epilogue): EPI_CHUNK sums of each epilogue thread (eight chunks per thread), and per
+// warp the self dots and 1/scale of its requested rows
+constexpr int EPI_CHUNK = COLS_PER_THREAD / 8;
 constexpr uint32_t EPI_STAGE_BYTES = EPI_CHUNK * EPI_WARPS * 32 * 4;
 constexpr uint32_t EPI_CONST_BYTES = EPI_WARPS * 2 * COLS_PER_THREAD * 4;
 // prediction form: up to PRED_NC_SMEM coefficients of every epilogue thread's own instance (thread-private columns)
-constexpr int PRED_NC_SMEM = 9;
+constexpr int PRED_NC_SMEM = EPI_WARPS == 8 ? 9 : 4;
 constexpr uint32_t PRED_BYTES = PRED_NC_SMEM * EPI_WARPS * 32 * 4;
 // kernel-row form: output row (slot of the caller's row buffer) of every requested row, per epilogue warp
 constexpr uint32_t SLOT_BYTES = EPI_WARPS * COLS_PER_THREAD * 4;
@@ -424,7 +439,11 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
                                 kv[c] = j < n ? epilogue_value<EPI>(fn, dot, rowc[cbase + c], sdj) : 0.0f;
                             }
                         }
-                        const int col = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+                        // column of the chunk this lane ends up with: lane bit 16 >> s selects the upper half of step s
+                        int col = 0;
+#pragma unroll
+                        for (int st = 0, hn = EPI_CHUNK / 2; hn >= 1; ++st, hn >>= 1) col += ((lane >> (4 - st)) & 1) * hn;
+                        constexpr int REST = 32 / EPI_CHUNK;             // lanes that hold the same column afterwards
                         const int r = i0 + cbase + col;
                         for (int cl = cls_lo; cl <= cls_hi; ++cl)
                             for (int cr = 0; cr < nc; ++cr) {
@@ -437,17 +456,20 @@ dense_rows_tc2_kernel(const __grid_constant__ CUtensorMap map_xhi, const __grid_
 #pragma unroll
                                 for (int c = 0; c < EPI_CHUNK; ++c) w[c] = cf * kv[c];
 #pragma unroll
-                                for (int half_n = EPI_CHUNK / 2; half_n >= 1; half_n >>= 1) {
-                                    const bool upper = (lane & (half_n * 2)) != 0;     // lane bit 4, 3, 2, 1
+                                for (int st = 0, half_n = EPI_CHUNK / 2; half_n >= 1; ++st, half_n >>= 1) {
+                                    const int bit = 16 >> st;                          // lane bit 4, 3, 2, ...
+                                    const bool upper = (lane & bit) != 0;
 #pragma unroll
                                     for (int c = 0; c < half_n; ++c) {
                                         const float send = upper ? w[c] : w[c + half_n];
                                         const float keep = upper ? w[c + half_n] : w[c];
-                                        w[c] = keep + __shfl_xor_sync(0xffffffffu, send, half_n * 2);
+                                        w[c] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
                                     }
                                 }
-                                const float total = w[0] + __shfl_xor_sync(0xffffffffu, w[0], 1);
-                                if ((lane & 1) == 0 && r < m && total != 0.0f) {
+                                float total = w[0];
+#pragma unroll
+                                for (int o = REST >> 1; o >= 1; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+                                if ((lane & (REST - 1)) == 0 && r < m && total != 0.0f) {
                                     const int other = cr < cl ? cr : cr + 1;
                                     const int k = other > cl ? pair_index(pa.n_classes, cl, other)
                                                              : pair_index(pa.n_classes, other, cl);
