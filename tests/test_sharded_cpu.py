@@ -183,3 +183,41 @@ def test_working_set_size_helper_matches_the_library():
     f.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t]
     for n, d in ((150, 5), (1000, 785), (12025, 785), (400000, 2001), (3, 2), (2049, 64)):
         assert sharded.working_set_size(n, d) == f(n, d, 8 << 30, 0), (n, d)
+
+
+def _arrival_rank(rank, world, port, out_dir, late_rank):
+    """Every rank joins the process group; `late_rank` then stays away from the arrival check (as a rank
+    that raised or hangs before its first collective would)."""
+    import time
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    result = "ok"
+    if rank == late_rank:
+        time.sleep(6.0)                    # never arrives within the limit
+        result = "late"
+    else:
+        t0 = time.time()
+        try:
+            sharded.wait_for_peers(None, timeout_s=2.0)
+        except sharded.PeerTimeout as exc:
+            result = "timeout after %.1f s: %s" % (time.time() - t0, str(exc)[:200])
+    with open(os.path.join(out_dir, "arrival%d.txt" % rank), "w") as f:
+        f.write(result)
+
+
+def test_missing_rank_is_reported_by_the_arrival_check(tmp_path):
+    """Failure detection on the host: a rank that does not show up makes the others give up after the limit
+    with an error that names it, instead of blocking in the first collective of the solve."""
+    port = _free_port()
+    mp.spawn(_arrival_rank, args=(2, port, str(tmp_path), 1), nprocs=2, join=True)
+    got = open(os.path.join(str(tmp_path), "arrival0.txt")).read()
+    assert got.startswith("timeout after"), got
+    assert float(got.split()[2]) < 5.0
+    assert "1" in got.split(":", 1)[1]          # the message names rank 1
+    assert open(os.path.join(str(tmp_path), "arrival1.txt")).read() == "late"
+
+
+def test_all_ranks_pass_the_arrival_check(tmp_path):
+    port = _free_port()
+    mp.spawn(_arrival_rank, args=(2, port, str(tmp_path), -1), nprocs=2, join=True)
+    assert open(os.path.join(str(tmp_path), "arrival0.txt")).read() == "ok"
+    assert open(os.path.join(str(tmp_path), "arrival1.txt")).read() == "ok"

@@ -299,7 +299,38 @@ class ShardedSolver:
         return self.finish()
 
 
+class PeerTimeout(RuntimeError):
+    """A rank did not arrive in time (it raised, exited or hangs); the message names the missing ranks."""
+
+
+def wait_for_peers(control_group, timeout_s=30.0):
+    """Host-side arrival check before a multi-rank solve: every rank calls it on a gloo group; a rank that is
+    missing after `timeout_s` makes the others raise PeerTimeout instead of blocking in the first collective
+    (NCCL collectives have no time limit of their own once enqueued). No device work is involved."""
+    import datetime
+    try:
+        dist.monitored_barrier(group=control_group, timeout=datetime.timedelta(seconds=timeout_s), wait_all_ranks=True)
+    except RuntimeError as exc:
+        raise PeerTimeout(str(exc)) from exc
+
+
 _LIBRARY_COMMS = {}
+
+
+def close_library_comms():
+    """Destroys the library's NCCL communicators (also registered to run at interpreter exit)."""
+    from . import capi
+    for comm in list(_LIBRARY_COMMS.values()):
+        try:
+            capi.lib().tsvm_nccl_comm_destroy(comm)
+        except Exception:
+            pass
+    _LIBRARY_COMMS.clear()
+
+
+import atexit  # noqa: E402
+
+atexit.register(close_library_comms)
 
 
 def _library_comm(capi, group, rank, world):
