@@ -298,17 +298,21 @@ def hbm_roofline(name, bytes_per_call, us, hbm_peak, peak_src, note):
             "algorithmic_bytes": bytes_per_call, "us_per_call": us, "peak_source": peak_src, "note": note}
 
 
-def time_calls(torch, fn, reps, warm=3):
+def time_calls(torch, fn, reps, warm=3, windows=5):
+    """us per call: median of `windows` windows of `reps` back-to-back calls (CUDA events)."""
     for _ in range(warm):
         fn()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1e3 / reps        # us per call
+    out = []
+    for _ in range(windows):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1) * 1e3 / reps)
+    return float(np.median(out))
 
 
 def extra_rooflines(torch, capi, synth, hbm_peak, peak_src, n):
@@ -344,7 +348,7 @@ def extra_rooflines(torch, capi, synth, hbm_peak, peak_src, n):
         idx_np = np.random.default_rng(0).choice(nn, Q, replace=False).astype(np.int32)
         idx = torch.from_numpy(idx_np).cuda()
         buf = torch.empty((Q, nn), dtype=torch.float32, device="cuda")
-        us = time_calls(torch, lambda: km.get_rows(idx, buf), 100)
+        us = time_calls(torch, lambda: km.get_rows(idx, buf), 40)
         nnz, nnz_ws = int(rp[-1]), int(np.diff(rp)[idx_np].sum())
         r = hbm_roofline("CSR kernel rows (%s: 512 rows x %d, nnz %d)" % (tag, nn, nnz),
                          Q * nn * 4 + nnz * 8 + (nn + 1) * 4 + nnz_ws * 8, us, hbm_peak, peak_src,

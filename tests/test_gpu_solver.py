@@ -360,3 +360,22 @@ def test_row_cache_budget_does_not_change_results(capi, case):
     assert s1["cache_misses"] <= n and s1["cache_hits"] >= s0["cache_hits"]
     if s1["outer_iters"] > 12:
         assert s1["cache_hits"] > 0
+
+
+def test_working_set_that_cannot_be_filled_is_an_error(capi):
+    """A class with C = 0 (a zero class weight) belongs to neither I_up nor I_low; when the other class has fewer
+    instances than the working set has slots, the reference's selection loop never ends (csmosolver.cpp:131-164).
+    Here the empty slots are inert and the call fails with a message instead."""
+    import torch
+    prob = synth.config1(1500)
+    y_np = binary_labels(prob).copy()
+    y_np[:] = -1
+    y_np[:300] = 1                                   # 300 eligible instances for 1024 slots
+    km = device_matrix(capi, prob, 1500)
+    y = torch.from_numpy(y_np).cuda()
+    alpha = torch.zeros(1500, dtype=torch.float64, device="cuda")
+    f = -y.to(torch.float64)
+    with pytest.raises(capi.TsvmError, match="eligible"):
+        capi.smo_solve(km, y, alpha, f, 1e-3, 1.0, 0.0, 1024)
+    assert torch.isfinite(alpha).all() and torch.isfinite(f).all()
+    km.close()
