@@ -450,6 +450,8 @@ struct SelectArgs {
     int *shift_ids;
     int shift_q;
     unsigned char *shift_flags;
+    // optional: when *stop is non-zero the whole launch is a no-op (iterations queued past the end of a solve)
+    const int *stop;
 };
 
 __device__ void merge_lists(int solver_kind, const double *cand_f, const int *cand_id, int len, int want, int *out_ids,
@@ -467,6 +469,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) select_fused_kernel(const Se
     // the selection state is written by other blocks between the barriers: always read it from L2
     volatile SelectState *st = a.st;
     const int tid = threadIdx.x, gtid = blockIdx.x * FUSED_THREADS + tid, gsize = gridDim.x * FUSED_THREADS;
+    // written by an earlier launch only: every thread of every block reads the same value and leaves before
+    // the first grid barrier
+    if (a.stop && *a.stop) return;
 
     // ---- phase 0: state, histograms, candidate ids, optional rotation of the working set
     for (int i = gtid; i < lists * RADIX_BINS; i += gsize) a.hist[i] = 0;
@@ -649,18 +654,22 @@ static size_t merge_smem_bytes(int len) {
 // Local SMO (one CTA per working set)
 // =================================================================================================
 constexpr int SMO_THREADS = 256, SMO_WARPS = SMO_THREADS / 32;
+// two more warps own no slot: they copy rows ahead of their use (below); without them the block has SMO_THREADS
+constexpr int SMO_COPY_WARPS = 2, SMO_THREADS_PF = SMO_THREADS + 32 * SMO_COPY_WARPS;
+constexpr int SMO_WARPS_MAX = SMO_WARPS + SMO_COPY_WARPS;
 constexpr unsigned long long KEY_POS_INF = 0xfff0000000000000ull;   // ordered_key(+inf)
 constexpr int NO_SLOT = 0x7fffffff;
 
 struct RedBuf {                     // per-warp partial results of up to four simultaneous reductions
-    unsigned long long key[4][SMO_WARPS];
-    int slot[4][SMO_WARPS];
+    unsigned long long key[4][SMO_WARPS_MAX];
+    int slot[4][SMO_WARPS_MAX];
 };
 
-// Block-wide argmin of R (key, slot) pairs: one __syncthreads, result in every thread.
+// Block-wide argmin of R (key, slot) pairs: one __syncthreads, result in every thread. buf.slot[r][w] keeps
+// warp w's own best until the buffer's next use.
 template <int R>
 __device__ __forceinline__ void block_argmin(RedBuf &buf, unsigned long long (&key)[R], int (&slot)[R]) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         warp_argmin_u64(key[r], slot[r]);
@@ -669,12 +678,68 @@ __device__ __forceinline__ void block_argmin(RedBuf &buf, unsigned long long (&k
     __syncthreads();
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        unsigned long long k = lane < SMO_WARPS ? buf.key[r][lane] : ~0ull;
-        int s = lane < SMO_WARPS ? buf.slot[r][lane] : NO_SLOT;
+        unsigned long long k = lane < nwarps ? buf.key[r][lane] : ~0ull;
+        int s = lane < nwarps ? buf.slot[r][lane] : NO_SLOT;
         warp_argmin_u64(k, s);
         key[r] = k; slot[r] = s;
     }
 }
+
+// ---- speculative row copies -------------------------------------------------------------------------
+// An iteration waits twice for a row of the ws x ws block to arrive from L2: row i after the first-order
+// argmin, row j after the second-order one. Nearly every row is used once, so a cache of used rows never
+// hits - but the next winner is usually one of this iteration's losers: the eight warps' own best slots of an
+// argmin contain the next argmin's winner about three times out of four. Two extra warps, which own no slot
+// and only keep step with the barriers, therefore copy the rows of those eight slots into a ring of rows in
+// shared memory (cp.async; one warp and one ring for the i rows, one for the j rows). The working warps look a
+// winner up in the ring's tags and read its row there, or from L2 if it is absent. The values read are the
+// same floats either way, so the iterates do not depend on what was copied.
+constexpr int PF_ROWS = 24;             // ring entries per list; a lookup compares one tag per lane
+
+// entry of the ring that holds row `slot`, or -1 (every lane returns the same value)
+__device__ __forceinline__ int pf_lookup(const int *tag, int slot) {
+    const int lane = threadIdx.x & 31;
+    const unsigned m = __ballot_sync(0xffffffffu, lane < PF_ROWS && tag[lane] == slot);
+    return m ? __ffs(m) - 1 : -1;
+}
+
+// The copying warp of one ring, after an argmin: starts the copies of the working warps' own best slots
+// (cand[0..SMO_WARPS)) that are neither the winner nor in the ring already, as one cp.async group. Entries are
+// handed out in ring order, except the one that holds the winner's row, which the working warps are reading.
+// `head` lives in the copying warp's registers: it is the only writer of this ring and its tags.
+__device__ __forceinline__ void pf_copy_batch(int *tag, int &head, float *ring, const float *__restrict__ kww, int ws,
+                                              const int *cand, int winner) {
+    const int lane = threadIdx.x & 31;
+    const int in_use = pf_lookup(tag, winner);
+    const int c = lane < SMO_WARPS ? cand[lane] : NO_SLOT;
+    bool want = c != NO_SLOT && c != winner;
+    for (int e = 0; e < PF_ROWS; ++e) want = want && tag[e] != c;
+    const unsigned m = __ballot_sync(0xffffffffu, want);
+    const int n_new = __popc(m), rank = __popc(m & ((1u << lane) - 1));
+    int my_e = 0, p = head;
+    for (int r = 0; r < n_new;) {
+        const int e = p % PF_ROWS;
+        ++p;
+        if (e == in_use) continue;
+        if (r == rank) my_e = e;
+        ++r;
+    }
+    head = p % PF_ROWS;
+    if (want) tag[my_e] = c;
+    for (unsigned left = m; left; left &= left - 1) {
+        const int b = __ffs(left) - 1;
+        const int cb = __shfl_sync(0xffffffffu, c, b), eb = __shfl_sync(0xffffffffu, my_e, b);
+        const float *src = kww + (size_t) cb * ws;
+        float *dst = ring + (size_t) eb * ws;
+        for (int x = lane * 4; x < ws; x += 128) {
+            const unsigned d = (unsigned) __cvta_generic_to_shared(dst + x);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + x) : "memory");
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+__device__ __forceinline__ void pf_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // Local solver. Slot t of the working set is owned by thread t % 256 (register copies of f, alpha,
 // y, diag); mirrors of f / alpha / y / diag in shared memory serve the few values every thread
@@ -683,18 +748,34 @@ __device__ __forceinline__ void block_argmin(RedBuf &buf, unsigned long long (&k
 // lowest slot. NU = true: nu_smo_solve_kernel semantics of the CUDA backend
 // (smo_kernel.cu:118-252): bound held in float, float arithmetic in the curvature term.
 template <bool NU, int SLOTS>
-__global__ void __launch_bounds__(SMO_THREADS)
+__global__ void __launch_bounds__(SMO_THREADS_PF)
 local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict__ diag_ws,
                  const int *__restrict__ y_ws, const double *__restrict__ f_ws, double *__restrict__ alpha_ws,
                  double *__restrict__ alpha_diff, double Cp_in, double Cn_in, double eps, int max_iter,
-                 double *__restrict__ diff, const int *__restrict__ ids, double *__restrict__ alpha_global) {
+                 double *__restrict__ diff, const int *__restrict__ ids, double *__restrict__ alpha_global,
+                 const int *__restrict__ stop, int prefetch, long long *__restrict__ row_ctr) {
+    if (stop && *stop) {            // queued past the end of a solve: no step, so the f update that follows adds zero
+        for (int t = threadIdx.x; t < ws; t += blockDim.x) alpha_diff[t] = 0;
+        return;
+    }
+    // speculative row copies (C solver only): two rings of PF_ROWS rows in dynamic shared memory, filled by
+    // warps SMO_WARPS (i rows) and SMO_WARPS + 1 (j rows), which the launch adds when `prefetch` is set
+    extern __shared__ __align__(16) float pf_rings[];
+    __shared__ int pf_tag[2][32];
+    const bool PF = !NU && (prefetch & 1) != 0;
+    const bool copies = PF && (prefetch & 2) == 0;
+    const bool copy_i = copies && (threadIdx.x >> 5) == SMO_WARPS, copy_j = copies && (threadIdx.x >> 5) == SMO_WARPS + 1;
+    float *ring_i = pf_rings, *ring_j = pf_rings + (size_t) PF_ROWS * ws;
+    if (threadIdx.x < 64) pf_tag[threadIdx.x >> 5][threadIdx.x & 31] = -1;
+    int pf_head = 0;
     __shared__ RedBuf red[2];
     __shared__ double f_sm[1024], a_sm[1024];
     __shared__ float kd_sm[1024];
     __shared__ int y_sm[1024];
     const double Cp = NU ? (double) (float) Cp_in : Cp_in;
     const double Cn = NU ? Cp : Cn_in;
-    const int tid = threadIdx.x;
+    // threads past SMO_THREADS (the copying warps) own no slot: their slot numbers lie past the working set
+    const int tid = threadIdx.x < SMO_THREADS ? threadIdx.x : 1024;
     double f[SLOTS], a[SLOTS], aold[SLOTS];
     int y[SLOTS];
     float kd[SLOTS];
@@ -708,7 +789,7 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
     }
     __syncthreads();
     double local_eps = 0;
-    int it = 0;
+    int it = 0, n_ahead = 0;
     for (;;) {
         // ---- first-order selection --------------------------------------------------------
         constexpr int R1 = NU ? 4 : 2;
@@ -730,6 +811,7 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
                 if (y[s] < 0 && a[s] < Cp && knf < key[3]) { key[3] = knf; slot[3] = t; }    // low, -
             }
         }
+        if (copy_i) pf_wait_all();                  // the i rows copied during the last iteration have landed
         block_argmin<R1>(red[0], key, slot);
         // mirrors written only now: every thread has finished reading them for the last step
 #pragma unroll
@@ -742,12 +824,16 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
         const double up0 = key_to_double(key[0]);
         const double up1 = NU ? key_to_double(key[1]) : 0.0;
         float kI0[SLOTS], kI1[SLOTS];
+        const int e_i = PF ? pf_lookup(pf_tag[0], i0) : -1;          // row i copied ahead?
+        const float *row_i = e_i >= 0 ? ring_i + (size_t) e_i * ws : nullptr;
 #pragma unroll
         for (int s = 0; s < SLOTS; ++s) {
             const int t = tid + s * SMO_THREADS;
-            kI0[s] = t < ws ? __ldg(kww + (size_t) i0 * ws + t) : 0.0f;
+            if (row_i) kI0[s] = t < ws ? row_i[t] : 0.0f;
+            else kI0[s] = t < ws ? __ldg(kww + (size_t) i0 * ws + t) : 0.0f;
             kI1[s] = (NU && t < ws) ? __ldg(kww + (size_t) i1 * ws + t) : 0.0f;
         }
+        if (copy_i) pf_copy_batch(pf_tag[0], pf_head, ring_i, kww, ws, red[0].slot[0], slot[0]);
         double local_diff;
         if (!NU) local_diff = -key_to_double(key[1]) - up0;
         else local_diff = fmax(-key_to_double(key[2]) - up0, -key_to_double(key[3]) - up1);
@@ -756,6 +842,7 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
             if (tid == 0) diff[0] = local_diff;
         }
         if (it > max_iter || local_diff < local_eps) break;
+        n_ahead += e_i >= 0;
 
         // ---- second-order selection ---------------------------------------------------------
         constexpr int R2 = NU ? 2 : 1;
@@ -789,6 +876,7 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
                 }
             }
         }
+        if (copy_j) pf_wait_all();
         block_argmin<R2>(red[1], key2, slot2);
         int i, j2;
         double up;
@@ -802,7 +890,18 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
         // ---- step length, computed redundantly by every thread ---------------------------------
         const double ai = a_sm[i], aj = a_sm[j2], fj = f_sm[j2];
         const int yi = y_sm[i], yj = y_sm[j2];
-        const float kij = __ldg(kww + (size_t) i * ws + j2);
+        const float kij = row_i ? row_i[j2] : __ldg(kww + (size_t) i * ws + j2);
+        const int e_j = PF ? pf_lookup(pf_tag[1], j2) : -1;          // row j copied ahead?
+        n_ahead += e_j >= 0;
+        const float *row_j = e_j >= 0 ? ring_j + (size_t) e_j * ws : nullptr;
+        float kJ[SLOTS];
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int t = tid + s * SMO_THREADS;
+            if (row_j) kJ[s] = t < ws ? row_j[t] : 0.0f;
+            else kJ[s] = t < ws ? __ldg(kww + (size_t) j2 * ws + t) : 0.0f;
+        }
+        if (copy_j) pf_copy_batch(pf_tag[1], pf_head, ring_j, kww, ws, red[1].slot[0], slot2[0]);
         const double alpha_i_diff = yi > 0 ? Cp - ai : ai;
         const double curv = NU ? (double) (kd_sm[i] + kd_sm[j2] - 2 * kij)
                                : (double) (kd_sm[i] + kd_sm[j2]) - 2.0 * (double) kij;
@@ -814,10 +913,9 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
             if (t == i) a[s] += l * yi;
             if (t == j2) a[s] -= l * yj;
             if (t < ws) {
-                const float kJ = __ldg(kww + (size_t) j2 * ws + t);
                 const float kI = use1 ? kI1[s] : kI0[s];
-                if (NU) f[s] -= l * (double) (kJ - kI);
-                else f[s] -= l * ((double) kJ - (double) kI);
+                if (NU) f[s] -= l * (double) (kJ[s] - kI);
+                else f[s] -= l * ((double) kJ[s] - (double) kI);
             }
         }
         ++it;
@@ -831,7 +929,10 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
             if (alpha_global && ids[t] >= 0) alpha_global[ids[t]] = a[s];
         }
     }
-    if (tid == 0) diff[1] = it;
+    if (tid == 0) {
+        diff[1] = it;
+        if (row_ctr) { row_ctr[0] += 2ll * it; row_ctr[1] += n_ahead; }
+    }
 }
 
 // ---- gather of the working set's block and vectors ---------------------------------------------
@@ -877,7 +978,9 @@ __global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *
 // histogram over the stamps; ties go to the lower row number, so the choice does not depend on thread timing.
 // Everything stays on the device: the engine reads the number of misses from memory.
 constexpr int CACHE_THREADS = 1024, CACHE_BINS = 2048;
-enum { CACHE_N_MISS = 0, CACHE_HITS = 1, CACHE_MISSES = 2, CACHE_BLOCKS = 3, CACHE_BLOCKS_SAVED = 4, CACHE_CTRS = 8 };
+enum { CACHE_N_MISS = 0, CACHE_HITS = 1, CACHE_MISSES = 2, CACHE_BLOCKS = 3, CACHE_BLOCKS_SAVED = 4,
+       LOCAL_ROW_READS = 5, LOCAL_ROWS_AHEAD = 6,      // counted by the local solver
+       CACHE_CTRS = 8 };
 
 __device__ __forceinline__ int cache_bin(int stamp, int now) {
     // older -> smaller bin; never-used rows (stamp 0) are the oldest; rows used in this iteration are not candidates
@@ -890,7 +993,11 @@ __global__ void __launch_bounds__(CACHE_THREADS, 1)
 cache_assign_kernel(const int *__restrict__ ids, int t0, int n_new, int now, int *__restrict__ slot_of,
                     int *__restrict__ inst_of, int *__restrict__ stamp, int cap, int *__restrict__ row_slot,
                     int *__restrict__ miss_ids, int *__restrict__ miss_slot, int *__restrict__ victims,
-                    long long *__restrict__ ctr, int row_block) {
+                    long long *__restrict__ ctr, int row_block, const int *__restrict__ stop) {
+    if (stop && *stop) {            // queued past the end of a solve: no member changes, no row to compute
+        if (threadIdx.x == 0) reinterpret_cast<int *>(ctr)[0] = 0;
+        return;
+    }
     __shared__ int hist[CACHE_BINS];
     __shared__ int miss_t[CACHE_THREADS];
     __shared__ int wsum[32], wpre_b[32], wpre_sel[32];
@@ -1022,6 +1129,50 @@ cache_assign_kernel(const int *__restrict__ ids, int t0, int n_new, int now, int
         ctr[CACHE_BLOCKS] += (n_new + row_block - 1) / row_block;
         ctr[CACHE_BLOCKS_SAVED] += (n_new + row_block - 1) / row_block - (n_miss + row_block - 1) / row_block;
     }
+}
+
+// ---- end-of-iteration bookkeeping on the device ----------------------------------------------------
+// The reference decides after every outer iteration, on the host, whether to go on (csmosolver.cpp:83-111).
+// Here one thread applies the same rules to the same doubles on the device, so the host can queue several
+// iterations and read the outcome once: every kernel of a queued iteration looks at `stop` first and does
+// nothing once it is set.
+struct SolverCtl {
+    int stop;                       // first member: kernels take a pointer to it
+    int done;                       // the reference's own termination rules fired
+    int iter, same_cnt, swap_cnt;
+    int short_got, short_wanted;    // a selection that could not fill its slots (got < wanted)
+    int engine_status;              // non-zero: a bounded wait of the kernel-row engine ran out
+    double prev, last, second_last, diff0;
+    long long local_iter;
+    long long ctr[CACHE_CTRS];      // cache counters as of the last iteration that ran
+};
+static_assert(offsetof(SolverCtl, stop) == 0, "kernels read the stop flag through a pointer to the struct");
+
+__global__ void solver_status_kernel(SolverCtl *c, const double *__restrict__ diff, const int *__restrict__ got,
+                                     int wanted, double eps, int max_iter, const long long *__restrict__ cache_ctr,
+                                     const int *__restrict__ engine_status) {
+    if (threadIdx.x != 0 || c->stop) return;
+    const double d = diff[0];
+    c->diff0 = d;
+    c->local_iter += (long long) diff[1];
+    // csmosolver.cpp:86-111
+    if (fabs(d - c->prev) < eps * 0.001) c->same_cnt++;
+    else { c->same_cnt = 0; c->prev = d; }
+    if (fabs(d - c->second_last) < eps * 0.001) c->swap_cnt++;
+    else c->swap_cnt = 0;
+    c->second_last = c->last;
+    c->last = d;
+    int stop = 0;
+    if ((c->same_cnt >= 10 && fabs(d - 2.0) > eps) || d < eps || (c->swap_cnt >= 10 && fabs(d - 2.0) > eps)) {
+        c->done = 1;
+        stop = 1;
+    }
+    c->iter++;
+    if (max_iter != -1 && c->iter - 1 == max_iter) stop = 1;      // iteration cap (csmosolver.cpp:110)
+    if (*got < wanted) { c->short_got = *got; c->short_wanted = wanted; stop = 1; }
+    if (engine_status && *engine_status) { c->engine_status = *engine_status; stop = 1; }
+    for (int k = 0; k < CACHE_CTRS; ++k) c->ctr[k] = cache_ctr[k];
+    c->stop = stop;
 }
 
 __global__ void fill_int_kernel(int *p, long long n, int v) {
@@ -1266,12 +1417,23 @@ static inline int rows_vec_ok(const float *rows, long long ld) {
 static tsvm_status launch_local_smo(int solver_kind, int ws, const float *kww, const float *diag_ws, const int *y_ws,
                                     const double *f_ws, double *alpha_ws, double *alpha_diff, double Cp, double Cn,
                                     double eps, int max_iter, double *diff, const int *ids, double *alpha_global,
-                                    cudaStream_t st) {
+                                    cudaStream_t st, const int *stop = nullptr, long long *row_ctr = nullptr) {
     const bool nu = solver_kind != TSVM_SOLVER_C;
     const int slots = ceil_div(ws, SMO_THREADS);
+    // speculative row copies: rows must be whole 16-byte chunks per lane and the rings must fit
+    static const int pf_mode = [] { const char *e = getenv("TSVM_LOCAL_PREFETCH"); return e ? atoi(e) : 0; }();
+    const size_t ring_bytes = (size_t) 2 * PF_ROWS * ws * sizeof(float);
+    const bool pf = !nu && pf_mode != 0 && ws % 128 == 0 && (reinterpret_cast<uintptr_t>(kww) & 15) == 0 &&
+                    ring_bytes <= (size_t) 200 * 1024;
+    const size_t smem = pf ? ring_bytes : 0;
+    const int pf_arg = !pf ? 0 : (pf_mode == 2 ? 0 : pf_mode == 3 ? 3 : 1);
 #define SMO_CASE(NU, S)                                                                                        \
-    TSVM_LAUNCH((local_smo_kernel<NU, S>), 1, SMO_THREADS, 0, st, ws, kww, diag_ws, y_ws, f_ws, alpha_ws,      \
-                alpha_diff, Cp, Cn, eps, max_iter, diff, ids, alpha_global)
+    do {                                                                                                       \
+        if (pf) TSVM_ONCE_PER_DEVICE(TSVM_CUDA(cudaFuncSetAttribute(                                           \
+            (local_smo_kernel<NU, S>), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));             \
+        TSVM_LAUNCH((local_smo_kernel<NU, S>), 1, pf ? SMO_THREADS_PF : SMO_THREADS, smem, st, ws, kww, diag_ws, y_ws, f_ws, alpha_ws, \
+                    alpha_diff, Cp, Cn, eps, max_iter, diff, ids, alpha_global, stop, pf_arg, row_ctr);             \
+    } while (0)
     if (!nu) {
         if (slots <= 1) SMO_CASE(false, 1); else if (slots <= 2) SMO_CASE(false, 2); else SMO_CASE(false, 4);
     } else {
@@ -1343,6 +1505,7 @@ struct FusedExtra {
     int *shift_ids = nullptr;                     // optional rotation of the working set first
     int shift_q = 0;
     unsigned char *shift_flags = nullptr;
+    const int *stop = nullptr;
 };
 
 static size_t fused_smem_bytes(int lists, int cap, int mode) {
@@ -1379,7 +1542,7 @@ static tsvm_status ws_candidates_cap(tsvm_ws *w, int solver_kind, int n, const d
     a.Cp = Cp; a.Cn = Cn; a.st = w->state; a.hist = w->hist; a.ticket = w->ticket; a.want = want; a.cap = cap;
     a.id_offset = id_offset; a.cand_f = cand_f_dev; a.cand_id = cand_id_dev; a.mode = x.mode; a.out_ids = x.out_ids;
     a.out_count = w->count; a.sorted_f = x.sorted_f; a.sorted_id = x.sorted_id; a.shift_ids = x.shift_ids;
-    a.shift_q = x.shift_q; a.shift_flags = x.shift_flags;
+    a.shift_q = x.shift_q; a.shift_flags = x.shift_flags; a.stop = x.stop;
     int grid = ceil_div(n, FUSED_THREADS * 2);
     if (grid > max_blocks) grid = max_blocks;
     if (grid < (x.mode == FUSED_SORT ? lists : 1)) grid = x.mode == FUSED_SORT ? lists : 1;
@@ -1554,6 +1717,11 @@ int tsvm_working_set_size(int n_instances, int n_features, size_t max_mem_bytes,
 
 // Solver state that persists across outer iterations.
 struct tsvm_solver {
+    // Events of one queued iteration: phase boundaries on the first stream, start and end of the local solver
+    struct IterEvents {
+        cudaEvent_t ph[5] = {nullptr, nullptr, nullptr, nullptr, nullptr}, l0 = nullptr, l1 = nullptr;
+    };
+
     tsvm_km *km = nullptr;
     int kind = 0, ws = 0, q = 0, n = 0;
     const int *y = nullptr;
@@ -1568,23 +1736,28 @@ struct tsvm_solver {
     unsigned char *in_ws = nullptr;
     tsvm_ws *sel = nullptr;
     double *diff_host = nullptr;
-    cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
-    // overlapped iteration: second stream, fork / local-solver events, operand planes of the working set
+    // end-of-iteration state on the device, its pinned copy, and the events of the queued iterations
+    enum { MAX_QUEUED = 32 };
+    SolverCtl *ctl = nullptr, *ctl_host = nullptr;
+    IterEvents evs[MAX_QUEUED];
+    int max_iter = -1;              // iteration cap applied on the device; -1: none
+    bool stopped = false;           // the device stopped the queue (done, capped or an error)
+    // overlapped iteration: second stream, fork / join events, operand planes of the working set
     bool overlap = true;
     cudaStream_t st2 = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_l0 = nullptr, ev_l1 = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     float *ws_hi = nullptr, *ws_lo = nullptr, *ws_sd = nullptr, *ws_unscale = nullptr;
     // kernel-row cache (cache_assign_kernel): the row buffer holds cache_cap rows; directory and per-iteration lists
     long long cache_cap = 0;
     int *slot_of = nullptr, *inst_of = nullptr, *stamp = nullptr, *row_slot = nullptr, *miss_ids = nullptr,
         *miss_slot = nullptr, *victims = nullptr;
-    long long *cache_ctr = nullptr, *ctr_host = nullptr;
+    long long *cache_ctr = nullptr;
     float *miss_hi = nullptr, *miss_lo = nullptr, *miss_sd = nullptr, *miss_unscale = nullptr;
-    long long hits = 0, misses = 0, row_blocks = 0, row_blocks_saved = 0;
+    long long hits = 0, misses = 0, row_blocks = 0, row_blocks_saved = 0, local_row_reads = 0, local_rows_ahead = 0;
     // iteration state (csmosolver.cpp:51-57)
     long long iter = 0, local_iter = 0, rows_made = 0, launches0 = 0;
-    int same_cnt = 0, swap_cnt = 0, local_max_iter = 0;
-    double prev = INFINITY, last = INFINITY, second_last = INFINITY, diff0 = 0;
+    int local_max_iter = 0;
+    double diff0 = 0;
     double t_sel = 0, t_rows = 0, t_loc = 0, t_upd = 0;
     bool done = false;
     std::chrono::steady_clock::time_point t_begin;
@@ -1592,12 +1765,15 @@ struct tsvm_solver {
     ~tsvm_solver() {
         pool_free_many({ids, y_ws, rows, kww, diag_ws, f_ws, a_ws, alpha_diff, diff, red, in_ws, ws_hi, ws_lo, ws_sd,
                         ws_unscale, slot_of, inst_of, stamp, row_slot, miss_ids, miss_slot, victims, cache_ctr, miss_hi,
-                        miss_lo, miss_sd, miss_unscale});
+                        miss_lo, miss_sd, miss_unscale, ctl});
         tsvm_ws_destroy(sel);
         if (diff_host) pinned_free(diff_host);
-        if (ctr_host) pinned_free(ctr_host);
-        for (auto e : ev) if (e) cudaEventDestroy(e);
-        for (auto e : {ev_fork, ev_join, ev_l0, ev_l1}) if (e) cudaEventDestroy(e);
+        if (ctl_host) pinned_free(ctl_host);
+        for (auto &E : evs) {
+            for (auto e : E.ph) if (e) cudaEventDestroy(e);
+            for (auto e : {E.l0, E.l1}) if (e) cudaEventDestroy(e);
+        }
+        for (auto e : {ev_fork, ev_join}) if (e) cudaEventDestroy(e);
         if (st2) cudaStreamDestroy(st2);
     }
 
@@ -1643,7 +1819,6 @@ struct tsvm_solver {
         TSVM_TRY(dev_alloc(&miss_slot, (size_t) ws));
         TSVM_TRY(dev_alloc(&victims, (size_t) ws));
         TSVM_TRY(dev_alloc(&cache_ctr, (size_t) CACHE_CTRS));
-        TSVM_TRY(pinned_alloc((void **) &ctr_host, CACHE_CTRS * sizeof(long long)));
         TSVM_LAUNCH(fill_int_kernel, 296, 256, 0, st, slot_of, (long long) n, -1);
         TSVM_LAUNCH(fill_int_kernel, 296, 256, 0, st, inst_of, cache_cap, -1);
         TSVM_CUDA(cudaMemsetAsync(stamp, 0, sizeof(int) * (size_t) cache_cap, st));
@@ -1667,9 +1842,11 @@ struct tsvm_solver {
         TSVM_CUDA(cudaMemsetAsync(in_ws, 0, (size_t) n, st));
         TSVM_TRY(tsvm_ws_create(n, ws, &sel));
         TSVM_TRY(pinned_alloc((void **) &diff_host, 16 * sizeof(double)));
-        for (auto &e : ev) TSVM_CUDA(cudaEventCreate(&e));
-        TSVM_CUDA(cudaEventCreate(&ev_l0));
-        TSVM_CUDA(cudaEventCreate(&ev_l1));
+        TSVM_TRY(dev_alloc(&ctl, 1));
+        TSVM_TRY(pinned_alloc((void **) &ctl_host, sizeof(SolverCtl)));
+        memset(ctl_host, 0, sizeof(SolverCtl));
+        ctl_host->prev = ctl_host->last = ctl_host->second_last = INFINITY;     // csmosolver.cpp:51-57
+        TSVM_CUDA(cudaMemcpyAsync(ctl, ctl_host, sizeof(SolverCtl), cudaMemcpyHostToDevice, st));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
         {
@@ -1711,8 +1888,9 @@ struct tsvm_solver {
         return flush();
     }
 
-    // One outer iteration of csmosolver.cpp:59-120. Sets `done` by the reference's rules
-    // (csmosolver.cpp:86-111) except the iteration cap, which the caller applies.
+    // Queues one outer iteration of csmosolver.cpp:59-120, number `it`, without waiting for it. Its last launch
+    // applies the reference's termination rules (csmosolver.cpp:86-111) on the device; every launch of an
+    // iteration queued after the one that ended the solve is a no-op.
     //
     // Overlapped form (dense data on the CTA-pair tensor engine, every iteration but the first): the local
     // solver only needs the ws x ws block of kernel values, not the q full rows. The block's q new rows are
@@ -1721,13 +1899,14 @@ struct tsvm_solver {
     // gathered from the rows already in the buffer, and the one-CTA local solver then runs on a second stream
     // while the q x n launch - which leaves one SM pair free for it - fills the row buffer. Both meet before
     // the f update.
-    tsvm_status outer_iteration() {
-        const int t0 = iter == 0 ? 0 : q, n_new = iter == 0 ? ws : q;      // iteration 0 fills the whole working set
-        const bool overlapped = overlap && iter > 0 && st2 && km_pair_engine(km, st);
+    tsvm_status enqueue_iteration(long long it, const IterEvents &E) {
+        const int t0 = it == 0 ? 0 : q, n_new = it == 0 ? ws : q;          // iteration 0 fills the whole working set
+        const bool overlapped = overlap && it > 0 && st2 && km_pair_engine(km, st);
         const int row_block = km_pair_engine(km, st) ? 256 : 64;           // requested rows per tile of the engine
         const int *n_miss_dev = reinterpret_cast<const int *>(cache_ctr);
-        TSVM_CUDA(cudaEventRecord(ev[0], st));
-        if (iter == 0) {
+        const int *stop = &ctl->stop;
+        TSVM_CUDA(cudaEventRecord(E.ph[0], st));
+        if (it == 0) {
             TSVM_TRY(tsvm_select_working_set(sel, kind, n, f, alpha, y, nullptr, Cp, Cn, ws, ids, st));
         } else {
             // rotation of the working set (old second half -> first half, flags) and the selection of the new
@@ -1736,13 +1915,14 @@ struct tsvm_solver {
             x.mode = FUSED_MERGE;
             x.out_ids = ids + q;
             x.shift_ids = ids; x.shift_q = q; x.shift_flags = in_ws;
+            x.stop = stop;
             TSVM_TRY(ws_candidates_cap(sel, kind, n, f, alpha, y, in_ws, Cp, Cn, q, 2 * q <= sel->cand_cap ? 2 * q : q, 0,
                                        sel->cand_f, sel->cand_id, st, x));
         }
         // cache directory: hits point at their rows, misses get the least recently used rows
-        TSVM_LAUNCH(cache_assign_kernel, 1, CACHE_THREADS, 0, st, ids, t0, n_new, (int) (iter + 1), slot_of, inst_of, stamp,
-                    (int) cache_cap, row_slot, miss_ids, miss_slot, victims, cache_ctr, row_block);
-        TSVM_CUDA(cudaEventRecord(ev[1], st));
+        TSVM_LAUNCH(cache_assign_kernel, 1, CACHE_THREADS, 0, st, ids, t0, n_new, (int) (it + 1), slot_of, inst_of, stamp,
+                    (int) cache_cap, row_slot, miss_ids, miss_slot, victims, cache_ctr, row_block, stop);
+        TSVM_CUDA(cudaEventRecord(E.ph[1], st));
         if (!overlapped) {
             // the engine computes the missing rows only (their number is read on the device) into their cache rows
             km->rows_m_dev = n_miss_dev; km->rows_slot_dev = miss_slot;
@@ -1766,10 +1946,10 @@ struct tsvm_solver {
             TSVM_TRY(km_rows_planes_on(km, members, new_members, q, kww + (size_t) q * ws, ws, st2));
             TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st2, ws, q, 0, ids, rows, ld, km->diag, y, f, alpha, kww, diag_ws,
                         y_ws, f_ws, a_ws, q, row_slot);
-            TSVM_CUDA(cudaEventRecord(ev_l0, st2));
+            TSVM_CUDA(cudaEventRecord(E.l0, st2));
             TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter,
-                                      diff, ids, alpha, st2));
-            TSVM_CUDA(cudaEventRecord(ev_l1, st2));
+                                      diff, ids, alpha, st2, stop, cache_ctr + LOCAL_ROW_READS));
+            TSVM_CUDA(cudaEventRecord(E.l1, st2));
             // the rows that were in the buffer already can be applied to f at once (HBM-bound, next to the
             // tensor-bound launch); the new rows follow on the first stream
             TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st2, f, n, alpha_diff, ws, q, 0, rows, ld,
@@ -1785,22 +1965,21 @@ struct tsvm_solver {
             km->rows_m_dev = nullptr; km->rows_slot_dev = nullptr;
             TSVM_TRY(rs);
         }
-        rows_made += n_new;
-        TSVM_CUDA(cudaEventRecord(ev[2], st));
+        TSVM_CUDA(cudaEventRecord(E.ph[2], st));
         if (!overlapped) {
             TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st, ws, q, 0, ids, rows, ld, km->diag, y, f, alpha, kww, diag_ws,
                         y_ws, f_ws, a_ws, ws, row_slot);
-            TSVM_CUDA(cudaEventRecord(ev_l0, st));
+            TSVM_CUDA(cudaEventRecord(E.l0, st));
             TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter,
-                                      diff, ids, alpha, st));
-            TSVM_CUDA(cudaEventRecord(ev_l1, st));
+                                      diff, ids, alpha, st, stop, cache_ctr + LOCAL_ROW_READS));
+            TSVM_CUDA(cudaEventRecord(E.l1, st));
         } else {
             TSVM_CUDA(cudaStreamWaitEvent(st, ev_join, 0));
         }
-        TSVM_CUDA(cudaEventRecord(ev[3], st));
+        TSVM_CUDA(cudaEventRecord(E.ph[3], st));
         // f -= sum over the old half's rows, then f -= sum over the new half's rows: two launches in every
         // form of the iteration, so that all of them round alike (the first iteration has new rows only)
-        if (iter == 0) {
+        if (it == 0) {
             TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, 0, rows, ld,
                         rows_vec_ok(rows, ld), 0, ws, update_f_cols(n), row_slot);
         } else {
@@ -1810,44 +1989,73 @@ struct tsvm_solver {
             TSVM_LAUNCH(update_f_kernel, update_f_grid(n), 128, 0, st, f, n, alpha_diff, ws, q, 0, rows, ld,
                         rows_vec_ok(rows, ld), q, ws, update_f_cols(n), row_slot);
         }
-        TSVM_CUDA(cudaEventRecord(ev[4], st));
-        TSVM_CUDA(cudaMemcpyAsync(ctr_host, cache_ctr, CACHE_CTRS * sizeof(long long), cudaMemcpyDeviceToHost, st));
-        TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
-        int *got_host = reinterpret_cast<int *>(diff_host + 8);
-        TSVM_CUDA(cudaMemcpyAsync(got_host, sel->count, sizeof(int), cudaMemcpyDeviceToHost, st));
-        TSVM_CUDA(cudaMemcpyAsync(km->status_host, km->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
-        TSVM_CUDA(cudaStreamSynchronize(st));
-        if (km->status_host[0] != 0) {
-            set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", km->status_host[0]);
-            return TSVM_ERR_DEVICE;
-        }
-        hits = ctr_host[CACHE_HITS]; misses = ctr_host[CACHE_MISSES];
-        row_blocks = ctr_host[CACHE_BLOCKS]; row_blocks_saved = ctr_host[CACHE_BLOCKS_SAVED];
-        const int wanted = iter == 0 ? ws : q;
-        if (*got_host < wanted) {
-            // the reference's selection loop never ends here (csmosolver.cpp:131-164); the empty slots were inert
-            set_error("working-set selection found %d eligible instances for %d slots (is a class weight or C zero?)",
-                      *got_host, wanted);
-            return TSVM_ERR_INVALID;
-        }
-        float ms;
-        cudaEventElapsedTime(&ms, ev[0], ev[1]); t_sel += ms;
-        cudaEventElapsedTime(&ms, ev[1], ev[2]); t_rows += ms;
-        cudaEventElapsedTime(&ms, ev_l0, ev_l1); t_loc += ms;     // overlapped with the rows phase when both streams run
-        cudaEventElapsedTime(&ms, ev[3], ev[4]); t_upd += ms;
-        diff0 = diff_host[0];
-        local_iter += (long long) diff_host[1];
-        if (fabs(diff0 - prev) < eps * 0.001) same_cnt++;
-        else { same_cnt = 0; prev = diff0; }
-        if (fabs(diff0 - second_last) < eps * 0.001) swap_cnt++;
-        else swap_cnt = 0;
-        second_last = last;
-        last = diff0;
-        if ((same_cnt >= 10 && fabs(diff0 - 2.0) > eps) || diff0 < eps || (swap_cnt >= 10 && fabs(diff0 - 2.0) > eps))
-            done = true;
-        ++iter;
+        TSVM_CUDA(cudaEventRecord(E.ph[4], st));
+        TSVM_LAUNCH(solver_status_kernel, 1, 32, 0, st, ctl, diff, sel->count, n_new, eps, max_iter, cache_ctr,
+                    km->status_dev);
         return TSVM_OK;
     }
+
+    // How many iterations are queued between two reads of the device's verdict. The queue hides the host's
+    // wake-up and launch latency behind the device's work; the price is at most that many no-op iterations
+    // after the one that ends the solve.
+    static int sync_every() {
+        static const int k = [] {
+            const char *e = getenv("TSVM_SYNC_EVERY");
+            const int v = e ? atoi(e) : 8;
+            return v < 1 ? 1 : (v > MAX_QUEUED ? (int) MAX_QUEUED : v);
+        }();
+        return k;
+    }
+
+    // Queues up to `count` outer iterations, waits once and takes over what the device decided. Fewer than
+    // `count` may have run: the termination rules, the iteration cap or an error stop the queue on the device.
+    tsvm_status run_iterations(int count) {
+        if (count > sync_every()) count = sync_every();
+        if (iter == 0) count = 1;                   // the first iteration is read back on its own
+        for (int j = 0; j < count; ++j) {
+            IterEvents &E = evs[j];
+            if (!E.l0) {
+                for (auto &e : E.ph) TSVM_CUDA(cudaEventCreate(&e));
+                TSVM_CUDA(cudaEventCreate(&E.l0));
+                TSVM_CUDA(cudaEventCreate(&E.l1));
+            }
+            TSVM_TRY(enqueue_iteration(iter + j, E));
+        }
+        TSVM_CUDA(cudaMemcpyAsync(ctl_host, ctl, sizeof(SolverCtl), cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaStreamSynchronize(st));
+        const SolverCtl &c = *ctl_host;
+        if (c.engine_status != 0) {
+            set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", c.engine_status);
+            return TSVM_ERR_DEVICE;
+        }
+        const int ran = (int) (c.iter - iter);
+        for (int j = 0; j < ran; ++j) {
+            const IterEvents &E = evs[j];
+            float ms;
+            cudaEventElapsedTime(&ms, E.ph[0], E.ph[1]); t_sel += ms;
+            cudaEventElapsedTime(&ms, E.ph[1], E.ph[2]); t_rows += ms;
+            cudaEventElapsedTime(&ms, E.l0, E.l1); t_loc += ms;      // overlapped with the rows phase when both streams run
+            cudaEventElapsedTime(&ms, E.ph[3], E.ph[4]); t_upd += ms;
+            rows_made += iter + j == 0 ? ws : q;
+        }
+        hits = c.ctr[CACHE_HITS]; misses = c.ctr[CACHE_MISSES];
+        row_blocks = c.ctr[CACHE_BLOCKS]; row_blocks_saved = c.ctr[CACHE_BLOCKS_SAVED];
+        local_row_reads = c.ctr[LOCAL_ROW_READS]; local_rows_ahead = c.ctr[LOCAL_ROWS_AHEAD];
+        iter = c.iter;
+        local_iter = c.local_iter;
+        diff0 = c.diff0;
+        done = c.done != 0;
+        stopped = c.stop != 0;
+        if (c.short_wanted > 0) {
+            // the reference's selection loop never ends here (csmosolver.cpp:131-164); the empty slots were inert
+            set_error("working-set selection found %d eligible instances for %d slots (is a class weight or C zero?)",
+                      c.short_got, c.short_wanted);
+            return TSVM_ERR_INVALID;
+        }
+        return TSVM_OK;
+    }
+
+    tsvm_status outer_iteration() { return run_iterations(1); }
 
     void fill_stats(tsvm_solve_stats *out, double obj) const {
         out->outer_iters = iter;
@@ -1866,6 +2074,8 @@ struct tsvm_solver {
         out->cache_rows = cache_cap;
         out->row_blocks = row_blocks;
         out->row_blocks_saved = row_blocks_saved;
+        out->local_row_reads = local_row_reads;
+        out->local_rows_ahead = local_rows_ahead;
     }
 
     // rho and objective (csmosolver.cpp:167-187,227-239; nusmosolver.cpp:9-46,120-126)
@@ -1924,7 +2134,7 @@ tsvm_status tsvm_solver_create(tsvm_km *km, int solver_kind, const int *y_dev, d
 
 tsvm_status tsvm_solver_iterate(tsvm_solver *S, int n_iters, int *done_host) {
     TSVM_REQUIRE(S && n_iters > 0, "solver_iterate: bad arguments");
-    for (int it = 0; it < n_iters && !S->done; ++it) TSVM_TRY(S->outer_iteration());
+    for (long long end = S->iter + n_iters; S->iter < end && !S->done;) TSVM_TRY(S->run_iterations((int) (end - S->iter)));
     if (done_host) *done_host = S->done ? 1 : 0;
     return TSVM_OK;
 }
@@ -1955,11 +2165,9 @@ tsvm_status tsvm_smo_solve(tsvm_km *km, int solver_kind, const int *y_dev, doubl
     tsvm_solver *S = nullptr;
     TSVM_TRY(tsvm_solver_create(km, solver_kind, y_dev, alpha_dev, f_dev, eps, Cp, Cn, ws_size, stream, &S));
     tsvm_status s = TSVM_OK;
-    // max_iter = k stops after outer iteration k, i.e. k + 1 iterations (csmosolver.cpp:110)
-    while (s == TSVM_OK && !S->done) {
-        s = S->outer_iteration();
-        if (s == TSVM_OK && max_iter != -1 && S->iter - 1 == max_iter) break;
-    }
+    // max_iter = k stops after outer iteration k, i.e. k + 1 iterations (csmosolver.cpp:110); applied on the device
+    S->max_iter = max_iter;
+    while (s == TSVM_OK && !S->stopped) s = S->run_iterations(tsvm_solver::MAX_QUEUED);
     if (s == TSVM_OK) s = S->finish(rho_host, stats_host);
     delete S;
     return s;
