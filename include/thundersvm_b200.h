@@ -142,8 +142,6 @@ typedef struct {
     long long cache_rows;       /* capacity of the cache, rows                               */
     long long row_blocks;       /* engine row blocks a cache-less solver would have computed */
     long long row_blocks_saved; /* ... of which the cache made this many unnecessary         */
-    long long local_row_reads;  /* rows of the ws x ws block read by the local solver (C solver)  */
-    long long local_rows_ahead; /* ... of which it found this many copied to shared memory ahead  */
 } tsvm_solve_stats;
 
 /* Kernel-row cache. The solver's row buffer holds as many kernel rows as this budget allows (at least the

@@ -37,8 +37,7 @@ class SolveStats(C.Structure):
                 ("seconds_local", C.c_double), ("seconds_update", C.c_double), ("seconds_total", C.c_double),
                 ("kernel_rows", C.c_longlong), ("gpu_launches", C.c_longlong), ("cache_hits", C.c_longlong),
                 ("cache_misses", C.c_longlong), ("cache_rows", C.c_longlong), ("row_blocks", C.c_longlong),
-                ("row_blocks_saved", C.c_longlong), ("local_row_reads", C.c_longlong),
-                ("local_rows_ahead", C.c_longlong)]
+                ("row_blocks_saved", C.c_longlong)]
 
     def as_dict(self):
         return {k: getattr(self, k) for k, _ in self._fields_}

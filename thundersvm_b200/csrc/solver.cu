@@ -654,22 +654,18 @@ static size_t merge_smem_bytes(int len) {
 // Local SMO (one CTA per working set)
 // =================================================================================================
 constexpr int SMO_THREADS = 256, SMO_WARPS = SMO_THREADS / 32;
-// two more warps own no slot: they copy rows ahead of their use (below); without them the block has SMO_THREADS
-constexpr int SMO_COPY_WARPS = 2, SMO_THREADS_PF = SMO_THREADS + 32 * SMO_COPY_WARPS;
-constexpr int SMO_WARPS_MAX = SMO_WARPS + SMO_COPY_WARPS;
 constexpr unsigned long long KEY_POS_INF = 0xfff0000000000000ull;   // ordered_key(+inf)
 constexpr int NO_SLOT = 0x7fffffff;
 
 struct RedBuf {                     // per-warp partial results of up to four simultaneous reductions
-    unsigned long long key[4][SMO_WARPS_MAX];
-    int slot[4][SMO_WARPS_MAX];
+    unsigned long long key[4][SMO_WARPS];
+    int slot[4][SMO_WARPS];
 };
 
-// Block-wide argmin of R (key, slot) pairs: one __syncthreads, result in every thread. buf.slot[r][w] keeps
-// warp w's own best until the buffer's next use.
+// Block-wide argmin of R (key, slot) pairs: one __syncthreads, result in every thread.
 template <int R>
 __device__ __forceinline__ void block_argmin(RedBuf &buf, unsigned long long (&key)[R], int (&slot)[R]) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         warp_argmin_u64(key[r], slot[r]);
@@ -678,68 +674,12 @@ __device__ __forceinline__ void block_argmin(RedBuf &buf, unsigned long long (&k
     __syncthreads();
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        unsigned long long k = lane < nwarps ? buf.key[r][lane] : ~0ull;
-        int s = lane < nwarps ? buf.slot[r][lane] : NO_SLOT;
+        unsigned long long k = lane < SMO_WARPS ? buf.key[r][lane] : ~0ull;
+        int s = lane < SMO_WARPS ? buf.slot[r][lane] : NO_SLOT;
         warp_argmin_u64(k, s);
         key[r] = k; slot[r] = s;
     }
 }
-
-// ---- speculative row copies -------------------------------------------------------------------------
-// An iteration waits twice for a row of the ws x ws block to arrive from L2: row i after the first-order
-// argmin, row j after the second-order one. Nearly every row is used once, so a cache of used rows never
-// hits - but the next winner is usually one of this iteration's losers: the eight warps' own best slots of an
-// argmin contain the next argmin's winner about three times out of four. Two extra warps, which own no slot
-// and only keep step with the barriers, therefore copy the rows of those eight slots into a ring of rows in
-// shared memory (cp.async; one warp and one ring for the i rows, one for the j rows). The working warps look a
-// winner up in the ring's tags and read its row there, or from L2 if it is absent. The values read are the
-// same floats either way, so the iterates do not depend on what was copied.
-constexpr int PF_ROWS = 24;             // ring entries per list; a lookup compares one tag per lane
-
-// entry of the ring that holds row `slot`, or -1 (every lane returns the same value)
-__device__ __forceinline__ int pf_lookup(const int *tag, int slot) {
-    const int lane = threadIdx.x & 31;
-    const unsigned m = __ballot_sync(0xffffffffu, lane < PF_ROWS && tag[lane] == slot);
-    return m ? __ffs(m) - 1 : -1;
-}
-
-// The copying warp of one ring, after an argmin: starts the copies of the working warps' own best slots
-// (cand[0..SMO_WARPS)) that are neither the winner nor in the ring already, as one cp.async group. Entries are
-// handed out in ring order, except the one that holds the winner's row, which the working warps are reading.
-// `head` lives in the copying warp's registers: it is the only writer of this ring and its tags.
-__device__ __forceinline__ void pf_copy_batch(int *tag, int &head, float *ring, const float *__restrict__ kww, int ws,
-                                              const int *cand, int winner) {
-    const int lane = threadIdx.x & 31;
-    const int in_use = pf_lookup(tag, winner);
-    const int c = lane < SMO_WARPS ? cand[lane] : NO_SLOT;
-    bool want = c != NO_SLOT && c != winner;
-    for (int e = 0; e < PF_ROWS; ++e) want = want && tag[e] != c;
-    const unsigned m = __ballot_sync(0xffffffffu, want);
-    const int n_new = __popc(m), rank = __popc(m & ((1u << lane) - 1));
-    int my_e = 0, p = head;
-    for (int r = 0; r < n_new;) {
-        const int e = p % PF_ROWS;
-        ++p;
-        if (e == in_use) continue;
-        if (r == rank) my_e = e;
-        ++r;
-    }
-    head = p % PF_ROWS;
-    if (want) tag[my_e] = c;
-    for (unsigned left = m; left; left &= left - 1) {
-        const int b = __ffs(left) - 1;
-        const int cb = __shfl_sync(0xffffffffu, c, b), eb = __shfl_sync(0xffffffffu, my_e, b);
-        const float *src = kww + (size_t) cb * ws;
-        float *dst = ring + (size_t) eb * ws;
-        for (int x = lane * 4; x < ws; x += 128) {
-            const unsigned d = (unsigned) __cvta_generic_to_shared(dst + x);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + x) : "memory");
-        }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-}
-
-__device__ __forceinline__ void pf_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // Local solver. Slot t of the working set is owned by thread t % 256 (register copies of f, alpha,
 // y, diag); mirrors of f / alpha / y / diag in shared memory serve the few values every thread
@@ -748,34 +688,23 @@ __device__ __forceinline__ void pf_wait_all() { asm volatile("cp.async.wait_grou
 // lowest slot. NU = true: nu_smo_solve_kernel semantics of the CUDA backend
 // (smo_kernel.cu:118-252): bound held in float, float arithmetic in the curvature term.
 template <bool NU, int SLOTS>
-__global__ void __launch_bounds__(SMO_THREADS_PF)
+__global__ void __launch_bounds__(SMO_THREADS)
 local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict__ diag_ws,
                  const int *__restrict__ y_ws, const double *__restrict__ f_ws, double *__restrict__ alpha_ws,
                  double *__restrict__ alpha_diff, double Cp_in, double Cn_in, double eps, int max_iter,
                  double *__restrict__ diff, const int *__restrict__ ids, double *__restrict__ alpha_global,
-                 const int *__restrict__ stop, int prefetch, long long *__restrict__ row_ctr) {
+                 const int *__restrict__ stop) {
     if (stop && *stop) {            // queued past the end of a solve: no step, so the f update that follows adds zero
-        for (int t = threadIdx.x; t < ws; t += blockDim.x) alpha_diff[t] = 0;
+        for (int t = threadIdx.x; t < ws; t += SMO_THREADS) alpha_diff[t] = 0;
         return;
     }
-    // speculative row copies (C solver only): two rings of PF_ROWS rows in dynamic shared memory, filled by
-    // warps SMO_WARPS (i rows) and SMO_WARPS + 1 (j rows), which the launch adds when `prefetch` is set
-    extern __shared__ __align__(16) float pf_rings[];
-    __shared__ int pf_tag[2][32];
-    const bool PF = !NU && (prefetch & 1) != 0;
-    const bool copies = PF && (prefetch & 2) == 0;
-    const bool copy_i = copies && (threadIdx.x >> 5) == SMO_WARPS, copy_j = copies && (threadIdx.x >> 5) == SMO_WARPS + 1;
-    float *ring_i = pf_rings, *ring_j = pf_rings + (size_t) PF_ROWS * ws;
-    if (threadIdx.x < 64) pf_tag[threadIdx.x >> 5][threadIdx.x & 31] = -1;
-    int pf_head = 0;
     __shared__ RedBuf red[2];
     __shared__ double f_sm[1024], a_sm[1024];
     __shared__ float kd_sm[1024];
     __shared__ int y_sm[1024];
     const double Cp = NU ? (double) (float) Cp_in : Cp_in;
     const double Cn = NU ? Cp : Cn_in;
-    // threads past SMO_THREADS (the copying warps) own no slot: their slot numbers lie past the working set
-    const int tid = threadIdx.x < SMO_THREADS ? threadIdx.x : 1024;
+    const int tid = threadIdx.x;
     double f[SLOTS], a[SLOTS], aold[SLOTS];
     int y[SLOTS];
     float kd[SLOTS];
@@ -787,9 +716,17 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
             f_sm[t] = f[s]; a_sm[t] = a[s]; y_sm[t] = y[s]; kd_sm[t] = kd[s];
         } else { f[s] = 0; a[s] = aold[s] = 0; y[s] = 0; kd[s] = 0; }   // y = 0: member of no set
     }
+    // C solver: membership of I_up / I_low only changes for the two slots a step moves, so it is kept in
+    // registers and recomputed for those two instead of for every slot in every selection
+    bool in_up[SLOTS], in_low[SLOTS];
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+        in_up[s] = !NU && in_I_up(a[s], y[s], Cp, Cn);
+        in_low[s] = !NU && in_I_low(a[s], y[s], Cp, Cn);
+    }
     __syncthreads();
     double local_eps = 0;
-    int it = 0, n_ahead = 0;
+    int it = 0;
     for (;;) {
         // ---- first-order selection --------------------------------------------------------
         constexpr int R1 = NU ? 4 : 2;
@@ -802,8 +739,8 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
             const int t = tid + s * SMO_THREADS;
             const unsigned long long kf = ordered_key(f[s]), knf = ordered_key(-f[s]);
             if (!NU) {
-                if (in_I_up(a[s], y[s], Cp, Cn) && kf < key[0]) { key[0] = kf; slot[0] = t; }
-                if (in_I_low(a[s], y[s], Cp, Cn) && knf < key[1]) { key[1] = knf; slot[1] = t; }
+                if (in_up[s] && kf < key[0]) { key[0] = kf; slot[0] = t; }
+                if (in_low[s] && knf < key[1]) { key[1] = knf; slot[1] = t; }
             } else {
                 if (y[s] > 0 && a[s] < Cp && kf < key[0]) { key[0] = kf; slot[0] = t; }      // up, +
                 if (y[s] < 0 && a[s] > 0 && kf < key[1]) { key[1] = kf; slot[1] = t; }       // up, -
@@ -811,7 +748,6 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
                 if (y[s] < 0 && a[s] < Cp && knf < key[3]) { key[3] = knf; slot[3] = t; }    // low, -
             }
         }
-        if (copy_i) pf_wait_all();                  // the i rows copied during the last iteration have landed
         block_argmin<R1>(red[0], key, slot);
         // mirrors written only now: every thread has finished reading them for the last step
 #pragma unroll
@@ -824,16 +760,12 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
         const double up0 = key_to_double(key[0]);
         const double up1 = NU ? key_to_double(key[1]) : 0.0;
         float kI0[SLOTS], kI1[SLOTS];
-        const int e_i = PF ? pf_lookup(pf_tag[0], i0) : -1;          // row i copied ahead?
-        const float *row_i = e_i >= 0 ? ring_i + (size_t) e_i * ws : nullptr;
 #pragma unroll
         for (int s = 0; s < SLOTS; ++s) {
             const int t = tid + s * SMO_THREADS;
-            if (row_i) kI0[s] = t < ws ? row_i[t] : 0.0f;
-            else kI0[s] = t < ws ? __ldg(kww + (size_t) i0 * ws + t) : 0.0f;
+            kI0[s] = t < ws ? __ldg(kww + (size_t) i0 * ws + t) : 0.0f;
             kI1[s] = (NU && t < ws) ? __ldg(kww + (size_t) i1 * ws + t) : 0.0f;
         }
-        if (copy_i) pf_copy_batch(pf_tag[0], pf_head, ring_i, kww, ws, red[0].slot[0], slot[0]);
         double local_diff;
         if (!NU) local_diff = -key_to_double(key[1]) - up0;
         else local_diff = fmax(-key_to_double(key[2]) - up0, -key_to_double(key[3]) - up1);
@@ -842,7 +774,6 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
             if (tid == 0) diff[0] = local_diff;
         }
         if (it > max_iter || local_diff < local_eps) break;
-        n_ahead += e_i >= 0;
 
         // ---- second-order selection ---------------------------------------------------------
         constexpr int R2 = NU ? 2 : 1;
@@ -851,32 +782,69 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
 #pragma unroll
         for (int r = 0; r < R2; ++r) { key2[r] = KEY_POS_INF; slot2[r] = NO_SLOT; }
         const float kd_i0 = kd_sm[i0], kd_i1 = NU ? kd_sm[i1] : 0.0f;
+        if (!NU) {
+            // The exact quotient -b^2 / a costs a double-precision division per slot, and only the thread's best
+            // slot matters. An FP32 estimate of b^2 / a (relative error below 5e-7: two roundings to FP32, a
+            // product, a 2-ulp division) first rules out every slot whose estimate is more than 8e-6 below the
+            // thread's largest: its exact quotient is smaller by more than any rounding, so it can neither win nor
+            // tie. What is left - almost always one slot - is divided exactly. Estimates outside the range
+            // where the error bound holds send all of the thread's candidates to the exact path.
+            bool cnd[SLOTS];
+            double aIJ[SLOTS], bIJ[SLOTS];
+            float q32[SLOTS];
+            float m = -1.0f;
+            bool trust = true;
 #pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            const int t = tid + s * SMO_THREADS;
-            if (!NU) {
-                if (-up0 > -f[s] && in_I_low(a[s], y[s], Cp, Cn)) {
-                    const double aIJ = (double) (kd_i0 + kd[s]) - 2.0 * (double) kI0[s];
-                    const double bIJ = -up0 + f[s];
-                    const unsigned long long k = ordered_key(-bIJ * bIJ / aIJ);
-                    if (k < key2[0]) { key2[0] = k; slot2[0] = t; }
-                }
-            } else {
-                if (-up0 > -f[s] && y[s] > 0 && a[s] > 0) {
-                    const double aIJ = (double) (kd_i0 + kd[s] - 2 * kI0[s]);
-                    const double bIJ = -up0 + f[s];
-                    const unsigned long long k = ordered_key(-bIJ * bIJ / aIJ);
-                    if (k < key2[0]) { key2[0] = k; slot2[0] = t; }
-                }
-                if (-up1 > -f[s] && y[s] < 0 && a[s] < Cp) {
-                    const double aIJ = (double) (kd_i1 + kd[s] - 2 * kI1[s]);
-                    const double bIJ = -up1 + f[s];
-                    const unsigned long long k = ordered_key(-bIJ * bIJ / aIJ);
-                    if (k < key2[1]) { key2[1] = k; slot2[1] = t; }
+            for (int s = 0; s < SLOTS; ++s) {
+                cnd[s] = -up0 > -f[s] && in_low[s];
+                aIJ[s] = (double) (kd_i0 + kd[s]) - 2.0 * (double) kI0[s];
+                bIJ[s] = -up0 + f[s];
+                const float b32 = (float) bIJ[s], a32 = (float) aIJ[s];
+                q32[s] = __fdividef(b32 * b32, a32);
+                trust = trust && (!cnd[s] || (b32 > 1e-15f && b32 < 1e15f && a32 > 1e-30f && a32 < 1e30f));
+                if (cnd[s]) m = fmaxf(m, q32[s]);
+            }
+            const float thr = m * (1.0f - 8e-6f);
+            // the first slot that holds the largest estimate, divided without a branch
+            int pick = SLOTS;
+            double pa = 1.0, pb = 0.0;
+#pragma unroll
+            for (int s = SLOTS - 1; s >= 0; --s)
+                if (cnd[s] && q32[s] == m) { pick = s; pa = aIJ[s]; pb = bIJ[s]; }
+            if (pick < SLOTS) {
+                key2[0] = ordered_key(-pb * pb / pa);
+                slot2[0] = tid + pick * SMO_THREADS;
+            }
+            // any other slot the estimate cannot rule out: exact, ties to the lower slot as in a pass in slot order
+            bool more = false;
+#pragma unroll
+            for (int s = 0; s < SLOTS; ++s) more = more || (cnd[s] && s != pick && (!trust || q32[s] >= thr));
+            if (more) {
+#pragma unroll
+                for (int s = 0; s < SLOTS; ++s) {
+                    if (cnd[s] && s != pick && (!trust || q32[s] >= thr)) {
+                        const int t = tid + s * SMO_THREADS;
+                        const unsigned long long k = ordered_key(-bIJ[s] * bIJ[s] / aIJ[s]);
+                        if (k < key2[0] || (k == key2[0] && t < slot2[0])) { key2[0] = k; slot2[0] = t; }
+                    }
                 }
             }
+        } else {
+#pragma unroll
+            for (int s = 0; s < SLOTS; ++s) {
+                const int t = tid + s * SMO_THREADS;
+                // every slot computes its quotients, candidates or not (the others divide by one and are
+                // discarded): the divisions of a thread's slots then overlap instead of one divergent branch each
+                const bool c0 = -up0 > -f[s] && y[s] > 0 && a[s] > 0;
+                const bool c1 = -up1 > -f[s] && y[s] < 0 && a[s] < Cp;
+                const double a0 = (double) (kd_i0 + kd[s] - 2 * kI0[s]), a1 = (double) (kd_i1 + kd[s] - 2 * kI1[s]);
+                const double b0 = -up0 + f[s], b1 = -up1 + f[s];
+                const double v0 = -b0 * b0 / (c0 ? a0 : 1.0), v1 = -b1 * b1 / (c1 ? a1 : 1.0);
+                const unsigned long long k0 = ordered_key(v0), k1 = ordered_key(v1);
+                if (c0 && k0 < key2[0]) { key2[0] = k0; slot2[0] = t; }
+                if (c1 && k1 < key2[1]) { key2[1] = k1; slot2[1] = t; }
+            }
         }
-        if (copy_j) pf_wait_all();
         block_argmin<R2>(red[1], key2, slot2);
         int i, j2;
         double up;
@@ -890,18 +858,13 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
         // ---- step length, computed redundantly by every thread ---------------------------------
         const double ai = a_sm[i], aj = a_sm[j2], fj = f_sm[j2];
         const int yi = y_sm[i], yj = y_sm[j2];
-        const float kij = row_i ? row_i[j2] : __ldg(kww + (size_t) i * ws + j2);
-        const int e_j = PF ? pf_lookup(pf_tag[1], j2) : -1;          // row j copied ahead?
-        n_ahead += e_j >= 0;
-        const float *row_j = e_j >= 0 ? ring_j + (size_t) e_j * ws : nullptr;
+        const float kij = __ldg(kww + (size_t) i * ws + j2);
         float kJ[SLOTS];
 #pragma unroll
         for (int s = 0; s < SLOTS; ++s) {
             const int t = tid + s * SMO_THREADS;
-            if (row_j) kJ[s] = t < ws ? row_j[t] : 0.0f;
-            else kJ[s] = t < ws ? __ldg(kww + (size_t) j2 * ws + t) : 0.0f;
+            kJ[s] = t < ws ? __ldg(kww + (size_t) j2 * ws + t) : 0.0f;
         }
-        if (copy_j) pf_copy_batch(pf_tag[1], pf_head, ring_j, kww, ws, red[1].slot[0], slot2[0]);
         const double alpha_i_diff = yi > 0 ? Cp - ai : ai;
         const double curv = NU ? (double) (kd_sm[i] + kd_sm[j2] - 2 * kij)
                                : (double) (kd_sm[i] + kd_sm[j2]) - 2.0 * (double) kij;
@@ -912,6 +875,10 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
             const int t = tid + s * SMO_THREADS;
             if (t == i) a[s] += l * yi;
             if (t == j2) a[s] -= l * yj;
+            if (!NU && (t == i || t == j2)) {
+                in_up[s] = in_I_up(a[s], y[s], Cp, Cn);
+                in_low[s] = in_I_low(a[s], y[s], Cp, Cn);
+            }
             if (t < ws) {
                 const float kI = use1 ? kI1[s] : kI0[s];
                 if (NU) f[s] -= l * (double) (kJ[s] - kI);
@@ -929,10 +896,7 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
             if (alpha_global && ids[t] >= 0) alpha_global[ids[t]] = a[s];
         }
     }
-    if (tid == 0) {
-        diff[1] = it;
-        if (row_ctr) { row_ctr[0] += 2ll * it; row_ctr[1] += n_ahead; }
-    }
+    if (tid == 0) diff[1] = it;
 }
 
 // ---- gather of the working set's block and vectors ---------------------------------------------
@@ -978,9 +942,7 @@ __global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *
 // histogram over the stamps; ties go to the lower row number, so the choice does not depend on thread timing.
 // Everything stays on the device: the engine reads the number of misses from memory.
 constexpr int CACHE_THREADS = 1024, CACHE_BINS = 2048;
-enum { CACHE_N_MISS = 0, CACHE_HITS = 1, CACHE_MISSES = 2, CACHE_BLOCKS = 3, CACHE_BLOCKS_SAVED = 4,
-       LOCAL_ROW_READS = 5, LOCAL_ROWS_AHEAD = 6,      // counted by the local solver
-       CACHE_CTRS = 8 };
+enum { CACHE_N_MISS = 0, CACHE_HITS = 1, CACHE_MISSES = 2, CACHE_BLOCKS = 3, CACHE_BLOCKS_SAVED = 4, CACHE_CTRS = 8 };
 
 __device__ __forceinline__ int cache_bin(int stamp, int now) {
     // older -> smaller bin; never-used rows (stamp 0) are the oldest; rows used in this iteration are not candidates
@@ -1417,23 +1379,12 @@ static inline int rows_vec_ok(const float *rows, long long ld) {
 static tsvm_status launch_local_smo(int solver_kind, int ws, const float *kww, const float *diag_ws, const int *y_ws,
                                     const double *f_ws, double *alpha_ws, double *alpha_diff, double Cp, double Cn,
                                     double eps, int max_iter, double *diff, const int *ids, double *alpha_global,
-                                    cudaStream_t st, const int *stop = nullptr, long long *row_ctr = nullptr) {
+                                    cudaStream_t st, const int *stop = nullptr) {
     const bool nu = solver_kind != TSVM_SOLVER_C;
     const int slots = ceil_div(ws, SMO_THREADS);
-    // speculative row copies: rows must be whole 16-byte chunks per lane and the rings must fit
-    static const int pf_mode = [] { const char *e = getenv("TSVM_LOCAL_PREFETCH"); return e ? atoi(e) : 0; }();
-    const size_t ring_bytes = (size_t) 2 * PF_ROWS * ws * sizeof(float);
-    const bool pf = !nu && pf_mode != 0 && ws % 128 == 0 && (reinterpret_cast<uintptr_t>(kww) & 15) == 0 &&
-                    ring_bytes <= (size_t) 200 * 1024;
-    const size_t smem = pf ? ring_bytes : 0;
-    const int pf_arg = !pf ? 0 : (pf_mode == 2 ? 0 : pf_mode == 3 ? 3 : 1);
 #define SMO_CASE(NU, S)                                                                                        \
-    do {                                                                                                       \
-        if (pf) TSVM_ONCE_PER_DEVICE(TSVM_CUDA(cudaFuncSetAttribute(                                           \
-            (local_smo_kernel<NU, S>), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));             \
-        TSVM_LAUNCH((local_smo_kernel<NU, S>), 1, pf ? SMO_THREADS_PF : SMO_THREADS, smem, st, ws, kww, diag_ws, y_ws, f_ws, alpha_ws, \
-                    alpha_diff, Cp, Cn, eps, max_iter, diff, ids, alpha_global, stop, pf_arg, row_ctr);             \
-    } while (0)
+    TSVM_LAUNCH((local_smo_kernel<NU, S>), 1, SMO_THREADS, 0, st, ws, kww, diag_ws, y_ws, f_ws, alpha_ws,      \
+                alpha_diff, Cp, Cn, eps, max_iter, diff, ids, alpha_global, stop)
     if (!nu) {
         if (slots <= 1) SMO_CASE(false, 1); else if (slots <= 2) SMO_CASE(false, 2); else SMO_CASE(false, 4);
     } else {
@@ -1753,7 +1704,7 @@ struct tsvm_solver {
         *miss_slot = nullptr, *victims = nullptr;
     long long *cache_ctr = nullptr;
     float *miss_hi = nullptr, *miss_lo = nullptr, *miss_sd = nullptr, *miss_unscale = nullptr;
-    long long hits = 0, misses = 0, row_blocks = 0, row_blocks_saved = 0, local_row_reads = 0, local_rows_ahead = 0;
+    long long hits = 0, misses = 0, row_blocks = 0, row_blocks_saved = 0;
     // iteration state (csmosolver.cpp:51-57)
     long long iter = 0, local_iter = 0, rows_made = 0, launches0 = 0;
     int local_max_iter = 0;
@@ -1948,7 +1899,7 @@ struct tsvm_solver {
                         y_ws, f_ws, a_ws, q, row_slot);
             TSVM_CUDA(cudaEventRecord(E.l0, st2));
             TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter,
-                                      diff, ids, alpha, st2, stop, cache_ctr + LOCAL_ROW_READS));
+                                      diff, ids, alpha, st2, stop));
             TSVM_CUDA(cudaEventRecord(E.l1, st2));
             // the rows that were in the buffer already can be applied to f at once (HBM-bound, next to the
             // tensor-bound launch); the new rows follow on the first stream
@@ -1971,7 +1922,7 @@ struct tsvm_solver {
                         y_ws, f_ws, a_ws, ws, row_slot);
             TSVM_CUDA(cudaEventRecord(E.l0, st));
             TSVM_TRY(launch_local_smo(kind, ws, kww, diag_ws, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter,
-                                      diff, ids, alpha, st, stop, cache_ctr + LOCAL_ROW_READS));
+                                      diff, ids, alpha, st, stop));
             TSVM_CUDA(cudaEventRecord(E.l1, st));
         } else {
             TSVM_CUDA(cudaStreamWaitEvent(st, ev_join, 0));
@@ -2040,7 +1991,6 @@ struct tsvm_solver {
         }
         hits = c.ctr[CACHE_HITS]; misses = c.ctr[CACHE_MISSES];
         row_blocks = c.ctr[CACHE_BLOCKS]; row_blocks_saved = c.ctr[CACHE_BLOCKS_SAVED];
-        local_row_reads = c.ctr[LOCAL_ROW_READS]; local_rows_ahead = c.ctr[LOCAL_ROWS_AHEAD];
         iter = c.iter;
         local_iter = c.local_iter;
         diff0 = c.diff0;
@@ -2074,8 +2024,6 @@ struct tsvm_solver {
         out->cache_rows = cache_cap;
         out->row_blocks = row_blocks;
         out->row_blocks_saved = row_blocks_saved;
-        out->local_row_reads = local_row_reads;
-        out->local_rows_ahead = local_rows_ahead;
     }
 
     // rho and objective (csmosolver.cpp:167-187,227-239; nusmosolver.cpp:9-46,120-126)
