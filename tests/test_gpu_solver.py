@@ -379,3 +379,66 @@ def test_working_set_that_cannot_be_filled_is_an_error(capi):
         capi.smo_solve(km, y, alpha, f, 1e-3, 1.0, 0.0, 1024)
     assert torch.isfinite(alpha).all() and torch.isfinite(f).all()
     km.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("data", ["dense_tensor", "csr"])
+def test_queued_iterations_equal_single_steps(capi, data):
+    """tsvm_solver_iterate queues up to eight outer iterations between reads of the device's verdict; the
+    iterations queued past the one that ends the solve must be no-ops. One iteration per call, all of them in
+    one call, and tsvm_smo_solve (with and without an iteration cap, csmosolver.cpp:110) must agree bit for bit."""
+    import torch
+    if data == "dense_tensor":
+        prob = synth.config5(5000, d=200)
+        make = lambda: capi.KernelMatrix(dense=torch.from_numpy(prob["X"]).cuda(), gamma=prob["gamma"])
+    else:
+        prob = synth.config2(4000)
+        make = lambda: device_matrix(capi, prob)
+    y = np.where(prob["y"] > 0, 1, -1).astype(np.int32)
+    n = len(y)
+
+    def fresh():
+        return (torch.zeros(n, dtype=torch.float64, device="cuda"), torch.from_numpy(-y.astype(np.float64)).cuda())
+
+    # one iteration per call, until done
+    km = make()
+    a1, f1 = fresh()
+    sv = capi.Solver(km, torch.from_numpy(y).cuda(), a1, f1, 1e-3, 1.0, 1.0, 512)
+    steps = 0
+    while not sv.iterate(1):
+        steps += 1
+        assert steps < 2000
+    s1 = sv.stats()
+    sv.close(); km.close()
+    assert s1["outer_iters"] == steps + 1
+    # all in one call: far more iterations asked for than the solve takes
+    km = make()
+    a2, f2 = fresh()
+    sv = capi.Solver(km, torch.from_numpy(y).cuda(), a2, f2, 1e-3, 1.0, 1.0, 512)
+    assert sv.iterate(s1["outer_iters"] + 50)
+    s2 = sv.stats()
+    sv.close(); km.close()
+    assert s2["outer_iters"] == s1["outer_iters"] and s2["local_iters"] == s1["local_iters"]
+    assert s2["final_diff"] == s1["final_diff"]
+    assert torch.equal(a1, a2) and torch.equal(f1, f2)
+    # the one-call solver
+    km = make()
+    a3, f3 = fresh()
+    _, s3 = capi.smo_solve(km, torch.from_numpy(y).cuda(), a3, f3, 1e-3, 1.0, 1.0, 512)
+    assert s3["outer_iters"] == s1["outer_iters"] and torch.equal(a1, a3) and torch.equal(f1, f3)
+    km.close()
+    # an iteration cap in the middle of a queue: max_iter = k means k + 1 iterations
+    cap = 4
+    assert s1["outer_iters"] > cap + 2
+    km = make()
+    a4, f4 = fresh()
+    _, s4 = capi.smo_solve(km, torch.from_numpy(y).cuda(), a4, f4, 1e-3, 1.0, 1.0, 512, max_iter=cap)
+    km.close()
+    km = make()
+    a5, f5 = fresh()
+    sv = capi.Solver(km, torch.from_numpy(y).cuda(), a5, f5, 1e-3, 1.0, 1.0, 512)
+    for _ in range(cap + 1):
+        sv.iterate(1)
+    sv.close(); km.close()
+    assert s4["outer_iters"] == cap + 1
+    assert torch.equal(a4, a5) and torch.equal(f4, f5)
