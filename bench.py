@@ -334,8 +334,9 @@ def extra_rooflines(torch, capi, synth, hbm_peak, peak_src, n):
     sel = capi.WorkingSetSelector(n, WS)
     us = time_calls(torch, lambda: sel.select(fv, av, yv, 1.0, 1.0, Q, in_ws=flags), 50)
     out.append(hbm_roofline("working-set selection (radix top-k + merge, config 5: 512 of %d)" % n, n * 21, us, hbm_peak,
-                            peak_src, "bytes = n*(8 f + 8 alpha + 4 y + 1 flag) read once; the selection is several "
-                                      "short launches, so this is launch-latency-bound, not bandwidth-bound"))
+                            peak_src, "bytes = n*(8 f + 8 alpha + 4 y + 1 flag) read once; the selection is one cooperative "
+                                      "launch of two or three sweeps separated by grid barriers plus an exact sort of the "
+                                      "candidates by one block: a latency chain, not bandwidth-bound"))
     sel.close()
     del yv, fv, av, flags, f
     # CSR kernel rows, 512 rows per call
