@@ -348,7 +348,8 @@ def extra_rooflines(torch, capi, synth, hbm_peak, peak_src, n):
         nn = km.n
         idx_np = np.random.default_rng(0).choice(nn, Q, replace=False).astype(np.int32)
         idx = torch.from_numpy(idx_np).cuda()
-        buf = torch.empty((Q, nn), dtype=torch.float32, device="cuda")
+        # row stride as in the solver's row buffer (a multiple of four floats)
+        buf = torch.empty((Q, (nn + 3) // 4 * 4), dtype=torch.float32, device="cuda")
         us = time_calls(torch, lambda: km.get_rows(idx, buf), 40)
         nnz, nnz_ws = int(rp[-1]), int(np.diff(rp)[idx_np].sum())
         r = hbm_roofline("CSR kernel rows (%s: 512 rows x %d, nnz %d)" % (tag, nn, nnz),

@@ -204,3 +204,50 @@ def test_error_returns(capi):
         capi.smo_solve(km, torch.ones(200, dtype=torch.int32, device="cuda"),
                        torch.zeros(200, dtype=torch.float64, device="cuda"),
                        torch.zeros(200, dtype=torch.float64, device="cuda"), 1e-3, 1.0, 1.0, 300)   # ws > n
+
+
+_CSR_ENGINE_DIGEST = r"""
+import hashlib, sys
+import numpy as np, torch
+from thundersvm_b200 import capi
+rng = np.random.default_rng(17)
+n, d = 4099, 150                                   # n not a multiple of 32; d within the shared-memory panel
+lens = rng.integers(0, 70, n)                      # empty instances and instances longer than one 32-entry batch
+lens[::97] = 0
+rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+col = np.concatenate([np.sort(rng.choice(d, k, replace=False)) for k in lens]).astype(np.int32)
+val = rng.standard_normal(len(col)).astype(np.float32)
+h = hashlib.sha256()
+for kernel, kw in (("rbf", dict(gamma=0.3)), ("poly", dict(gamma=0.2, coef0=1.0, degree=3)), ("linear", {})):
+    km = capi.KernelMatrix(csr=(torch.from_numpy(val).cuda(), torch.from_numpy(rp).cuda(), torch.from_numpy(col).cuda()),
+                           d=d, kernel=kernel, **kw)
+    for q in (1024, 512, 300, 7):
+        ids = rng.choice(n, q, replace=False).astype(np.int32)
+        if q == 300:
+            ids[[5, 299]] = -1                     # empty working-set slots
+        for ld in (n, (n + 3) // 4 * 4):           # unaligned and aligned row stride
+            out = torch.zeros((q, ld), dtype=torch.float32, device="cuda")
+            km.get_rows(torch.from_numpy(ids).cuda(), out)
+            h.update(out[:, :n].contiguous().cpu().numpy().tobytes())
+    km.close()
+print(h.hexdigest())
+"""
+
+
+def test_csr_engines_agree_bit_for_bit():
+    """CSR data with few features runs on the engine that keeps the requested rows' panel in shared memory,
+    everything else on the engine that reads it from L2. Both compute every value as the same FP32 recurrence
+    over the instance's stored entries in storage order, so switching the first one off (TSVM_CSR_SMEM=0, read
+    once per process) must not change a bit: ragged and empty instances, empty slots, every request size,
+    aligned and unaligned output rows, three kernel functions."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    digests = []
+    for flag in ("0", "1"):
+        env = dict(os.environ, TSVM_CSR_SMEM=flag, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        r = subprocess.run([sys.executable, "-c", _CSR_ENGINE_DIGEST], env=env, capture_output=True, text=True,
+                           timeout=600, cwd=root)
+        assert r.returncode == 0, r.stderr[-2000:]
+        digests.append(r.stdout.strip().splitlines()[-1])
+    assert len(digests[0]) == 64 and digests[0] == digests[1]

@@ -560,6 +560,149 @@ csr_rows_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr, 
     }
 }
 
+// ---- CSR engine for few features: the panel in shared memory ---------------------------------------
+// csr_rows_kernel reads a 2 KB panel row from L2 for every stored entry; with d features the panel is only
+// d x 1 KB per 256 requested rows, which fits in shared memory for d <= CSR_SMEM_MAX_D. A block then loads
+// its 256-row part of the panel once and sweeps instance tiles with it (grid: blocks x parts, every block a
+// strided share of the 32-instance tiles): a stored entry costs two 16-byte shared-memory loads and eight
+// multiply-adds per lane instead of a trip to L2. Same FP32 recurrence in storage order per (row, instance),
+// so the values are those of csr_rows_kernel bit for bit. Results go through a double-buffered transposed
+// tile so that every requested row receives 128-byte coalesced stores.
+constexpr int CSR_SMEM_THREADS = 512, CSR_SMEM_PART = 256, CSR_SMEM_TILE = CSR_SMEM_PART * 33;
+constexpr int CSR_SMEM_MAX_D = (227 * 1024 - 2 * CSR_SMEM_TILE * 4 - 2 * CSR_SMEM_PART * 4 - 64) / (CSR_SMEM_PART * 4);
+
+__global__ void __launch_bounds__(CSR_SMEM_THREADS, 1)
+csr_rows_smem_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr, const int *__restrict__ col, int n,
+                     int d, const float *__restrict__ WT, int wt_ld, int m_launch, const float *__restrict__ sd,
+                     const float *__restrict__ sd_rows, KernelFn fn, float *__restrict__ out, long long ld_out,
+                     const int *__restrict__ m_dev, const int *__restrict__ row_slot) {
+    extern __shared__ __align__(16) float csr_sm[];          // panel [d][256] | tile [2][256][33]
+    const int m = m_dev ? min(m_launch, max(*m_dev, 0)) : m_launch;     // the count found on the device, if any
+    const int c0 = blockIdx.y * CSR_SMEM_PART;
+    if (c0 >= m) return;
+    const int mh = min(CSR_SMEM_PART, m - c0);
+    float4 *panel4 = reinterpret_cast<float4 *>(csr_sm);
+    float *tiles = csr_sm + (size_t) d * CSR_SMEM_PART;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    __shared__ int orow_sm[CSR_SMEM_PART];
+    __shared__ float sdr_sm[CSR_SMEM_PART];
+    if (tid < mh) {
+        orow_sm[tid] = row_slot ? row_slot[c0 + tid] : c0 + tid;
+        sdr_sm[tid] = sd_rows[c0 + tid];
+    }
+    for (int i = tid; i < d * (CSR_SMEM_PART / 4); i += CSR_SMEM_THREADS) {
+        const int c = i / (CSR_SMEM_PART / 4), v = i % (CSR_SMEM_PART / 4);
+        panel4[i] = __ldg(reinterpret_cast<const float4 *>(WT + (size_t) c * wt_ld + c0) + v);
+    }
+    __syncthreads();
+    const int n_tiles = (n + 31) / 32;
+    const bool vec_ok = (ld_out & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    constexpr int PER_WARP = 32 / (CSR_SMEM_THREADS / 32);        // instances of a tile per warp
+    // The CSR entries of the next tile's instances are fetched (row bounds, then the first 32 entries) while
+    // this tile is computed: the two dependent trips to memory per instance stay off the critical path.
+    int nb[PER_WARP], ne[PER_WARP], ncc[PER_WARP];
+    float nvv[PER_WARP], nsd = 0.0f;
+    auto fetch = [&](int ti) {
+#pragma unroll
+        for (int u = 0; u < PER_WARP; ++u) {
+            const int j = ti * 32 + warp + u * (CSR_SMEM_THREADS / 32);
+            nb[u] = ne[u] = 0; ncc[u] = 0; nvv[u] = 0.0f;
+            if (ti < n_tiles && j < n) { nb[u] = row_ptr[j]; ne[u] = row_ptr[j + 1]; }
+        }
+#pragma unroll
+        for (int u = 0; u < PER_WARP; ++u)
+            if (nb[u] + lane < ne[u]) { ncc[u] = col[nb[u] + lane]; nvv[u] = val[nb[u] + lane]; }
+        const int j = ti * 32 + lane;
+        nsd = (ti < n_tiles && j < n) ? sd[j] : 0.0f;
+    };
+    fetch(blockIdx.x);
+    int buf = 0;
+    for (int ti = blockIdx.x; ti < n_tiles; ti += gridDim.x, buf ^= 1) {
+        const int j0 = ti * 32;
+        float *T = tiles + buf * CSR_SMEM_TILE;
+        int cb[PER_WARP], ce[PER_WARP], ccc[PER_WARP];
+        float cvv[PER_WARP];
+#pragma unroll
+        for (int u = 0; u < PER_WARP; ++u) { cb[u] = nb[u]; ce[u] = ne[u]; ccc[u] = ncc[u]; cvv[u] = nvv[u]; }
+        const float sdj = nsd;
+        fetch(ti + gridDim.x);
+#pragma unroll
+        for (int u = 0; u < PER_WARP; ++u) {
+            const int jj = warp + u * (CSR_SMEM_THREADS / 32);
+            // rows c0 + 4 * lane + 0..3 and c0 + 128 + 4 * lane + 0..3: a warp's 16-byte loads cover 512 contiguous bytes
+            float4 a0 = make_float4(0, 0, 0, 0), a1 = make_float4(0, 0, 0, 0);
+            for (int p0 = cb[u]; p0 < ce[u]; p0 += 32) {
+                int cc = ccc[u];
+                float vv = cvv[u];
+                if (p0 != cb[u]) {                  // beyond the prefetched entries
+                    cc = 0; vv = 0;
+                    if (p0 + lane < ce[u]) { cc = col[p0 + lane]; vv = val[p0 + lane]; }
+                }
+                const int cnt = min(32, ce[u] - p0);
+                int t = 0;
+                // four stored entries at a time: their panel loads are independent, the sums keep the storage order
+                for (; t + 4 <= cnt; t += 4) {
+                    float x[4];
+                    float4 w0[4], w1[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int c = __shfl_sync(0xffffffffu, cc, t + k);
+                        x[k] = __shfl_sync(0xffffffffu, vv, t + k);
+                        const float4 *w = panel4 + (size_t) c * (CSR_SMEM_PART / 4) + lane;
+                        w0[k] = w[0]; w1[k] = w[32];
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        a0.x = fmaf(x[k], w0[k].x, a0.x); a0.y = fmaf(x[k], w0[k].y, a0.y);
+                        a0.z = fmaf(x[k], w0[k].z, a0.z); a0.w = fmaf(x[k], w0[k].w, a0.w);
+                        a1.x = fmaf(x[k], w1[k].x, a1.x); a1.y = fmaf(x[k], w1[k].y, a1.y);
+                        a1.z = fmaf(x[k], w1[k].z, a1.z); a1.w = fmaf(x[k], w1[k].w, a1.w);
+                    }
+                }
+                for (; t < cnt; ++t) {
+                    const int c = __shfl_sync(0xffffffffu, cc, t);
+                    const float x = __shfl_sync(0xffffffffu, vv, t);
+                    const float4 *w = panel4 + (size_t) c * (CSR_SMEM_PART / 4) + lane;
+                    const float4 w0 = w[0], w1 = w[32];
+                    a0.x = fmaf(x, w0.x, a0.x); a0.y = fmaf(x, w0.y, a0.y);
+                    a0.z = fmaf(x, w0.z, a0.z); a0.w = fmaf(x, w0.w, a0.w);
+                    a1.x = fmaf(x, w1.x, a1.x); a1.y = fmaf(x, w1.y, a1.y);
+                    a1.z = fmaf(x, w1.z, a1.z); a1.w = fmaf(x, w1.w, a1.w);
+                }
+            }
+            // row 4 * lane + k (+ 128) sits in tile row 32 * k + lane (+ 128): a warp's stores hit 32 banks each
+            T[(0 * 32 + lane) * 33 + jj] = a0.x; T[(1 * 32 + lane) * 33 + jj] = a0.y;
+            T[(2 * 32 + lane) * 33 + jj] = a0.z; T[(3 * 32 + lane) * 33 + jj] = a0.w;
+            T[(4 * 32 + lane) * 33 + jj] = a1.x; T[(5 * 32 + lane) * 33 + jj] = a1.y;
+            T[(6 * 32 + lane) * 33 + jj] = a1.z; T[(7 * 32 + lane) * 33 + jj] = a1.w;
+        }
+        __syncthreads();
+        // (the other buffer is written next; this one again only after the next barrier, which every warp
+        // reaches after it has read its rows here)
+        if (vec_ok && j0 + 32 <= n) {
+            // four consecutive instances of one row per thread, one 16-byte store: a warp covers four rows
+            const int jq = 4 * (lane & 7);
+            const float s0 = __shfl_sync(0xffffffffu, sdj, jq), s1 = __shfl_sync(0xffffffffu, sdj, jq + 1),
+                        s2 = __shfl_sync(0xffffffffu, sdj, jq + 2), s3 = __shfl_sync(0xffffffffu, sdj, jq + 3);
+#pragma unroll 2
+            for (int c = 4 * warp + (lane >> 3); c < mh; c += 4 * (CSR_SMEM_THREADS / 32)) {
+                const float *tr = T + ((((c >> 7) << 2) + (c & 3)) * 32 + ((c & 127) >> 2)) * 33 + jq;
+                const float sr = sdr_sm[c];
+                float4 o;
+                o.x = apply_kernel(fn, tr[0], sr, s0); o.y = apply_kernel(fn, tr[1], sr, s1);
+                o.z = apply_kernel(fn, tr[2], sr, s2); o.w = apply_kernel(fn, tr[3], sr, s3);
+                *reinterpret_cast<float4 *>(out + (size_t) orow_sm[c] * ld_out + j0 + jq) = o;
+            }
+        } else {
+            const int j = j0 + lane;
+            for (int c = warp; c < mh; c += CSR_SMEM_THREADS / 32) {
+                const float dot = T[((((c >> 7) << 2) + (c & 3)) * 32 + ((c & 127) >> 2)) * 33 + lane];
+                if (j < n) out[(size_t) orow_sm[c] * ld_out + j] = apply_kernel(fn, dot, sdr_sm[c], sdj);
+            }
+        }
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 
 static tsvm_status ensure_scratch(tsvm_km *km, int m) {
@@ -636,6 +779,12 @@ static tsvm_status finish_create(tsvm_km *km, cudaStream_t st) {
     return ensure_planes(km, st);
 }
 
+// TSVM_CSR_SMEM=0 keeps the L2-panel engine for every CSR matrix (used to compare the two engines)
+static bool csr_smem_engine_allowed() {
+    static const bool on = [] { const char *e = getenv("TSVM_CSR_SMEM"); return !e || atoi(e) != 0; }();
+    return on;
+}
+
 static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
     // W / WT and sd_rows are staged; run the engine.
     if (km->dense) {
@@ -643,6 +792,26 @@ static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out,
         dim3 grid(ceil_div(km->n, 64), ceil_div(m, 64));
         TSVM_LAUNCH(dense_rows_simt_kernel, grid, 256, 0, st, km->X, km->ldx, km->n, km->W, km->d_pad, m, km->d_pad,
                     km->self_dot, km->sd_rows, km->fn, out, ld_out, km->rows_m_dev, km->rows_slot_dev);
+        return TSVM_OK;
+    }
+    if (km->d <= CSR_SMEM_MAX_D && csr_smem_engine_allowed()) {
+        // few features: the panel of 256 requested rows fits in shared memory
+        const size_t smem = ((size_t) km->d * CSR_SMEM_PART + 2 * CSR_SMEM_TILE) * sizeof(float);
+        TSVM_ONCE_PER_DEVICE(TSVM_CUDA(cudaFuncSetAttribute(csr_rows_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                            (int) (((size_t) CSR_SMEM_MAX_D * CSR_SMEM_PART + 2 * CSR_SMEM_TILE) * sizeof(float)))));
+        const int parts = ceil_div(m, CSR_SMEM_PART);
+        int sms = 148;
+        {
+            int dev = 0;
+            TSVM_CUDA(cudaGetDevice(&dev));
+            TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        }
+        int bx = sms / parts > 0 ? sms / parts : 1;
+        const int n_tiles = ceil_div(km->n, 32);
+        if (bx > n_tiles) bx = n_tiles;
+        TSVM_LAUNCH(csr_rows_smem_kernel, dim3(bx, parts), CSR_SMEM_THREADS, smem, st, km->val, km->row_ptr, km->col,
+                    km->n, km->d, km->WT, km->wt_ld, m, km->self_dot, km->sd_rows, km->fn, out, ld_out, km->rows_m_dev,
+                    km->rows_slot_dev);
         return TSVM_OK;
     }
     const int nv = ceil_div(m, 128);
