@@ -554,6 +554,23 @@ csr_rows_kernel(const float *__restrict__ val, const int *__restrict__ row_ptr, 
     __syncthreads();
     const int j = j0 + lane;
     const float sdj = j < n ? sd[j] : 0.0f;
+    if ((ld_out & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && j0 + 32 <= n) {
+        // four consecutive instances of one row per thread, one 16-byte store: a warp covers four rows
+        const int jq = 4 * (lane & 7);
+        const float s0 = __shfl_sync(0xffffffffu, sdj, jq), s1 = __shfl_sync(0xffffffffu, sdj, jq + 1),
+                    s2 = __shfl_sync(0xffffffffu, sdj, jq + 2), s3 = __shfl_sync(0xffffffffu, sdj, jq + 3);
+#pragma unroll 2
+        for (int c = 4 * warp + (lane >> 3); c < m; c += 32) {
+            const float *tr = tile + c * 33 + jq;
+            const float sr = sd_rows[c];
+            const size_t orow = row_slot ? (size_t) row_slot[c] : (size_t) c;
+            float4 o;
+            o.x = apply_kernel(fn, tr[0], sr, s0); o.y = apply_kernel(fn, tr[1], sr, s1);
+            o.z = apply_kernel(fn, tr[2], sr, s2); o.w = apply_kernel(fn, tr[3], sr, s3);
+            *reinterpret_cast<float4 *>(out + orow * ld_out + j0 + jq) = o;
+        }
+        return;
+    }
     for (int c = warp; c < m; c += 8) {
         const size_t orow = row_slot ? (size_t) row_slot[c] : (size_t) c;
         if (j < n) out[orow * ld_out + j] = apply_kernel(fn, tile[c * 33 + lane], sd_rows[c], sdj);
