@@ -802,15 +802,19 @@ static bool csr_smem_engine_allowed() {
     return on;
 }
 
-static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
-    // W / WT and sd_rows are staged; run the engine.
-    if (km->dense) {
-        if (use_tensor_engine(km)) return launch_dense_tc(km, m, out, ld_out, st);
-        dim3 grid(ceil_div(km->n, 64), ceil_div(m, 64));
-        TSVM_LAUNCH(dense_rows_simt_kernel, grid, 256, 0, st, km->X, km->ldx, km->n, km->W, km->d_pad, m, km->d_pad,
-                    km->self_dot, km->sd_rows, km->fn, out, ld_out, km->rows_m_dev, km->rows_slot_dev);
-        return TSVM_OK;
-    }
+// A set of stored instances the CSR engines sweep: the kernel matrix's own, or a gathered subset of them.
+struct CsrView {
+    const float *val;
+    const int *row_ptr, *col;
+    int n;
+    const float *sd;                // self dots of the instances
+};
+
+// Kernel rows of the m requested rows staged in `panel` (feature-major, row stride km->wt_ld; self dots in
+// sd_rows) against the instances of X. spare_sms: SMs the persistent engine leaves free.
+static tsvm_status csr_engine_launch(tsvm_km *km, const CsrView &X, const float *panel, const float *sd_rows, int m,
+                                     float *out, long long ld_out, const int *m_dev, const int *row_slot, int spare_sms,
+                                     cudaStream_t st) {
     if (km->d <= CSR_SMEM_MAX_D && csr_smem_engine_allowed()) {
         // few features: the panel of 256 requested rows fits in shared memory
         const size_t smem = ((size_t) km->d * CSR_SMEM_PART + 2 * CSR_SMEM_TILE) * sizeof(float);
@@ -823,24 +827,23 @@ static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out,
             TSVM_CUDA(cudaGetDevice(&dev));
             TSVM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
         }
+        sms = sms - spare_sms > 0 ? sms - spare_sms : 1;
         int bx = sms / parts > 0 ? sms / parts : 1;
-        const int n_tiles = ceil_div(km->n, 32);
+        const int n_tiles = ceil_div(X.n, 32);
         if (bx > n_tiles) bx = n_tiles;
-        TSVM_LAUNCH(csr_rows_smem_kernel, dim3(bx, parts), CSR_SMEM_THREADS, smem, st, km->val, km->row_ptr, km->col,
-                    km->n, km->d, km->WT, km->wt_ld, m, km->self_dot, km->sd_rows, km->fn, out, ld_out, km->rows_m_dev,
-                    km->rows_slot_dev);
+        TSVM_LAUNCH(csr_rows_smem_kernel, dim3(bx, parts), CSR_SMEM_THREADS, smem, st, X.val, X.row_ptr, X.col, X.n, km->d,
+                    panel, km->wt_ld, m, X.sd, sd_rows, km->fn, out, ld_out, m_dev, row_slot);
         return TSVM_OK;
     }
     const int nv = ceil_div(m, 128);
-    const int grid = ceil_div(km->n, 32);
+    const int grid = ceil_div(X.n, 32);
 #define CSR_CASE(NV)                                                                                             \
     {                                                                                                            \
         size_t smem = (size_t) (NV) * 128 * 33 * sizeof(float);                                                  \
         TSVM_CUDA(cudaFuncSetAttribute(csr_rows_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
                                        (int) smem));                                                             \
-        TSVM_LAUNCH(csr_rows_kernel<NV>, grid, 256, smem, st, km->val, km->row_ptr, km->col, km->n, km->WT,      \
-                    km->wt_ld, m, km->self_dot, km->sd_rows, km->fn, out, ld_out, km->rows_m_dev,                \
-                    km->rows_slot_dev);                                                                          \
+        TSVM_LAUNCH(csr_rows_kernel<NV>, grid, 256, smem, st, X.val, X.row_ptr, X.col, X.n, panel, km->wt_ld, m, \
+                    X.sd, sd_rows, km->fn, out, ld_out, m_dev, row_slot);                                        \
     }
     if (nv <= 1) CSR_CASE(1)
     else if (nv <= 2) CSR_CASE(2)
@@ -851,8 +854,20 @@ static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out,
     return TSVM_OK;
 }
 
-// ---- pieces of tsvm_km_rows_by_index for callers that overlap them (the solver) -------------------
+static tsvm_status rows_common(tsvm_km *km, int m, float *out, long long ld_out, cudaStream_t st) {
+    // W / WT and sd_rows are staged; run the engine.
+    if (km->dense) {
+        if (use_tensor_engine(km)) return launch_dense_tc(km, m, out, ld_out, st);
+        dim3 grid(ceil_div(km->n, 64), ceil_div(m, 64));
+        TSVM_LAUNCH(dense_rows_simt_kernel, grid, 256, 0, st, km->X, km->ldx, km->n, km->W, km->d_pad, m, km->d_pad,
+                    km->self_dot, km->sd_rows, km->fn, out, ld_out, km->rows_m_dev, km->rows_slot_dev);
+        return TSVM_OK;
+    }
+    return csr_engine_launch(km, CsrView{km->val, km->row_ptr, km->col, km->n, km->self_dot}, km->WT, km->sd_rows, m, out,
+                             ld_out, km->rows_m_dev, km->rows_slot_dev, 0, st);
+}
 
+// ---- pieces of tsvm_km_rows_by_index for callers that overlap them (the solver) -------------------
 tsvm_status launch_dense_tc2_on(tsvm_km *km, const InstancePlanes &X, int m, float *out, long long ld_out,
                                 cudaStream_t st);   // dense_tc2.cu
 
