@@ -944,7 +944,9 @@ __global__ void gather_ws_kernel(int ws, int q, int first_half_phys, const int *
 // histogram over the stamps; ties go to the lower row number, so the choice does not depend on thread timing.
 // Everything stays on the device: the engine reads the number of misses from memory.
 constexpr int CACHE_THREADS = 1024, CACHE_BINS = 2048;
-enum { CACHE_N_MISS = 0, CACHE_HITS = 1, CACHE_MISSES = 2, CACHE_BLOCKS = 3, CACHE_BLOCKS_SAVED = 4, CACHE_CTRS = 8 };
+enum { CACHE_N_MISS = 0, CACHE_HITS = 1, CACHE_MISSES = 2, CACHE_BLOCKS = 3, CACHE_BLOCKS_SAVED = 4,
+       CACHE_NEXT_FREE = 5,         // rows [0, next_free) have been handed out; the rest never held a row
+       CACHE_CTRS = 8 };
 
 __device__ __forceinline__ int cache_bin(int stamp, int now) {
     // older -> smaller bin; never-used rows (stamp 0) are the oldest; rows used in this iteration are not candidates
@@ -1002,7 +1004,18 @@ cache_assign_kernel(const int *__restrict__ ids, int t0, int n_new, int now, int
     // (the stamps written above must be visible to the sweeps below)
     __threadfence_block();
     __syncthreads();
-    if (n_miss > 0) {
+    // While rows that never held anything are left, the misses take the lowest of them - the rows the sweeps
+    // below would pick (stamp 0 is the oldest, ties go to the lower row) without sweeping the stamps.
+    __shared__ long long next_free_s;
+    if (tid == 0) next_free_s = ctr[CACHE_NEXT_FREE];
+    __syncthreads();
+    const long long next_free = next_free_s;
+    const bool fresh = next_free + n_miss <= cap;
+    if (n_miss > 0 && fresh) {
+        if (tid < n_miss) victims[tid] = (int) next_free + tid;
+        __threadfence_block();
+        __syncthreads();
+    } else if (n_miss > 0) {
         // histogram of the candidates' stamps
         for (int r = tid; r < cap; r += CACHE_THREADS) {
             const int st = stamp[r];
@@ -1071,6 +1084,8 @@ cache_assign_kernel(const int *__restrict__ ids, int t0, int n_new, int now, int
         }
         __threadfence_block();
         __syncthreads();
+    }
+    if (n_miss > 0) {
         // the misses take the victims' rows
         if (tid < n_miss) {
             const int t = miss_t[tid];
@@ -1092,6 +1107,7 @@ cache_assign_kernel(const int *__restrict__ ids, int t0, int n_new, int now, int
         ctr[CACHE_MISSES] += n_miss;
         ctr[CACHE_BLOCKS] += (n_new + row_block - 1) / row_block;
         ctr[CACHE_BLOCKS_SAVED] += (n_new + row_block - 1) / row_block - (n_miss + row_block - 1) / row_block;
+        ctr[CACHE_NEXT_FREE] = fresh ? next_free + n_miss : (long long) cap;
     }
 }
 
