@@ -39,6 +39,9 @@ def main():
     ap.add_argument("--d", type=int, default=2000, help="features of the dense cases")
     ap.add_argument("--no-overlap", action="store_true", help="solver case: run the steps one after the other")
     ap.add_argument("--engine", default="auto", help="dense engine: auto, simt, tensor2 (TF32 planes), tensor (FP16 planes)")
+    ap.add_argument("--csr-config", default="c4", choices=["c2", "c4"],
+                    help="csr_rows case: config 4 (47,236 features, L2-panel engine) or config 2 (123 features, "
+                         "shared-memory-panel engine)")
     args = ap.parse_args()
     capi.lib()
     if args.case == "predict":
@@ -64,7 +67,7 @@ def main():
         km = capi.KernelMatrix(dense=torch.from_numpy(prob["X"]).cuda(), gamma=prob["gamma"])
         km.set_dense_engine(args.engine)
     else:
-        prob = synth.config4(args.rows)
+        prob = synth.config4(args.rows) if args.csr_config == "c4" else synth.config2(args.rows)
         val, rp, col = prob["csr"]
         km = capi.KernelMatrix(csr=(torch.from_numpy(val).cuda(), torch.from_numpy(rp).cuda(),
                                     torch.from_numpy(col).cuda()), d=prob["d"], gamma=prob["gamma"])
@@ -79,7 +82,7 @@ def main():
         print("solver steps (ms):", ["%.3f" % t for t in ms], sv.stats())
         return
     idx = torch.from_numpy(np.random.default_rng(0).choice(n, args.q, replace=False).astype(np.int32)).cuda()
-    out = torch.empty((args.q, n), dtype=torch.float32, device="cuda")
+    out = torch.empty((args.q, (n + 3) // 4 * 4), dtype=torch.float32, device="cuda")      # the solver's row stride
     km.get_rows(idx, out)
     torch.cuda.synchronize()
     ms = _time(lambda: km.get_rows(idx, out), args.reps)
