@@ -718,13 +718,13 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
             f_sm[t] = f[s]; a_sm[t] = a[s]; y_sm[t] = y[s]; kd_sm[t] = kd[s];
         } else { f[s] = 0; a[s] = aold[s] = 0; y[s] = 0; kd[s] = 0; }   // y = 0: member of no set
     }
-    // C solver: membership of I_up / I_low only changes for the two slots a step moves, so it is kept in
-    // registers and recomputed for those two instead of for every slot in every selection
+    // Membership of I_up / I_low only changes for the two slots a step moves, so it is kept in registers and
+    // recomputed for those two instead of for every slot in every selection
     bool in_up[SLOTS], in_low[SLOTS];
 #pragma unroll
     for (int s = 0; s < SLOTS; ++s) {
-        in_up[s] = !NU && in_I_up(a[s], y[s], Cp, Cn);
-        in_low[s] = !NU && in_I_low(a[s], y[s], Cp, Cn);
+        in_up[s] = in_I_up(a[s], y[s], Cp, Cn);
+        in_low[s] = in_I_low(a[s], y[s], Cp, Cn);
     }
     __syncthreads();
     double local_eps = 0;
@@ -744,10 +744,11 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
                 if (in_up[s] && kf < key[0]) { key[0] = kf; slot[0] = t; }
                 if (in_low[s] && knf < key[1]) { key[1] = knf; slot[1] = t; }
             } else {
-                if (y[s] > 0 && a[s] < Cp && kf < key[0]) { key[0] = kf; slot[0] = t; }      // up, +
-                if (y[s] < 0 && a[s] > 0 && kf < key[1]) { key[1] = kf; slot[1] = t; }       // up, -
-                if (y[s] > 0 && a[s] > 0 && knf < key[2]) { key[2] = knf; slot[2] = t; }     // low, +
-                if (y[s] < 0 && a[s] < Cp && knf < key[3]) { key[3] = knf; slot[3] = t; }    // low, -
+                // the four lists are I_up and I_low split by class (Cn = Cp here)
+                if (y[s] > 0 && in_up[s] && kf < key[0]) { key[0] = kf; slot[0] = t; }       // up, +:  a < C
+                if (y[s] < 0 && in_up[s] && kf < key[1]) { key[1] = kf; slot[1] = t; }       // up, -:  a > 0
+                if (y[s] > 0 && in_low[s] && knf < key[2]) { key[2] = knf; slot[2] = t; }    // low, +: a > 0
+                if (y[s] < 0 && in_low[s] && knf < key[3]) { key[3] = knf; slot[3] = t; }    // low, -: a < C
             }
         }
         block_argmin<R1, SMO_THREADS / 32>(red[0], key, slot);
@@ -837,8 +838,8 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
                 const int t = tid + s * SMO_THREADS;
                 // every slot computes its quotients, candidates or not (the others divide by one and are
                 // discarded): the divisions of a thread's slots then overlap instead of one divergent branch each
-                const bool c0 = -up0 > -f[s] && y[s] > 0 && a[s] > 0;
-                const bool c1 = -up1 > -f[s] && y[s] < 0 && a[s] < Cp;
+                const bool c0 = -up0 > -f[s] && y[s] > 0 && in_low[s];
+                const bool c1 = -up1 > -f[s] && y[s] < 0 && in_low[s];
                 const double a0 = (double) (kd_i0 + kd[s] - 2 * kI0[s]), a1 = (double) (kd_i1 + kd[s] - 2 * kI1[s]);
                 const double b0 = -up0 + f[s], b1 = -up1 + f[s];
                 const double v0 = -b0 * b0 / (c0 ? a0 : 1.0), v1 = -b1 * b1 / (c1 ? a1 : 1.0);
@@ -877,7 +878,7 @@ local_smo_kernel(int ws, const float *__restrict__ kww, const float *__restrict_
             const int t = tid + s * SMO_THREADS;
             if (t == i) a[s] += l * yi;
             if (t == j2) a[s] -= l * yj;
-            if (!NU && (t == i || t == j2)) {
+            if (t == i || t == j2) {
                 in_up[s] = in_I_up(a[s], y[s], Cp, Cn);
                 in_low[s] = in_I_low(a[s], y[s], Cp, Cn);
             }

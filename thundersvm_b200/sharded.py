@@ -685,8 +685,8 @@ def bench(args, rank, world, local_rank, clock_sampler=None, peaks=None):
         Th = torch.from_numpy(test["X"][tl:th]).pin_memory()
         y_test = test["y"][tl:th]
         del test
-        capi.predict_labels(km_sv, coef, counts, rho_d, 2, dense=Th[:1024].cuda())      # warm-up
         Td = Th.cuda()
+        capi.predict_labels(km_sv, coef, counts, rho_d, 2, dense=Td)      # warm-up at the timed size (scratch allocation)
         torch.cuda.synchronize()
         dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
