@@ -211,7 +211,7 @@ import hashlib, sys
 import numpy as np, torch
 from thundersvm_b200 import capi
 rng = np.random.default_rng(17)
-n, d = 4099, 150                                   # n not a multiple of 32; d within the shared-memory panel
+n, d = 4099, 158                                   # n not a multiple of 32; d = the most the shared-memory panel holds
 lens = rng.integers(0, 70, n)                      # empty instances and instances longer than one 32-entry batch
 lens[::97] = 0
 rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
