@@ -158,6 +158,10 @@ bool CMDParser::check_parameter() {
     const bool uses_nu = p.svm_type == SvmParam::NU_SVC || p.svm_type == SvmParam::ONE_CLASS || p.svm_type == SvmParam::NU_SVR;
     if (uses_c && p.C <= 0) return fail("C <= 0");
     if (uses_nu && (p.nu <= 0 || p.nu > 1)) return fail("nu <= 0 or nu > 1");
+    // a class weight of zero makes that class's C zero: its instances belong to neither I_up nor I_low and the
+    // working set may not fill (the solver reports that case; rejecting it here gives the clearer message)
+    for (int i = 0; i < p.nr_weight; ++i)
+        if (p.weight[i] <= 0) return fail("class weight <= 0");
     if (p.svm_type == SvmParam::EPSILON_SVR && p.p < 0) return fail("p < 0");
     if (p.max_mem_size <= 0) return fail("max memory size <= 0");
     if (p.probability != 0 && p.probability != 1) return fail("probability != 0 and probability != 1");
