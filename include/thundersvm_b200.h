@@ -217,6 +217,10 @@ tsvm_status tsvm_nccl_comm_create(const void *id128_host, int rank, int world, v
 void tsvm_nccl_comm_destroy(void *comm);
 tsvm_status tsvm_shard_attach_nccl(tsvm_shard *shard, void *comm);
 tsvm_status tsvm_shard_step(tsvm_shard *shard, int *done_host);
+/* Up to n_iters such iterations. The termination rules run on the device, as in tsvm_solver_iterate: several
+ * iterations (eight, TSVM_SYNC_EVERY) are queued between reads of the verdict, collectives included - every rank
+ * must call it with the same n_iters. Stops early when the solve is done. */
+tsvm_status tsvm_shard_run(tsvm_shard *shard, int n_iters, int *done_host);
 tsvm_status tsvm_shard_get_stats(const tsvm_shard *shard, tsvm_solve_stats *stats_host);
 void tsvm_shard_destroy(tsvm_shard *shard);
 

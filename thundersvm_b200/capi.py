@@ -24,7 +24,7 @@ EXPORTS = [
     "tsvm_km_n_instances", "tsvm_km_n_features", "tsvm_km_nnz", "tsvm_km_is_dense", "tsvm_km_diag_dev",
     "tsvm_km_self_dot_dev", "tsvm_km_rows_by_index", "tsvm_km_rows_by_instances_dense",
     "tsvm_km_rows_by_instances_csr", "tsvm_km_rows_for_features_dense", "tsvm_km_set_dense_engine", "tsvm_rho_partials", "tsvm_smo_solve", "tsvm_solver_create",
-    "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_set_overlap", "tsvm_solver_destroy", "tsvm_shard_create", "tsvm_shard_candidates", "tsvm_shard_select", "tsvm_shard_iterate", "tsvm_nccl_unique_id", "tsvm_nccl_comm_create", "tsvm_nccl_comm_destroy", "tsvm_shard_attach_nccl", "tsvm_shard_step", "tsvm_shard_get_stats", "tsvm_shard_destroy", "tsvm_working_set_size",
+    "tsvm_solver_iterate", "tsvm_solver_finish", "tsvm_solver_get_stats", "tsvm_solver_set_overlap", "tsvm_solver_destroy", "tsvm_shard_create", "tsvm_shard_candidates", "tsvm_shard_select", "tsvm_shard_iterate", "tsvm_nccl_unique_id", "tsvm_nccl_comm_create", "tsvm_nccl_comm_destroy", "tsvm_shard_attach_nccl", "tsvm_shard_step", "tsvm_shard_run", "tsvm_shard_get_stats", "tsvm_shard_destroy", "tsvm_working_set_size",
     "tsvm_ws_create", "tsvm_ws_destroy", "tsvm_ws_candidates", "tsvm_ws_merge", "tsvm_ws_sort_candidates", "tsvm_ws_merge_sorted", "tsvm_select_working_set",
     "tsvm_select_working_set_static",
     "tsvm_local_smo", "tsvm_update_f", "tsvm_predict_dec", "tsvm_predict_labels", "tsvm_vote",
@@ -102,6 +102,7 @@ def lib():
     L.tsvm_nccl_comm_destroy.argtypes = [vp]
     L.tsvm_nccl_comm_destroy.restype = None
     L.tsvm_shard_step.argtypes = [vp, C.POINTER(i)]
+    L.tsvm_shard_run.argtypes = [vp, i, C.POINTER(i)]
     L.tsvm_shard_destroy.argtypes = [vp]
     L.tsvm_shard_destroy.restype = None
     L.tsvm_solver_destroy.argtypes = [vp]
@@ -337,6 +338,12 @@ class Shard:
         """One whole outer iteration, exchange steps included (after attach_nccl, or with one rank)."""
         done = C.c_int(0)
         check(lib().tsvm_shard_step(self._h, C.byref(done)))
+        return bool(done.value)
+
+    def run(self, n_iters):
+        """Up to n_iters whole outer iterations (after attach_nccl, or with one rank), queued several at a time."""
+        done = C.c_int(0)
+        check(lib().tsvm_shard_run(self._h, n_iters, C.byref(done)))
         return bool(done.value)
 
     def stats(self):

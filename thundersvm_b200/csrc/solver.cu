@@ -1152,7 +1152,8 @@ __global__ void solver_status_kernel(SolverCtl *c, const double *__restrict__ di
     if (max_iter != -1 && c->iter - 1 == max_iter) stop = 1;      // iteration cap (csmosolver.cpp:110)
     if (*got < wanted) { c->short_got = *got; c->short_wanted = wanted; stop = 1; }
     if (engine_status && *engine_status) { c->engine_status = *engine_status; stop = 1; }
-    for (int k = 0; k < CACHE_CTRS; ++k) c->ctr[k] = cache_ctr[k];
+    if (cache_ctr)
+        for (int k = 0; k < CACHE_CTRS; ++k) c->ctr[k] = cache_ctr[k];
     c->stop = stop;
 }
 
@@ -1685,6 +1686,19 @@ int tsvm_working_set_size(int n_instances, int n_features, size_t max_mem_bytes,
 }  // extern "C"
 
 // Solver state that persists across outer iterations.
+// How many iterations are queued between two reads of the device's verdict. The queue hides the host's wake-up
+// and launch latency behind the device's work; the price is at most that many no-op iterations after the one
+// that ends the solve.
+enum { MAX_QUEUED = 32 };
+static int sync_every() {
+    static const int k = [] {
+        const char *e = getenv("TSVM_SYNC_EVERY");
+        const int v = e ? atoi(e) : 8;
+        return v < 1 ? 1 : (v > MAX_QUEUED ? (int) MAX_QUEUED : v);
+    }();
+    return k;
+}
+
 struct tsvm_solver {
     // Events of one queued iteration: phase boundaries on the first stream, start and end of the local solver
     struct IterEvents {
@@ -1706,7 +1720,6 @@ struct tsvm_solver {
     tsvm_ws *sel = nullptr;
     double *diff_host = nullptr;
     // end-of-iteration state on the device, its pinned copy, and the events of the queued iterations
-    enum { MAX_QUEUED = 32 };
     SolverCtl *ctl = nullptr, *ctl_host = nullptr;
     IterEvents evs[MAX_QUEUED];
     int max_iter = -1;              // iteration cap applied on the device; -1: none
@@ -1964,17 +1977,6 @@ struct tsvm_solver {
         return TSVM_OK;
     }
 
-    // How many iterations are queued between two reads of the device's verdict. The queue hides the host's
-    // wake-up and launch latency behind the device's work; the price is at most that many no-op iterations
-    // after the one that ends the solve.
-    static int sync_every() {
-        static const int k = [] {
-            const char *e = getenv("TSVM_SYNC_EVERY");
-            const int v = e ? atoi(e) : 8;
-            return v < 1 ? 1 : (v > MAX_QUEUED ? (int) MAX_QUEUED : v);
-        }();
-        return k;
-    }
 
     // Queues up to `count` outer iterations, waits once and takes over what the device decided. Fewer than
     // `count` may have run: the termination rules, the iteration cap or an error stop the queue on the device.
@@ -2133,7 +2135,7 @@ tsvm_status tsvm_smo_solve(tsvm_km *km, int solver_kind, const int *y_dev, doubl
     tsvm_status s = TSVM_OK;
     // max_iter = k stops after outer iteration k, i.e. k + 1 iterations (csmosolver.cpp:110); applied on the device
     S->max_iter = max_iter;
-    while (s == TSVM_OK && !S->stopped) s = S->run_iterations(tsvm_solver::MAX_QUEUED);
+    while (s == TSVM_OK && !S->stopped) s = S->run_iterations(MAX_QUEUED);
     if (s == TSVM_OK) s = S->finish(rho_host, stats_host);
     delete S;
     return s;
@@ -2201,8 +2203,13 @@ struct tsvm_shard {
     long long ld = 0;
     cudaStream_t st = nullptr, st2 = nullptr;
     ncclComm_t comm = nullptr;       // set by tsvm_shard_attach_nccl (not owned): the library then runs the exchange steps itself
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_r0 = nullptr, ev_r1 = nullptr, ev_b0 = nullptr, ev_b1 = nullptr;
-    double t_rows = 0, t_loc = 0;    // ms: kernel-row launch (first stream); block + local solver (second stream)
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_blk = nullptr;
+    // timing events of the queued iterations: kernel-row launch (first stream), block + local solver (second)
+    struct StepEvents { cudaEvent_t r0 = nullptr, r1 = nullptr, b0 = nullptr, b1 = nullptr; };
+    StepEvents evs[MAX_QUEUED];
+    int queued = 0;                  // iterations enqueued since the last read of the device's verdict
+    SolverCtl *ctl = nullptr, *ctl_host = nullptr;   // termination rules applied on the device (solver_status_kernel)
+    double t_rows = 0, t_loc = 0;    // ms
     // exchange buffers (caller's)
     double *cand_f = nullptr, *all_f = nullptr, *cstate = nullptr;
     int *cand_id = nullptr, *all_id = nullptr;
@@ -2218,17 +2225,20 @@ struct tsvm_shard {
     double *diff_host = nullptr;
     size_t row_bytes = 0;
     long long iter = 0, local_iter = 0, rows_made = 0, launches0 = 0;
-    int same_cnt = 0, swap_cnt = 0, local_max_iter = 0, n_new = 0, slot0 = 0, phase = 0;
-    double prev = INFINITY, last = INFINITY, second_last = INFINITY, diff0 = 0;
+    int local_max_iter = 0, n_new = 0, slot0 = 0, phase = 0;
+    double diff0 = 0;
     bool done = false;
     std::chrono::steady_clock::time_point t_begin;
 
     ~tsvm_shard() {
         pool_free_many({ids, y_ws, rows, kww, m_hi, m_lo, m_sd, m_unscale, m_diag, f_ws, a_ws, alpha_diff, diff, grp_f,
-                        grp_id, in_ws});
+                        grp_id, in_ws, ctl});
         tsvm_ws_destroy(sel);
         if (diff_host) pinned_free(diff_host);
-        for (auto e : {ev_fork, ev_join, ev_r0, ev_r1, ev_b0, ev_b1}) if (e) cudaEventDestroy(e);
+        if (ctl_host) pinned_free(ctl_host);
+        for (auto e : {ev_fork, ev_join, ev_blk}) if (e) cudaEventDestroy(e);
+        for (auto &E : evs)
+            for (auto e : {E.r0, E.r1, E.b0, E.b1}) if (e) cudaEventDestroy(e);
         if (st2) cudaStreamDestroy(st2);
     }
 
@@ -2256,9 +2266,14 @@ struct tsvm_shard {
         TSVM_CUDA(cudaMemsetAsync(in_ws, 0, (size_t) n_local, st));
         TSVM_TRY(tsvm_ws_create(n_local, ws, &sel));
         TSVM_TRY(pinned_alloc((void **) &diff_host, 4 * sizeof(double)));
+        TSVM_TRY(dev_alloc(&ctl, 1));
+        TSVM_TRY(pinned_alloc((void **) &ctl_host, sizeof(SolverCtl)));
+        memset(ctl_host, 0, sizeof(SolverCtl));
+        ctl_host->prev = ctl_host->last = ctl_host->second_last = INFINITY;     // csmosolver.cpp:51-57
+        TSVM_CUDA(cudaMemcpyAsync(ctl, ctl_host, sizeof(SolverCtl), cudaMemcpyHostToDevice, st));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
-        for (auto e : {&ev_r0, &ev_r1, &ev_b0, &ev_b1}) TSVM_CUDA(cudaEventCreate(e));
+        TSVM_CUDA(cudaEventCreateWithFlags(&ev_blk, cudaEventDisableTiming));
         int lo_prio = 0, hi_prio = 0;
         TSVM_CUDA(cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio));
         TSVM_CUDA(cudaStreamCreateWithPriority(&st2, cudaStreamNonBlocking, hi_prio));
@@ -2270,9 +2285,10 @@ struct tsvm_shard {
     tsvm_status candidates(int *lists_out, int *want_out) {
         TSVM_REQUIRE(phase == 0, "shard solver: phases out of order (candidates)");
         const int lists = kind == TSVM_SOLVER_C ? 2 : 4;
-        n_new = iter == 0 ? ws : q;
-        slot0 = iter == 0 ? 0 : q;
-        if (iter > 0) {
+        const long long it = iter + queued;         // the iteration being enqueued
+        n_new = it == 0 ? ws : q;
+        slot0 = it == 0 ? 0 : q;
+        if (it > 0) {
             TSVM_LAUNCH(shard_shift_kernel, 1, 1024, 0, st, ids, q, lo, hi, in_ws, m_sd, m_unscale, m_diag);
             TSVM_CUDA(cudaMemcpyAsync(m_hi, (char *) m_hi + (size_t) q * row_bytes, (size_t) q * row_bytes,
                                       cudaMemcpyDeviceToDevice, st));
@@ -2286,7 +2302,8 @@ struct tsvm_shard {
         FusedExtra x;
         x.mode = FUSED_SORT;
         x.sorted_f = cand_f; x.sorted_id = cand_id;
-        TSVM_TRY(ws_candidates_cap(sel, kind, n_local, f, alpha, y, iter == 0 ? nullptr : in_ws, Cp, Cn, n_new, cap, lo,
+        x.stop = &ctl->stop;
+        TSVM_TRY(ws_candidates_cap(sel, kind, n_local, f, alpha, y, it == 0 ? nullptr : in_ws, Cp, Cn, n_new, cap, lo,
                                    sel->cand_f, sel->cand_id, st, x));
         *lists_out = lists;
         *want_out = n_new;
@@ -2312,10 +2329,17 @@ struct tsvm_shard {
         return TSVM_OK;
     }
 
-    // phase C: everything after the exchange
-    tsvm_status iterate() {
+    // phase C: everything after the exchange, enqueued without waiting. The last launch applies the
+    // termination rules on the device (solver_status_kernel); once it has set the stop word, the selection and
+    // the local solver of any iteration queued behind it do nothing - the local solver leaves a zero step, so
+    // the f updates subtract zero and the scatter writes back the alphas it read.
+    tsvm_status enqueue_tail() {
         TSVM_REQUIRE(phase == 2, "shard solver: phases out of order (iterate)");
-        const int first_half_phys = (int) (iter & 1);
+        TSVM_REQUIRE(queued < MAX_QUEUED, "shard solver: too many iterations queued");
+        const long long it = iter + queued;
+        const int first_half_phys = (int) (it & 1);
+        StepEvents &E = evs[queued];
+        if (!E.r0) for (auto e : {&E.r0, &E.r1, &E.b0, &E.b1}) TSVM_CUDA(cudaEventCreate(e));
         TSVM_LAUNCH(shard_unpack_kernel, ceil_div(ws, 256), 256, 0, st, crow, slot0, n_new, dp, ws, cstate, m_sd, m_diag,
                     y_ws, f_ws, a_ws);
         TSVM_TRY(km_stage_rows_features(km, crow, dp + 4, m_sd + slot0, n_new, st));
@@ -2330,58 +2354,74 @@ struct tsvm_shard {
         TSVM_CUDA(cudaStreamWaitEvent(st2, ev_fork, 0));
         const InstancePlanes members{m_hi, m_lo, m_sd, m_unscale, ws};
         const RowPlanes member_rows{m_hi, m_lo, m_sd, m_unscale};
-        TSVM_CUDA(cudaEventRecord(ev_b0, st2));
+        TSVM_CUDA(cudaEventRecord(E.b0, st2));
         TSVM_TRY(km_rows_planes_on(km, members, member_rows, ws, kww, ws, st2));
+        // The kernel-row launch below leaves one SM pair free; started first it would leave the block's eight
+        // pairs that one pair to run on, and the local solver - the longer of the two paths once the rows are
+        // split - would start late. With iterations queued nothing else orders the two, so the first stream waits
+        // for the block.
+        TSVM_CUDA(cudaEventRecord(ev_blk, st2));
         TSVM_TRY(launch_local_smo(kind, ws, kww, m_diag, y_ws, f_ws, a_ws, alpha_diff, Cp, Cn, eps, local_max_iter, diff,
-                                  nullptr, nullptr, st2));
-        TSVM_CUDA(cudaEventRecord(ev_b1, st2));
-        if (iter > 0)      // the old half's rows are in the buffer already
+                                  nullptr, nullptr, st2, &ctl->stop));
+        TSVM_CUDA(cudaEventRecord(E.b1, st2));
+        if (it > 0)        // the old half's rows are in the buffer already
             TSVM_LAUNCH(update_f_kernel, update_f_grid(n_local), 128, 0, st2, f, n_local, alpha_diff, ws, q,
                         first_half_phys, rows, ld, rows_vec_ok(rows, ld), 0, q, update_f_cols(n_local), (const int *) nullptr);
         TSVM_CUDA(cudaEventRecord(ev_join, st2));
         // first stream: the new rows against this rank's columns
-        float *new_rows = rows + (size_t) (iter == 0 ? 0 : (1 - first_half_phys) * q) * ld;
+        float *new_rows = rows + (size_t) (it == 0 ? 0 : (1 - first_half_phys) * q) * ld;
         km->reserve_clusters = 1;
-        TSVM_CUDA(cudaEventRecord(ev_r0, st));
+        TSVM_CUDA(cudaStreamWaitEvent(st, ev_blk, 0));
+        TSVM_CUDA(cudaEventRecord(E.r0, st));
         const tsvm_status rs = km_rows_staged(km, n_new, new_rows, ld, st);
         km->reserve_clusters = 0;
         TSVM_TRY(rs);
-        TSVM_CUDA(cudaEventRecord(ev_r1, st));
-        rows_made += n_new;
+        TSVM_CUDA(cudaEventRecord(E.r1, st));
         TSVM_CUDA(cudaStreamWaitEvent(st, ev_join, 0));
         TSVM_LAUNCH(update_f_kernel, update_f_grid(n_local), 128, 0, st, f, n_local, alpha_diff, ws, q, first_half_phys,
-                    rows, ld, rows_vec_ok(rows, ld), iter == 0 ? 0 : q, ws, update_f_cols(n_local), (const int *) nullptr);
+                    rows, ld, rows_vec_ok(rows, ld), it == 0 ? 0 : q, ws, update_f_cols(n_local), (const int *) nullptr);
         TSVM_LAUNCH(shard_scatter_kernel, ceil_div(ws, 256), 256, 0, st, ids, ws, lo, hi, a_ws, alpha);
-        TSVM_CUDA(cudaMemcpyAsync(diff_host, diff, 2 * sizeof(double), cudaMemcpyDeviceToHost, st));
-        int *got_host = reinterpret_cast<int *>(diff_host + 2);
-        TSVM_CUDA(cudaMemcpyAsync(got_host, sel->count, sizeof(int), cudaMemcpyDeviceToHost, st));
-        TSVM_CUDA(cudaMemcpyAsync(km->status_host, km->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
-        TSVM_CUDA(cudaStreamSynchronize(st));
-        if (km->status_host[0] != 0) {
-            set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", km->status_host[0]);
-            return TSVM_ERR_DEVICE;
-        }
-        if (*got_host < n_new) {
-            set_error("working-set selection found %d eligible instances for %d slots (is a class weight or C zero?)",
-                      *got_host, n_new);
-            return TSVM_ERR_INVALID;
-        }
-        float ms_ev = 0;
-        cudaEventElapsedTime(&ms_ev, ev_r0, ev_r1); t_rows += ms_ev;
-        cudaEventElapsedTime(&ms_ev, ev_b0, ev_b1); t_loc += ms_ev;
-        diff0 = diff_host[0];
-        local_iter += (long long) diff_host[1];
-        if (fabs(diff0 - prev) < eps * 0.001) same_cnt++;
-        else { same_cnt = 0; prev = diff0; }
-        if (fabs(diff0 - second_last) < eps * 0.001) swap_cnt++;
-        else swap_cnt = 0;
-        second_last = last;
-        last = diff0;
-        if ((same_cnt >= 10 && fabs(diff0 - 2.0) > eps) || diff0 < eps || (swap_cnt >= 10 && fabs(diff0 - 2.0) > eps))
-            done = true;
-        ++iter;
+        TSVM_LAUNCH(solver_status_kernel, 1, 32, 0, st, ctl, diff, sel->count, n_new, eps, -1, (const long long *) nullptr,
+                    km->status_dev);
+        ++queued;
         phase = 0;
         return TSVM_OK;
+    }
+
+    // Waits for the queued iterations and takes over what the device decided (fewer than queued may have run).
+    tsvm_status collect() {
+        if (queued == 0) return TSVM_OK;
+        TSVM_CUDA(cudaMemcpyAsync(ctl_host, ctl, sizeof(SolverCtl), cudaMemcpyDeviceToHost, st));
+        TSVM_CUDA(cudaStreamSynchronize(st));
+        const SolverCtl &c = *ctl_host;
+        const int was_queued = queued;
+        queued = 0;
+        if (c.engine_status != 0) {
+            set_error("dense kernel-row engine reported status %d (a bounded wait ran out)", c.engine_status);
+            return TSVM_ERR_DEVICE;
+        }
+        const int ran = (int) (c.iter - iter);
+        for (int j = 0; j < ran && j < was_queued; ++j) {
+            float ms_ev = 0;
+            cudaEventElapsedTime(&ms_ev, evs[j].r0, evs[j].r1); t_rows += ms_ev;
+            cudaEventElapsedTime(&ms_ev, evs[j].b0, evs[j].b1); t_loc += ms_ev;
+            rows_made += iter + j == 0 ? ws : q;
+        }
+        iter = c.iter;
+        local_iter = c.local_iter;
+        diff0 = c.diff0;
+        done = c.done != 0;
+        if (c.short_wanted > 0) {
+            set_error("working-set selection found %d eligible instances for %d slots (is a class weight or C zero?)",
+                      c.short_got, c.short_wanted);
+            return TSVM_ERR_INVALID;
+        }
+        return TSVM_OK;
+    }
+
+    tsvm_status iterate() {
+        TSVM_TRY(enqueue_tail());
+        return collect();
     }
 
     // One whole outer iteration with the exchange steps enqueued on the solver's stream by the library
@@ -2409,7 +2449,22 @@ struct tsvm_shard {
             TSVM_NCCL(nc.AllReduce(cstate, cstate, (size_t) ws * 3, NCCL_FLOAT64, NCCL_SUM, comm, st));
             TSVM_NCCL(nc.GroupEnd());
         }
-        return iterate();
+        return enqueue_tail();
+    }
+
+    // Up to n_iters whole iterations, queued sync_every() at a time between reads of the device's verdict.
+    tsvm_status run(int n_iters) {
+        for (long long end = iter + n_iters; iter < end && !done;) {
+            long long k = end - iter;
+            if (k > sync_every()) k = sync_every();
+            if (iter == 0) k = 1;                   // the first iteration is read back on its own
+            for (int j = 0; j < (int) k; ++j) {
+                const tsvm_status s = step();
+                if (s != TSVM_OK) { collect(); return s; }
+            }
+            TSVM_TRY(collect());
+        }
+        return TSVM_OK;
     }
 };
 
@@ -2449,8 +2504,15 @@ tsvm_status tsvm_shard_attach_nccl(tsvm_shard *S, void *comm) {
 
 tsvm_status tsvm_shard_step(tsvm_shard *S, int *done_host) {
     TSVM_REQUIRE(S && done_host, "shard_step: null argument");
-    TSVM_TRY(S->step());
+    TSVM_TRY(S->run(1));
     *done_host = S->done ? 1 : 0;
+    return TSVM_OK;
+}
+
+tsvm_status tsvm_shard_run(tsvm_shard *S, int n_iters, int *done_host) {
+    TSVM_REQUIRE(S && n_iters > 0, "shard_run: bad arguments");
+    TSVM_TRY(S->run(n_iters));
+    if (done_host) *done_host = S->done ? 1 : 0;
     return TSVM_OK;
 }
 

@@ -392,6 +392,11 @@ class NativeShardedSolver:
         self.iter += 1
 
     def iterate(self, n_iters):
+        if (self.native_exchange or self.world == 1) and not self.done and n_iters > 0:
+            # one C call: the library queues several iterations between reads of the device's verdict
+            self.done = self.shard.run(n_iters)
+            self.iter = self.shard.stats()["outer_iters"]
+            return self.done
         for _ in range(n_iters):
             if self.done:
                 break
@@ -416,6 +421,14 @@ class NativeShardedSolver:
         return rho, st
 
     def solve(self, max_iter=-1):
+        if self.native_exchange or self.world == 1:
+            # max_iter = k stops after outer iteration k, i.e. k + 1 iterations (csmosolver.cpp:110)
+            while not self.done:
+                left = 4096 if max_iter == -1 else max_iter + 1 - self.iter
+                if left <= 0:
+                    break
+                self.iterate(left)
+            return self.finish()
         while not self.done:
             self.outer_iteration()
             if max_iter != -1 and self.iter - 1 == max_iter:
