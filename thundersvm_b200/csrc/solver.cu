@@ -2222,7 +2222,6 @@ struct tsvm_shard {
     int *grp_id = nullptr;
     unsigned char *in_ws = nullptr;
     tsvm_ws *sel = nullptr;
-    double *diff_host = nullptr;
     size_t row_bytes = 0;
     long long iter = 0, local_iter = 0, rows_made = 0, launches0 = 0;
     int local_max_iter = 0, n_new = 0, slot0 = 0, phase = 0;
@@ -2234,7 +2233,6 @@ struct tsvm_shard {
         pool_free_many({ids, y_ws, rows, kww, m_hi, m_lo, m_sd, m_unscale, m_diag, f_ws, a_ws, alpha_diff, diff, grp_f,
                         grp_id, in_ws, ctl});
         tsvm_ws_destroy(sel);
-        if (diff_host) pinned_free(diff_host);
         if (ctl_host) pinned_free(ctl_host);
         for (auto e : {ev_fork, ev_join, ev_blk}) if (e) cudaEventDestroy(e);
         for (auto &E : evs)
@@ -2265,7 +2263,6 @@ struct tsvm_shard {
         TSVM_TRY(dev_alloc(&in_ws, (size_t) n_local));
         TSVM_CUDA(cudaMemsetAsync(in_ws, 0, (size_t) n_local, st));
         TSVM_TRY(tsvm_ws_create(n_local, ws, &sel));
-        TSVM_TRY(pinned_alloc((void **) &diff_host, 4 * sizeof(double)));
         TSVM_TRY(dev_alloc(&ctl, 1));
         TSVM_TRY(pinned_alloc((void **) &ctl_host, sizeof(SolverCtl)));
         memset(ctl_host, 0, sizeof(SolverCtl));
