@@ -1727,7 +1727,7 @@ struct tsvm_solver {
     // overlapped iteration: second stream, fork / join events, operand planes of the working set
     bool overlap = true;
     cudaStream_t st2 = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_fork2 = nullptr, ev_join = nullptr;
     float *ws_hi = nullptr, *ws_lo = nullptr, *ws_sd = nullptr, *ws_unscale = nullptr;
     // kernel-row cache (cache_assign_kernel): the row buffer holds cache_cap rows; directory and per-iteration lists
     long long cache_cap = 0;
@@ -1755,7 +1755,7 @@ struct tsvm_solver {
             for (auto e : E.ph) if (e) cudaEventDestroy(e);
             for (auto e : {E.l0, E.l1}) if (e) cudaEventDestroy(e);
         }
-        for (auto e : {ev_fork, ev_join}) if (e) cudaEventDestroy(e);
+        for (auto e : {ev_fork, ev_fork2, ev_join}) if (e) cudaEventDestroy(e);
         if (st2) cudaStreamDestroy(st2);
     }
 
@@ -1830,6 +1830,7 @@ struct tsvm_solver {
         ctl_host->prev = ctl_host->last = ctl_host->second_last = INFINITY;     // csmosolver.cpp:51-57
         TSVM_CUDA(cudaMemcpyAsync(ctl, ctl_host, sizeof(SolverCtl), cudaMemcpyHostToDevice, st));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+        TSVM_CUDA(cudaEventCreateWithFlags(&ev_fork2, cudaEventDisableTiming));
         TSVM_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
         {
             int lo_prio = 0, hi_prio = 0;
@@ -1901,6 +1902,22 @@ struct tsvm_solver {
             TSVM_TRY(ws_candidates_cap(sel, kind, n, f, alpha, y, in_ws, Cp, Cn, q, 2 * q <= sel->cand_cap ? 2 * q : q, 0,
                                        sel->cand_f, sel->cand_id, st, x));
         }
+        if (overlapped) {
+            // The block's new rows need the members' planes and nothing else: the second stream starts on them
+            // (new members against all members, from the members' own operand planes) while the first one still
+            // runs the cache directory, i.e. before the big launch takes all SM pairs but one.
+            TSVM_TRY(ensure_ws_planes());
+            TSVM_TRY(ensure_miss_planes());
+            TSVM_TRY(km_gather_planes(km, ids, ws, nullptr, ws_hi, ws_lo, ws_sd, ws_unscale, st));
+            TSVM_CUDA(cudaEventRecord(ev_fork, st));
+            TSVM_CUDA(cudaStreamWaitEvent(st2, ev_fork, 0));
+            const size_t rb = km_plane_row_bytes(km);
+            const InstancePlanes members{ws_hi, ws_lo, ws_sd, ws_unscale, ws};
+            const RowPlanes new_members{reinterpret_cast<const float *>(reinterpret_cast<const char *>(ws_hi) + (size_t) q * rb),
+                                        reinterpret_cast<const float *>(reinterpret_cast<const char *>(ws_lo) + (size_t) q * rb),
+                                        ws_sd + q, ws_unscale + q};
+            TSVM_TRY(km_rows_planes_on(km, members, new_members, q, kww + (size_t) q * ws, ws, st2));
+        }
         // cache directory: hits point at their rows, misses get the least recently used rows
         TSVM_LAUNCH(cache_assign_kernel, 1, CACHE_THREADS, 0, st, ids, t0, n_new, (int) (it + 1), slot_of, inst_of, stamp,
                     (int) cache_cap, row_slot, miss_ids, miss_slot, victims, cache_ctr, row_block, stop);
@@ -1912,20 +1929,11 @@ struct tsvm_solver {
             km->rows_m_dev = nullptr; km->rows_slot_dev = nullptr;
             TSVM_TRY(rs);
         } else {
-            TSVM_TRY(ensure_ws_planes());
-            TSVM_TRY(ensure_miss_planes());
-            TSVM_TRY(km_gather_planes(km, ids, ws, nullptr, ws_hi, ws_lo, ws_sd, ws_unscale, st));
             TSVM_TRY(km_gather_planes(km, miss_ids, q, n_miss_dev, miss_hi, miss_lo, miss_sd, miss_unscale, st));
-            TSVM_CUDA(cudaEventRecord(ev_fork, st));
-            // second stream: block rows q..ws-1 by the engine (new members against all members, from the members'
-            // own operand planes), rows 0..q-1 and the slot vectors by gather, then the local solver
-            TSVM_CUDA(cudaStreamWaitEvent(st2, ev_fork, 0));
-            const size_t rb = km_plane_row_bytes(km);
-            const InstancePlanes members{ws_hi, ws_lo, ws_sd, ws_unscale, ws};
-            const RowPlanes new_members{reinterpret_cast<const float *>(reinterpret_cast<const char *>(ws_hi) + (size_t) q * rb),
-                                        reinterpret_cast<const float *>(reinterpret_cast<const char *>(ws_lo) + (size_t) q * rb),
-                                        ws_sd + q, ws_unscale + q};
-            TSVM_TRY(km_rows_planes_on(km, members, new_members, q, kww + (size_t) q * ws, ws, st2));
+            TSVM_CUDA(cudaEventRecord(ev_fork2, st));
+            // second stream, after the directory: block rows 0..q-1 and the slot vectors by gather from the rows in
+            // the buffer, then the local solver
+            TSVM_CUDA(cudaStreamWaitEvent(st2, ev_fork2, 0));
             TSVM_LAUNCH(gather_ws_kernel, ws, 256, 0, st2, ws, q, 0, ids, rows, ld, km->diag, y, f, alpha, kww, diag_ws,
                         y_ws, f_ws, a_ws, q, row_slot);
             TSVM_CUDA(cudaEventRecord(E.l0, st2));
