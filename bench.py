@@ -378,6 +378,21 @@ def small_configs(torch, capi, synth, which, cpu_which):
             model = sharded.train_ovo(ops, X, prob["y"].astype(np.int64), prob["C"], prob["eps"], gamma=prob["gamma"])
             torch.cuda.synchronize()
             sec = time.perf_counter() - t0
+            # the same job with the pairs solved on four streams by four host threads (same model)
+            four = None
+            try:
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                X4 = Xh.cuda(non_blocking=True)
+                model4 = sharded.train_ovo(ops, X4, prob["y"].astype(np.int64), prob["C"], prob["eps"], gamma=prob["gamma"],
+                                           streams=4)
+                torch.cuda.synchronize()
+                four = {"train_seconds": time.perf_counter() - t0,
+                        "same_model": bool(np.array_equal(model4["coef"], model["coef"]) and
+                                           np.array_equal(model4["rho"], model["rho"]))}
+                del X4, model4
+            except Exception as exc:                # reported, never fatal for the main line
+                four = {"error": str(exc)[:200]}
             test = synth.config3(10000, seed=5)
             Th = torch.from_numpy(test["X"]).pin_memory()
             torch.cuda.synchronize()
@@ -385,7 +400,7 @@ def small_configs(torch, capi, synth, which, cpu_which):
             lab = sharded.predict_ovo(ops, model, X, Th.cuda(non_blocking=True), gamma=prob["gamma"]).cpu().numpy()
             sec_p = time.perf_counter() - t0
             out[tag] = {"workload": "10-class one-vs-one C-SVC, 60000x784 dense, 45 binary problems", "train_seconds": sec,
-                        "total_sv": int(sum(model["n_sv"])), "predict_rows": 10000, "predict_rows_per_s": 10000 / sec_p,
+                        "pairs_on_four_streams": four, "total_sv": int(sum(model["n_sv"])), "predict_rows": 10000, "predict_rows_per_s": 10000 / sec_p,
                         "test_accuracy": float((lab == test["y"]).mean())}
             del X
         else:

@@ -142,3 +142,19 @@ def test_one_vs_one_on_the_gpu_matches_the_oracle_back_end(capi):
     assert np.max(np.abs(got["rho"] - ref["rho"])) < 1e-3
     assert (pred == ref_pred).mean() >= 0.999
     assert (pred == np.arange(200) % k).mean() > 0.9
+
+
+def test_one_vs_one_pairs_on_several_streams_give_the_same_model(capi):
+    """train_ovo(streams=3) solves the pairs from three host threads on three CUDA streams; the pairs are
+    independent, so every coefficient, rho and the SV set must equal the one-stream run's exactly."""
+    import torch
+    from thundersvm_b200 import sharded
+    prob = synth.config3(6000)
+    X = torch.from_numpy(prob["X"]).cuda()
+    lab = prob["y"].astype(np.int64)
+    one = sharded.train_ovo(sharded.CapiOps(), X, lab, C=prob["C"], gamma=prob["gamma"])
+    for _ in range(3):
+        many = sharded.train_ovo(sharded.CapiOps(), X, lab, C=prob["C"], gamma=prob["gamma"], streams=3)
+        assert many["n_sv"] == one["n_sv"]
+        assert np.array_equal(many["sv_index"], one["sv_index"])
+        assert np.array_equal(many["coef"], one["coef"]) and np.array_equal(many["rho"], one["rho"])

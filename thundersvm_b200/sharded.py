@@ -460,8 +460,12 @@ def working_set_size(n, d, free_bytes=8 << 30):
     return int(min(p2(n), min(p2(free_bytes / 4 / (n + d)), 1024)))
 
 
-def train_ovo(ops, X, labels, C, eps=1e-3, kernel="rbf", gamma=0.5, coef0=0.0, degree=3, group=None):
+def train_ovo(ops, X, labels, C, eps=1e-3, kernel="rbf", gamma=0.5, coef0=0.0, degree=3, group=None, streams=1):
     """One-vs-one C-SVC (SVC::train, svc.cpp:50-108) with the binary sub-problems split over the ranks.
+
+    streams > 1 (CUDA only): a rank's pairs are solved by that many host threads, each on a CUDA stream of its
+    own, so that the small launches and host waits of one pair's solve fill the gaps of another's. The pairs
+    are independent, so the model does not depend on it.
 
     Every rank holds X [n, d] and the class index of every instance (0 .. k-1, in order of first appearance
     as DataSet::group_classes numbers them). Pairs are assigned by `assign_pairs`; a rank solves its pairs
@@ -481,15 +485,35 @@ def train_ovo(ops, X, labels, C, eps=1e-3, kernel="rbf", gamma=0.5, coef0=0.0, d
     dev = X.device
     flat = torch.zeros(int(offs[-1]), dtype=torch.float64, device=dev)       # signed alphas of all pairs
     rho = torch.zeros(len(pairs), dtype=torch.float64, device=dev)
-    for p, (i, j) in enumerate(pairs):
-        if owner[p] != rank:
-            continue
+    def solve(p):
+        i, j = pairs[p]
         idx = torch.from_numpy(np.concatenate([members[i], members[j]])).to(dev)
         y = torch.cat([torch.ones(counts[i], dtype=torch.int32), -torch.ones(counts[j], dtype=torch.int32)]).to(dev)
         ws = working_set_size(len(idx), X.shape[1])
         a, r = ops.solve_pair(X[idx].contiguous(), y, C, eps, ws, kernel, gamma, coef0, degree)
         flat[offs[p]:offs[p + 1]] = a * y.to(torch.float64)
         rho[p] = r
+
+    mine = [p for p in range(len(pairs)) if owner[p] == rank]
+    if streams > 1 and dev.type == "cuda" and len(mine) > 1:
+        from concurrent.futures import ThreadPoolExecutor
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(dev))            # X, flat and rho exist on the caller's stream
+        side = [torch.cuda.Stream(device=dev) for _ in range(min(streams, len(mine)))]
+
+        def worker(k):
+            torch.cuda.set_device(dev)
+            side[k].wait_event(ready)
+            with torch.cuda.stream(side[k]):
+                for p in mine[k::len(side)]:
+                    solve(p)
+            side[k].synchronize()
+
+        with ThreadPoolExecutor(len(side)) as pool:
+            list(pool.map(worker, range(len(side))))            # re-raises a worker's exception
+    else:
+        for p in mine:
+            solve(p)
     if world > 1:                                   # every entry is written by exactly one rank: a sum gathers
         dist.all_reduce(flat, group=group)
         dist.all_reduce(rho, group=group)
@@ -784,6 +808,11 @@ def bench_ovo(args, rank, world):
     train()                                                   # warm-up: library pool, kernel set-up
     runs = [timed(train) for _ in range(3)]
     model, sec = min(runs, key=lambda r: r[1])
+    # the same with each rank's pairs solved on four streams by four host threads
+    train4 = lambda: train_ovo(ops, X, labels, prob["C"], prob["eps"], gamma=prob["gamma"], streams=4)
+    train4()
+    model4, sec4 = min([timed(train4) for _ in range(3)], key=lambda r: r[1])
+    four = {"streams": 4, "train_seconds": sec4, "model_identical_to_one_stream": digest(model4) == digest(model)}
     T = Th.cuda()
     predict = lambda: predict_ovo(ops, model, X, T, gamma=prob["gamma"])
     predict()
@@ -799,13 +828,15 @@ def bench_ovo(args, rank, world):
     if world > 1:
         dist.barrier()
     acc = float((lab.cpu().numpy() == test["y"]).mean())
-    return {"metric": "ovo_train_seconds", "value": sec, "unit": "s", "n_gpus": world, "steps": 1, "warmup": 1,
-            "ms_per_step": sec * 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+    best = sec4 if four["model_identical_to_one_stream"] and sec4 < sec else sec
+    return {"metric": "ovo_train_seconds", "value": best, "unit": "s", "n_gpus": world, "steps": 1, "warmup": 1,
+            "ms_per_step": best * 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32 kernel values, f64 solver state", "data": "synthetic",
             "config": {"workload": "config3: 10-class one-vs-one C-SVC, RBF gamma=0.125 C=10, 60000x784 dense, 45 binary "
                                    "problems assigned to %d GPUs by size (longest first); predict 10000 rows" % world,
-                       "parallelism": "pairs x%d" % world},
-            "train_seconds": sec, "train_seconds_from_host_rows": sec_e2e, "predict_rows_per_s": 10000 / sec_p,
+                       "parallelism": "pairs x%d; `value` is the faster of one stream and four streams per GPU" % world},
+            "train_seconds": sec, "train_seconds_from_host_rows": sec_e2e, "pairs_on_four_streams": four,
+            "predict_rows_per_s": 10000 / sec_p,
             "total_sv": int(sum(model["n_sv"])), "test_accuracy": acc, "model_sha256_16": digest(model),
             "one_gpu_model_sha256_16": one, "model_identical_to_one_gpu": (one == digest(model)) if one else None,
             "pair_load_per_rank": load, "load_imbalance": max(load) / (sum(load) / world),
