@@ -442,3 +442,36 @@ def test_queued_iterations_equal_single_steps(capi, data):
     sv.close(); km.close()
     assert s4["outer_iters"] == cap + 1
     assert torch.equal(a4, a5) and torch.equal(f4, f5)
+
+
+_SYNC_EVERY_DIGEST = r"""
+import hashlib
+import numpy as np, torch
+from thundersvm_b200 import capi, synth
+prob = synth.config5(5000, d=200)
+y = np.where(prob["y"] > 0, 1, -1).astype(np.int32)
+km = capi.KernelMatrix(dense=torch.from_numpy(prob["X"]).cuda(), gamma=prob["gamma"])
+alpha = torch.zeros(len(y), dtype=torch.float64, device="cuda")
+f = torch.from_numpy(-y.astype(np.float64)).cuda()
+rho, st = capi.smo_solve(km, torch.from_numpy(y).cuda(), alpha, f, 1e-3, 1.0, 1.0, 512)
+h = hashlib.sha256(alpha.cpu().numpy().tobytes() + f.cpu().numpy().tobytes()).hexdigest()
+print(h, st["outer_iters"], st["local_iters"], repr(rho))
+"""
+
+
+def test_results_do_not_depend_on_how_many_iterations_are_queued():
+    """TSVM_SYNC_EVERY (read once per process) sets how many outer iterations are queued between reads of the
+    device's verdict: 1 is the reference's rhythm, 32 the most the library queues. Alpha, f, rho and the iteration
+    counts must be the same for any value."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lines = []
+    for k in ("1", "3", "32"):
+        env = dict(os.environ, TSVM_SYNC_EVERY=k, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        r = subprocess.run([sys.executable, "-c", _SYNC_EVERY_DIGEST], env=env, capture_output=True, text=True,
+                           timeout=600, cwd=root)
+        assert r.returncode == 0, r.stderr[-2000:]
+        lines.append(r.stdout.strip().splitlines()[-1])
+    assert len(lines[0].split()[0]) == 64
+    assert lines[0] == lines[1] == lines[2]
