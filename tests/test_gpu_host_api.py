@@ -155,3 +155,39 @@ def test_cached_memory_is_reused_and_released(capi):
     capi.lib().tsvm_release_cached_memory()
     assert torch.cuda.mem_get_info()[0] >= free_before - (64 << 20)
     assert torch.equal(cycle(), first)
+
+
+_PAIR_STREAMS_MODEL = r"""
+import hashlib, sys
+sys.path.insert(0, "tests")
+import numpy as np
+import host_api as H
+from thundersvm_b200 import synth
+L = H.load()
+prob = synth.config3(5000)
+h = hashlib.sha256()
+for svm_type, kw in ((0, dict(C_=prob["C"])), (1, dict(nu=0.3))):        # C-SVC and nu-SVC, ten classes = 45 pairs
+    m, nf, nc, ok = H.train(L, svm_type, X=prob["X"], y=prob["y"].astype(np.float32), gamma=prob["gamma"], **kw)
+    assert ok and nc == 10
+    h.update(H.model_text(L, m).encode())
+    L.model_free(m)
+print(h.hexdigest())
+"""
+
+
+def test_pairs_on_several_host_threads_give_the_same_model_file():
+    """SVC::train solves the class pairs of a device-resident data set from four host threads, each with a CUDA
+    stream of its own (THUNDERSVM_PAIR_STREAMS, read at every call). The pairs are independent: the model text -
+    every support vector, coefficient and rho - must be the same as with the sequential loop."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    digests = []
+    for k in ("1", "4", "4", "7"):
+        env = dict(os.environ, THUNDERSVM_PAIR_STREAMS=k, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        r = subprocess.run([sys.executable, "-c", _PAIR_STREAMS_MODEL], env=env, capture_output=True, text=True,
+                           timeout=600, cwd=root)
+        assert r.returncode == 0, r.stderr[-2000:]
+        digests.append(r.stdout.strip().splitlines()[-1])
+    assert len(digests[0]) == 64 and len(set(digests)) == 1

@@ -6,10 +6,10 @@
 #include <cstdio>
 #include <fstream>
 
-DataSet::DataSet() : total_count_(0), n_features_(0) {}
+DataSet::DataSet() : rows_(std::make_shared<node2d>()), total_count_(0), n_features_(0) {}
 
 DataSet::DataSet(const DataSet::node2d &instances, int n_features, const vector<float_type> &y)
-    : y_(y), instances_(instances), total_count_(instances.size()), n_features_(n_features) {}
+    : y_(y), rows_(std::make_shared<node2d>(instances)), total_count_(instances.size()), n_features_(n_features) {}
 
 namespace {
 // parses one "label idx:val idx:val ..." line in place; returns false for blank lines
@@ -40,7 +40,9 @@ bool parse_line(const char *p, const char *end, float_type &label, vector<DataSe
 
 void DataSet::load_from_file(string file_name) {
     LOG(INFO) << "loading dataset from file \"" << file_name << "\"";
-    y_.clear(); instances_.clear(); total_count_ = 0; n_features_ = 0;
+    rows_ = std::make_shared<node2d>();
+    node2d &instances_ = *rows_;
+    y_.clear(); total_count_ = 0; n_features_ = 0;
     std::ifstream ifs(file_name, std::ifstream::binary);
     if (!ifs.is_open()) {
         LOG(INFO) << "file " << file_name << " not found";
@@ -73,7 +75,9 @@ void DataSet::load_from_file(string file_name) {
 }
 
 void DataSet::load_from_python(float *y, char **x, int len) {
-    y_.clear(); instances_.clear(); total_count_ = 0; n_features_ = 0;
+    rows_ = std::make_shared<node2d>();
+    node2d &instances_ = *rows_;
+    y_.clear(); total_count_ = 0; n_features_ = 0;
     bool saw_zero = false;
     size_t max_index = 0;
     for (int i = 0; i < len; ++i) {
@@ -89,7 +93,9 @@ void DataSet::load_from_python(float *y, char **x, int len) {
 }
 
 void DataSet::load_from_sparse(int row_size, float *val, int *row_ptr, int *col_ptr, float *label) {
-    y_.clear(); instances_.clear(); total_count_ = 0; n_features_ = 0;
+    rows_ = std::make_shared<node2d>();
+    node2d &instances_ = *rows_;
+    y_.clear(); total_count_ = 0; n_features_ = 0;
     instances_.resize(row_size);
     for (int r = 0; r < row_size; ++r) {
         if (label) y_.push_back(label[r]);
@@ -106,10 +112,13 @@ void DataSet::load_from_sparse(int row_size, float *val, int *row_ptr, int *col_
 }
 
 void DataSet::load_from_dense(int row_size, int features, float *data, float *label) {
-    y_.clear(); instances_.clear(); total_count_ = 0;
+    rows_ = std::make_shared<node2d>();
+    node2d &instances_ = *rows_;
+    y_.clear(); total_count_ = 0;
     instances_.resize(row_size);
+    if (label) y_.assign(label, label + row_size);
+#pragma omp parallel for schedule(static)
     for (int r = 0; r < row_size; ++r) {
-        if (label) y_.push_back(label[r]);
         auto &row = instances_[r];
         row.reserve(features);
         const float *src = data + (size_t) r * features;
@@ -123,10 +132,10 @@ void DataSet::load_from_dense(int row_size, int features, float *data, float *la
 void DataSet::group_classes(bool classification) {
     start_.clear(); count_.clear(); label_.clear(); perm_.clear();
     if (!classification) {
-        perm_.resize(instances_.size());
+        perm_.resize(rows_->size());
         for (size_t i = 0; i < perm_.size(); ++i) perm_[i] = (int) i;
         start_.push_back(0);
-        count_.push_back((int) instances_.size());
+        count_.push_back((int) rows_->size());
         return;
     }
     vector<int> cls(y_.size());
@@ -151,13 +160,13 @@ const vector<int> &DataSet::count() const { return count_; }
 const vector<int> &DataSet::start() const { return start_; }
 const vector<int> &DataSet::label() const { return label_; }
 const vector<float_type> &DataSet::y() const { return y_; }
-const DataSet::node2d &DataSet::instances() const { return instances_; }
+const DataSet::node2d &DataSet::instances() const { return *rows_; }
 const bool DataSet::is_zero_based() const { return zero_based; }
 
 const DataSet::node2d DataSet::instances(int y_i) const {
     node2d out;
     out.reserve(count_[y_i]);
-    for (int k = start_[y_i]; k < start_[y_i] + count_[y_i]; ++k) out.push_back(instances_[perm_[k]]);
+    for (int k = start_[y_i]; k < start_[y_i] + count_[y_i]; ++k) out.push_back((*rows_)[perm_[k]]);
     return out;
 }
 const DataSet::node2d DataSet::instances(int y_i, int y_j) const {

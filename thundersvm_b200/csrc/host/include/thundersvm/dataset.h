@@ -4,6 +4,7 @@
 #define THUNDERSVM_DATASET_H
 #include "thundersvm.h"
 #include "syncarray.h"
+#include <memory>
 
 class DataSet {
 public:
@@ -40,7 +41,8 @@ public:
 
 private:
     vector<float_type> y_;
-    node2d instances_;
+    // shared between copies of a data set (a copy costs no rows): the loaders replace it, nothing edits it in place
+    std::shared_ptr<node2d> rows_;
     size_t total_count_;
     size_t n_features_;
     vector<int> start_, count_, label_, perm_;

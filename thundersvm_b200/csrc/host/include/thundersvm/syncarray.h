@@ -5,6 +5,8 @@
 // it. A process-wide byte counter feeds SvmModel::get_working_set_size as in the reference.
 #ifndef THUNDERSVM_SYNCARRAY_H
 #define THUNDERSVM_SYNCARRAY_H
+#include <atomic>
+#include <cuda_runtime.h>
 #include "thundersvm.h"
 #include <cstring>
 #include <new>
@@ -16,7 +18,11 @@ void copy_to_device(void *dst, const void *src, size_t bytes);
 void copy_to_host(void *dst, const void *src, size_t bytes);
 void copy_on_device(void *dst, const void *src, size_t bytes);
 void device_zero(void *p, size_t bytes);
-size_t &total_memory_size();
+std::atomic<size_t> &total_memory_size();
+// The CUDA stream this host thread's copies and library calls go to (nullptr: the default stream). SVC::train
+// gives each of its worker threads a stream of its own.
+cudaStream_t work_stream();
+void set_work_stream(cudaStream_t s);
 }  // namespace thundersvm
 
 template <typename T>

@@ -60,13 +60,13 @@ KernelMatrix::KernelMatrix(const DataSet::node2d &instances, SvmParam param) : p
             for (int p = c.row_ptr[i]; p < c.row_ptr[i + 1]; ++p) X[(size_t) i * n_features_ + c.col[p]] = c.val[p];
         b200_check(tsvm_km_create_dense(X.data(), (int) n_instances_, (int) n_features_, (int) n_features_, TSVM_HOST,
                                         param.kernel_type, param.degree, (float) param.gamma, (float) param.coef0,
-                                        nullptr, &km_));
+                                        thundersvm::work_stream(), &km_));
     } else {
         b200_check(tsvm_km_create_csr(c.val.data(), c.row_ptr.data(), c.col.data(), (int) n_instances_,
                                       (int) n_features_, TSVM_HOST, param.kernel_type, param.degree,
-                                      (float) param.gamma, (float) param.coef0, nullptr, &km_));
+                                      (float) param.gamma, (float) param.coef0, thundersvm::work_stream(), &km_));
     }
-    cudaStreamSynchronize(nullptr);          // the host staging buffers above go out of scope
+    cudaStreamSynchronize(thundersvm::work_stream());    // the host staging buffers above go out of scope
     thundersvm::total_memory_size() += (dense_ ? (size_t) dense_bytes : nnz_ * 8 + n_instances_ * 12);
     diag_.resize(n_instances_);
     thundersvm::copy_to_host(diag_.host_data(), tsvm_km_diag_dev(km_), sizeof(kernel_type) * n_instances_);
@@ -83,7 +83,7 @@ KernelMatrix::KernelMatrix(const float *X_dev, size_t d, size_t ld, size_t r0, s
     thundersvm::copy_on_device(pair_x_, X_dev + r0 * ld, n0 * ld * sizeof(float));
     thundersvm::copy_on_device(pair_x_ + n0 * ld, X_dev + r1 * ld, n1 * ld * sizeof(float));
     b200_check(tsvm_km_create_dense(pair_x_, (int) n_instances_, (int) d, (int) ld, TSVM_DEVICE, param.kernel_type,
-                                    param.degree, (float) param.gamma, (float) param.coef0, nullptr, &km_));
+                                    param.degree, (float) param.gamma, (float) param.coef0, thundersvm::work_stream(), &km_));
     const double dense_bytes = 3.0 * n_instances_ * ((n_features_ + 3) & ~3ul) * 4.0 + 1024.0 * n_instances_ * 4.0;
     thundersvm::total_memory_size() += (size_t) dense_bytes;
     diag_.resize(n_instances_);
@@ -102,7 +102,7 @@ KernelMatrix::~KernelMatrix() {
 void KernelMatrix::get_rows(const SyncArray<int> &idx, SyncArray<kernel_type> &kernel_rows) const {
     CHECK_GE(kernel_rows.size(), idx.size() * n_instances_) << "kernel_rows memory is too small";
     b200_check(tsvm_km_rows_by_index(km_, idx.device_data(), (int) idx.size(), kernel_rows.device_data(),
-                                     (long long) n_instances_, nullptr));
+                                     (long long) n_instances_, thundersvm::work_stream()));
 }
 
 void KernelMatrix::get_rows(const DataSet::node2d &instances, SyncArray<kernel_type> &kernel_rows) const {
@@ -115,8 +115,8 @@ void KernelMatrix::get_rows(const DataSet::node2d &instances, SyncArray<kernel_t
     rp.copy_from(c.row_ptr.data(), c.row_ptr.size());
     b200_check(tsvm_km_rows_by_instances_csr(km_, val.device_data(), rp.device_data(), col.device_data(),
                                              (int) instances.size(), (long long) c.val.size(), kernel_rows.device_data(),
-                                             (long long) n_instances_, nullptr));
-    cudaStreamSynchronize(nullptr);
+                                             (long long) n_instances_, thundersvm::work_stream()));
+    cudaStreamSynchronize(thundersvm::work_stream());
 }
 
 const SyncArray<kernel_type> &KernelMatrix::diag() const { return diag_; }
@@ -131,7 +131,7 @@ void CSMOSolver::solve(const KernelMatrix &k_mat, const SyncArray<int> &y, SyncA
     tsvm_solve_stats st;
     double rho_out = 0;
     b200_check(tsvm_smo_solve(k_mat.handle(), solver_kind(), y.device_data(), alpha.device_data(), f_val.device_data(),
-                              eps, Cp, Cn, ws_size, max_iter, &rho_out, &st, nullptr));
+                              eps, Cp, Cn, ws_size, max_iter, &rho_out, &st, thundersvm::work_stream()));
     rho = rho_out;
     LOG(INFO) << "global iter = " << st.outer_iters - 1 << ", total local iter = " << st.local_iters << ", diff = "
               << st.final_diff;

@@ -2,6 +2,10 @@
 // extraction, voting / probabilities, cross validation and the LibSVM-compatible model text follow
 // the reference (src/thundersvm/model/{svmmodel,svc,nusvc,svr,nusvr,oneclass_svc}.cpp); every
 // numerical step goes through KernelMatrix / CSMOSolver / NuSMOSolver or the C ABI directly.
+#include <atomic>
+#include <exception>
+#include <mutex>
+#include <thread>
 #include <thundersvm/model/svmmodel.h>
 #include <thundersvm/model/svc.h>
 #include <thundersvm/model/nusvc.h>
@@ -375,9 +379,13 @@ void SVC::build_device_rows(const DataSet &ds) {
     if (n == 0) return;
     size_t nnz = 0;
     int mx = 0;
-    for (auto &r : ds.instances()) {
-        nnz += r.size();
-        for (auto &nd : r) if (nd.index > mx) mx = nd.index;
+    {
+        const DataSet::node2d &all = ds.instances();
+#pragma omp parallel for schedule(static) reduction(+ : nnz) reduction(max : mx)
+        for (long r = 0; r < (long) all.size(); ++r) {
+            nnz += all[r].size();
+            for (auto &nd : all[r]) if (nd.index > mx) mx = nd.index;
+        }
     }
     const size_t d = (size_t) mx + 1, ld = (d + 3) & ~(size_t) 3;
     const double density = (double) nnz / ((double) n * d);
@@ -408,16 +416,57 @@ void SVC::train(const DataSet &dataset, SvmParam param) {
     if (n_classes > 2) build_device_rows(ds);       // two classes: one sub-problem, nothing to share
     vector<std::unique_ptr<SyncArray<float_type>>> alpha(n_binary_models);
     vector<char> is_sv(ds.n_instances(), 0);
-    int k = 0;
+    vector<std::pair<int, int>> pairs;
     for (int i = 0; i < n_classes; ++i)
-        for (int j = i + 1; j < n_classes; ++j, ++k) {
-            alpha[k].reset(new SyncArray<float_type>());
-            train_binary(ds, i, j, *alpha[k], rho.host_data()[k]);
-            const vector<int> ids = ds.original_index(i, j);
-            CHECK_EQ(ids.size(), alpha[k]->size());
-            const float_type *a = alpha[k]->host_data();
-            for (size_t l = 0; l < ids.size(); ++l) if (a[l] != 0) is_sv[ids[l]] = 1;
-        }
+        for (int j = i + 1; j < n_classes; ++j) pairs.emplace_back(i, j);
+    for (auto &a : alpha) a.reset(new SyncArray<float_type>());
+    float_type *rho_h = rho.host_data();
+    // The binary problems are independent (svc.cpp:50-61 solves them one after the other). With the data set on
+    // the device, a few host threads take them from a common counter, each with a CUDA stream of its own, so
+    // that the short launches and host waits of one solve fill the gaps of another; the model does not depend
+    // on the order. THUNDERSVM_PAIR_STREAMS=1 keeps the loop sequential.
+    int n_threads = 1;
+    if (dev_rows_.X && pairs.size() > 1) {
+        const char *e = getenv("THUNDERSVM_PAIR_STREAMS");
+        n_threads = e ? atoi(e) : 4;
+        if (n_threads < 1) n_threads = 1;
+        if (n_threads > (int) pairs.size()) n_threads = (int) pairs.size();
+    }
+    if (n_threads <= 1) {
+        for (size_t k = 0; k < pairs.size(); ++k) train_binary(ds, pairs[k].first, pairs[k].second, *alpha[k], rho_h[k]);
+    } else {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        std::atomic<size_t> next{0};
+        std::mutex err_mu;
+        std::exception_ptr err;
+        vector<std::thread> pool;
+        for (int t = 0; t < n_threads; ++t)
+            pool.emplace_back([&, dev]() {
+                cudaSetDevice(dev);
+                cudaStream_t s = nullptr;
+                if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) s = nullptr;
+                thundersvm::set_work_stream(s);
+                try {
+                    for (size_t k = next++; k < pairs.size(); k = next++)
+                        train_binary(ds, pairs[k].first, pairs[k].second, *alpha[k], rho_h[k]);
+                } catch (...) {
+                    std::lock_guard<std::mutex> lk(err_mu);
+                    if (!err) err = std::current_exception();
+                    next = pairs.size();            // the other workers stop after their current pair
+                }
+                if (s) { cudaStreamSynchronize(s); cudaStreamDestroy(s); }
+                thundersvm::set_work_stream(nullptr);
+            });
+        for (auto &th : pool) th.join();
+        if (err) std::rethrow_exception(err);
+    }
+    for (size_t k = 0; k < pairs.size(); ++k) {
+        const vector<int> ids = ds.original_index(pairs[k].first, pairs[k].second);
+        CHECK_EQ(ids.size(), alpha[k]->size());
+        const float_type *a = alpha[k]->host_data();
+        for (size_t l = 0; l < ids.size(); ++l) if (a[l] != 0) is_sv[ids[l]] = 1;
+    }
     free_device_rows();
     // support vectors in class order; n_sv per class
     int *cnt = n_sv.host_data();
@@ -434,7 +483,7 @@ void SVC::train(const DataSet &dataset, SvmParam param) {
     // coefficient layout (svmmodel.h:155-164): pair (i, j) writes class i's alphas into row j-1 and
     // class j's into row i, at the classes' support-vector positions
     float_type *cf = coef.host_data();
-    k = 0;
+    int k = 0;
     for (int i = 0; i < n_classes; ++i)
         for (int j = i + 1; j < n_classes; ++j, ++k) {
             const float_type *a = alpha[k]->host_data();

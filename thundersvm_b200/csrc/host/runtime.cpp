@@ -26,12 +26,25 @@ void *device_alloc(size_t bytes) {
     return p;
 }
 void device_free(void *p) { tsvm::pool_free(p); }
-void copy_to_device(void *dst, const void *src, size_t bytes) { cuda_ok(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice), "H2D copy"); }
-void copy_to_host(void *dst, const void *src, size_t bytes) { cuda_ok(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost), "D2H copy"); }
-void copy_on_device(void *dst, const void *src, size_t bytes) { cuda_ok(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToDevice), "D2D copy"); }
-void device_zero(void *p, size_t bytes) { cuda_ok(cudaMemset(p, 0, bytes), "cudaMemset"); }
-size_t &total_memory_size() {
-    static size_t bytes = 0;
+static thread_local cudaStream_t tl_stream = nullptr;
+cudaStream_t work_stream() { return tl_stream; }
+void set_work_stream(cudaStream_t s) { tl_stream = s; }
+// Copies are ordered on the calling thread's stream; those that touch host memory return when they are done,
+// as cudaMemcpy does.
+void copy_to_device(void *dst, const void *src, size_t bytes) {
+    cuda_ok(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, tl_stream), "H2D copy");
+    cuda_ok(cudaStreamSynchronize(tl_stream), "H2D copy");
+}
+void copy_to_host(void *dst, const void *src, size_t bytes) {
+    cuda_ok(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, tl_stream), "D2H copy");
+    cuda_ok(cudaStreamSynchronize(tl_stream), "D2H copy");
+}
+void copy_on_device(void *dst, const void *src, size_t bytes) {
+    cuda_ok(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, tl_stream), "D2D copy");
+}
+void device_zero(void *p, size_t bytes) { cuda_ok(cudaMemsetAsync(p, 0, bytes, tl_stream), "cudaMemset"); }
+std::atomic<size_t> &total_memory_size() {
+    static std::atomic<size_t> bytes{0};
     return bytes;
 }
 }  // namespace thundersvm
