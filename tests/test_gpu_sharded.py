@@ -158,3 +158,38 @@ def test_one_vs_one_pairs_on_several_streams_give_the_same_model(capi):
         assert many["n_sv"] == one["n_sv"]
         assert np.array_equal(many["sv_index"], one["sv_index"])
         assert np.array_equal(many["coef"], one["coef"]) and np.array_equal(many["rho"], one["rho"])
+
+
+def test_three_call_form_of_one_shard_equals_the_plain_solver(capi):
+    """tsvm_shard_candidates / _select / _iterate - the form a caller with its own collectives drives, here with
+    one shard and plain copies in place of the collectives - must give the plain solver's alpha, f and counts."""
+    import torch
+    prob = synth.config5(5000, d=256)
+    y = binary_labels(prob)
+    n = len(y)
+    X = torch.from_numpy(prob["X"]).cuda()
+    yt = torch.from_numpy(y).cuda()
+    a1 = torch.zeros(n, dtype=torch.float64, device="cuda")
+    f1 = -yt.to(torch.float64)
+    km1 = capi.KernelMatrix(dense=X, gamma=prob["gamma"])
+    _, st1 = capi.smo_solve(km1, yt, a1, f1, 1e-3, 1.0, 1.0, 1024)
+    km1.close()
+    a2 = torch.zeros(n, dtype=torch.float64, device="cuda")
+    f2 = -yt.to(torch.float64)
+    km2 = capi.KernelMatrix(dense=X, gamma=prob["gamma"])
+    sh = capi.Shard(km2, yt, a2, f2, n, 0, 1e-3, 1.0, 1.0, 1024, 1)
+    done, steps = False, 0
+    while not done:
+        lists, want = sh.candidates()
+        m = lists * want
+        sh.all_f[:m].copy_(sh.cand_f[:m])
+        sh.all_id[:m].copy_(sh.cand_id[:m])
+        sh.select()
+        done = sh.iterate()
+        steps += 1
+        assert steps < 5000
+    st2 = sh.stats()
+    assert steps == st1["outer_iters"] == st2["outer_iters"] and st2["local_iters"] == st1["local_iters"]
+    assert torch.equal(a1, a2) and torch.equal(f1, f2)
+    sh.close()
+    km2.close()
