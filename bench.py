@@ -81,9 +81,7 @@ def cpu_backend():
     from oracle import ref_binding as R
     if R.available():
         R.lib().ref_set_threads(cores)
-        # "reference": the reference's own CPU sources compiled where they lie; the `build` key says that its three
-        # Eigen products are restated as plain loops
-        return R, "reference", int(R.lib().ref_max_threads())
+        return R, "reference+eigenfree", int(R.lib().ref_max_threads())
     os.environ["OMP_NUM_THREADS"] = str(cores)
     from oracle import port_binding as P
     return P, "port", cores
